@@ -1,0 +1,59 @@
+"""CPU tests pinning the numpy checker (oracle/) to neon's NervanaCPU."""
+import os
+
+import numpy as np
+import pytest
+
+from oracle.numpy_backend import OracleBackend
+from tests.cases import run_case, standard_cases, summarize
+
+CASES = standard_cases()
+REFERENCE = os.environ.get("NEON_REFERENCE", "/root/reference")
+
+
+def _check(fingerprint, golden, prefix):
+    for field, val in fingerprint.items():
+        want = golden["%s/%s" % (prefix, field)]
+        if np.asarray(val).dtype.kind in "iub":
+            assert np.array_equal(val, want), prefix
+        else:
+            # same numpy calls in the same order: identical bits expected; the
+            # tolerance only absorbs a different numpy build's libm
+            np.testing.assert_allclose(val, want, rtol=1e-6, atol=1e-7, err_msg=prefix)
+
+
+@pytest.mark.parametrize("case", CASES, ids=lambda c: c.name)
+def test_oracle_reproduces_reference_golden(case, golden):
+    for dt in (np.float32, np.float64):
+        be = OracleBackend(default_dtype=dt)
+        with np.errstate(all="ignore"):
+            res = run_case(be, case, compute_dtype=dt)
+        for k, arr in res.items():
+            if k.startswith("grad"):
+                continue
+            _check(summarize(arr), golden, "%s/%s/%s" % (case.name, np.dtype(dt).name, k))
+
+
+@pytest.mark.skipif(not os.path.isdir(os.path.join(REFERENCE, "neon", "backends")),
+                    reason="no neon checkout on this machine")
+def test_oracle_matches_live_reference_bit_for_bit():
+    from tests.golden.make_golden import import_reference_cpu
+    NervanaCPU = import_reference_cpu(REFERENCE)
+    for case in CASES:
+        for dt in (np.float32, np.float64):
+            with np.errstate(all="ignore"):
+                ref = run_case(NervanaCPU(default_dtype=dt), case, compute_dtype=dt)
+                got = run_case(OracleBackend(default_dtype=dt), case, compute_dtype=dt)
+            for k in ref:
+                assert ref[k].dtype == got[k].dtype, (case.name, k)
+                assert np.array_equal(ref[k], got[k], equal_nan=True), (case.name, k)
+
+
+def test_onehot_assignment_matches_reference_rule():
+    be = OracleBackend()
+    idx = be.array(np.array([[2, 0, 3, 1, 1]], dtype=np.int32), dtype=np.int32)
+    out = be.zeros((4, 5))
+    out[:] = be.onehot(idx, axis=0)
+    want = np.zeros((4, 5), np.float32)
+    want[[2, 0, 3, 1, 1], np.arange(5)] = 1
+    assert np.array_equal(out.get(), want)
