@@ -1,0 +1,23 @@
+"""
+neon_b200 -- a B200-native backend for neon's compound op-tree tensor engine.
+
+    from neon_b200 import gen_backend
+    be = gen_backend(backend="b200", rng_seed=0)
+    x = be.array(host_array)
+    out = be.empty((1, x.shape[1]))
+    out[:] = be.sum(be.exp(x - be.max(x, axis=0)), axis=0)     # fused kernels on the GPU
+"""
+
+from .optree import OpCollection, OpTreeNode, Tensor          # noqa: F401
+
+
+def gen_backend(*args, **kwargs):
+    from .backend import gen_backend as _gen
+    return _gen(*args, **kwargs)
+
+
+def __getattr__(name):
+    if name in ("B200Backend", "B200Tensor"):
+        from . import backend, tensor
+        return {"B200Backend": backend.B200Backend, "B200Tensor": tensor.B200Tensor}[name]
+    raise AttributeError(name)

@@ -1,0 +1,410 @@
+"""
+The ``b200`` backend: executes op-trees on one B200 through libb200ew.so.
+
+Stands where neon's ``NervanaGPU`` stands for the op-tree path
+(neon/backends/nervanagpu.py:694-1439, 1825-1861, 3138-3231): same constructor
+keywords as ``gen_backend`` forwards (neon/backends/__init__.py:107-114), same
+tensor factories, ``execute``, RNG state functions and timing marks.  Methods
+of the abstract backend that are not op-tree work (GEMM, convolution, pooling,
+lookup tables) raise ``NotImplementedError``.
+"""
+
+import numpy as np
+
+from . import runtime as rt
+from .lowering import Planner, Statement
+from .optree import OpCollection, OpTreeBackend, OpTreeNode, Tensor
+from .tensor import B200Tensor
+
+_COUNTER_BYTES = 1 << 20          # zero-initialised arrival counters, reset by the kernels
+_SCRATCH_BYTES = 64 << 20
+
+
+class _Scratch(object):
+    """Bump allocator over two persistent device buffers: reduction results and
+    partials (reused by every statement; the stream orders the reuse) and the
+    arrival counters of split reductions (zeroed once, left zero by every kernel)."""
+
+    def __init__(self):
+        self.data = rt.malloc(_SCRATCH_BYTES)
+        self.data_size = _SCRATCH_BYTES
+        self.counters = rt.malloc(_COUNTER_BYTES)
+        rt.memset(self.counters, 0, 1, _COUNTER_BYTES)
+        self.reset()
+
+    def reset(self):
+        self.off = 0
+        self.coff = 0
+
+    def __call__(self, nbytes, zero):
+        nbytes = (nbytes + 255) & ~255
+        if zero:
+            if self.coff + nbytes > _COUNTER_BYTES:
+                raise MemoryError("split-reduction counters exceed %d bytes" % _COUNTER_BYTES)
+            p = self.counters + self.coff
+            self.coff += nbytes
+            return p
+        if self.off + nbytes > self.data_size:
+            raise MemoryError("statement needs more than %d bytes of reduction scratch" % self.data_size)
+        p = self.data + self.off
+        self.off += nbytes
+        return p
+
+    def release(self):
+        for p in (self.data, self.counters):
+            try:
+                rt.free(p)
+            except Exception:
+                pass
+
+
+class B200Backend(OpTreeBackend):
+    backend_name = "b200"
+    tensor_cls = B200Tensor
+
+    def __init__(self, rng_seed=None, default_dtype=np.float32, stochastic_round=False,
+                 deterministic_update=False, deterministic=None, device_id=0, bench=False,
+                 scratch_size=0, hist_bins=64, hist_offset=-48, compat_mode=None,
+                 enable_winograd=True, cache_dir=None, num_devices=None, max_devices=None):
+        if default_dtype not in (np.float16, np.float32):
+            raise ValueError("Default data type for the b200 backend must be float16 or 32")
+        if rt.device_count() <= int(device_id):
+            raise RuntimeError("b200 backend needs CUDA device %d; none is visible" % int(device_id))
+        rt.init(int(device_id))
+        self.device_id = int(device_id)
+        props = rt.device_props(self.device_id)
+        self.sm_count = props.sm_count
+        self.compute_capability = (props.cc_major, props.cc_minor)
+        self.device_name = props.name.decode()
+        self.stream = rt.default_stream()
+        self.bench = bench
+        self.use_pinned_mem = True
+        self.round_mode = None
+        self.set_stochastic_round(stochastic_round)
+        self._scratch = _Scratch()
+        self._planner = Planner(self.sm_count)
+        self._kernels = {}
+        self._temps = {}
+        self._temps_used = {}
+        self._marks = []
+        self.launches = 0                  # kernels launched so far (statements may take several)
+        self.launch_log = None             # set to a list to record (kind, desc) per launch
+        super(B200Backend, self).__init__(rng_seed, default_dtype, compat_mode=compat_mode,
+                                          deterministic=deterministic)
+
+    # ------------------------------------------------------------------ lifecycle
+    def cleanup_backend(self):
+        sc = getattr(self, "_scratch", None)
+        if sc is not None:
+            sc.release()
+            self._scratch = None
+
+    def __del__(self):
+        try:
+            self.cleanup_backend()
+        except Exception:
+            pass
+
+    def set_stochastic_round(self, rounding):
+        """True -> 10 mantissa bits; an int -> that many; False/0 -> nearest
+        (neon/backends/nervanagpu.py:892-899)."""
+        if rounding is True:
+            self.round_mode = 10
+        elif rounding:
+            self.round_mode = int(rounding)
+        else:
+            self.round_mode = 0
+
+    # ------------------------------------------------------------------ RNG (nervanagpu.py:901-1049)
+    def gen_rng(self, seed=None):
+        self.rng = np.random.RandomState(seed)
+        self.init_rng_state = self.rng.get_state()
+        # device generator: counter based, keyed by a seed drawn without
+        # advancing the host generator
+        save = self.rng.get_state()
+        dev_seed = int(self.rng.randint(0, 2 ** 31 - 1)) | (int(self.rng.randint(0, 2 ** 31 - 1)) << 31)
+        self.rng.set_state(save)
+        self.init_rng_state_dev = (dev_seed, 0)
+        rt.rng_set_state(self.init_rng_state_dev)
+        return self.rng
+
+    def rng_reset(self):
+        self.rng_set_state((self.init_rng_state, self.init_rng_state_dev))
+
+    def rng_set_state(self, rng_states):
+        if len(rng_states) != 2:
+            self.rng_reset()
+            self.rng.set_state(rng_states)
+            return
+        rt.rng_set_state(rng_states[1])
+        self.rng.set_state(rng_states[0])
+
+    def rng_get_state(self):
+        return (self.rng.get_state(), np.array(rt.rng_get_state(), dtype=np.uint64))
+
+    # ------------------------------------------------------------------ execute
+    def execute(self, optree):
+        """
+        Run one assignment.  A tree whose reductions share an axis is one
+        statement; otherwise inner results are first materialised into pooled
+        temporaries, as ``_split_to_stacks`` does (nervanagpu.py:1099-1283).
+        Whole-tensor reductions of contiguous operands become a single flat pass.
+        """
+        assert optree[0]["op"] == "assign"
+        out, rhs = optree[1], optree[2]
+        stmts = []
+        self._temps_used = {}
+        expr, tag = self._split(rhs, stmts)
+        if tag == "flat" and tuple(out.shape) != (1, 1):
+            expr = self._materialise(expr, (1, 1), stmts)
+        for dst, tree in stmts:
+            self._run(dst, tree)
+        self._run(out, expr)
+        return out
+
+    # -- splitting ----------------------------------------------------------------
+    def _temp(self, shape):
+        """Pooled temporary of the default dtype, keyed by shape and by how many
+        of that shape this statement already holds (nervanagpu.py:1051-1075)."""
+        shape = tuple(shape)
+        used = self._temps_used.get(shape, 0)
+        self._temps_used[shape] = used + 1
+        pool = self._temps.setdefault(shape, [])
+        while len(pool) <= used:
+            pool.append(self.empty(shape, dtype=self.default_dtype))
+        return pool[used]
+
+    def _materialise(self, expr, shape, stmts):
+        buf = self._temp(shape)
+        stmts.append((buf, expr))
+        return buf
+
+    @staticmethod
+    def _flat_leaves_ok(node, shape_box):
+        """True when every tensor under ``node`` is contiguous with one common shape
+        (or is a (1,1) scalar) and there is no reduction or addressing op inside."""
+        if isinstance(node, OpTreeNode):
+            op = node[0]["op"]
+            if op in OpCollection.reduction_ops or op in ("dot", "transpose", "onehot", "rand"):
+                return False
+            return all(B200Backend._flat_leaves_ok(c, shape_box) for c in node[1:] if c is not None)
+        if isinstance(node, Tensor):
+            if tuple(node.shape) == (1, 1):
+                return True
+            if not node.is_contiguous or node.take_array or len(node.shape) != 2:
+                return False
+            if shape_box[0] is None:
+                shape_box[0] = tuple(node.shape)
+            return shape_box[0] == tuple(node.shape)
+        return True
+
+    @staticmethod
+    def _flatten(node, size):
+        if isinstance(node, OpTreeNode):
+            info = dict(node[0])
+            info["shape"] = (1, size)
+            return OpTreeNode(info, *[B200Backend._flatten(c, size) if c is not None else None
+                                      for c in node[1:]])
+        if isinstance(node, Tensor) and tuple(node.shape) != (1, 1):
+            return node.reshape(1, size)
+        return node
+
+    def _split(self, node, stmts):
+        """Returns (expression, tag): tag is None (no reduction inside), 0/1 (reduces
+        along that axis) or 'flat' (contains a fused whole-tensor reduction and only
+        (1,1)-shaped values around it)."""
+        if not isinstance(node, OpTreeNode):
+            return node, None
+        info = node[0]
+        op = info["op"]
+        if op in OpCollection.reduction_ops:
+            axis = info["axis"]
+            child = node[1]
+            if (op in ("sum", "max", "min") and isinstance(child, OpTreeNode) and child[0]["op"] == op
+                    and child[0].get("axis") == 1 - axis):
+                inner, itag = self._split(child[1], stmts)
+                box = [None]
+                if itag is None and self._flat_leaves_ok(inner, box) and box[0] is not None:
+                    size = box[0][0] * box[0][1]
+                    flat = self._flatten(inner, size)
+                    return OpTreeNode({"op": op, "axis": 1, "shape": (1, 1)}, flat, None), "flat"
+                # not fusable: reduce along the inner axis, then along this one
+                if itag is not None and itag != 1 - axis:
+                    inner = self._materialise(inner, (1, 1) if itag == "flat" else inner.shape, stmts)
+                operand = self._materialise(OpTreeNode(child[0], inner, None), child[0]["shape"], stmts)
+                return OpTreeNode(info, operand, None), axis
+            operand, prev = self._split(child, stmts)
+            if prev is not None and prev != axis:
+                shape = (1, 1) if prev == "flat" else operand.shape
+                operand = self._materialise(operand, shape, stmts)
+            return OpTreeNode(info, operand, None), axis
+        if op == "transpose":
+            operand, _ = self._split(node[1], stmts)
+            if isinstance(operand, Tensor):
+                return operand.T, None
+            return self._materialise(operand, operand.shape, stmts).T, None
+        if op == "dot":
+            raise NotImplementedError("dot inside an op-tree is outside this backend's op-tree path")
+        if op in OpCollection.unary_ops or node[2] is None:
+            operand, tag = self._split(node[1], stmts)
+            return OpTreeNode(info, operand, None), tag
+        left, lt = self._split(node[1], stmts)
+        right, rt_ = self._split(node[2], stmts)
+        if lt is not None and rt_ is not None and lt != rt_:
+            # two sides reduce differently: evaluate one of them first.  A flat side
+            # is a (1,1) value; otherwise the side reducing along axis 0 goes first
+            # unless axis 0 is the more frequent one (nervanagpu.py:1112-1118,1188-1206)
+            if lt == "flat" or (rt_ != "flat" and lt == 0):
+                left = self._materialise(left, (1, 1) if lt == "flat" else left.shape, stmts)
+                lt = None
+            else:
+                right = self._materialise(right, (1, 1) if rt_ == "flat" else right.shape, stmts)
+                rt_ = None
+        tag = lt if lt is not None else rt_
+        if tag == "flat":
+            other = right if lt is not None else left
+            if lt is not None and rt_ is not None:
+                other = None
+            if isinstance(other, (Tensor, OpTreeNode)) and tuple(other.shape) != (1, 1):
+                # a whole-tensor reduction meets a full-size operand
+                if lt == "flat":
+                    left, tag = self._materialise(left, (1, 1), stmts), None
+                else:
+                    right, tag = self._materialise(right, (1, 1), stmts), None
+        return OpTreeNode(info, left, right), tag
+
+    # -- one statement ------------------------------------------------------------
+    def _run(self, out, expr):
+        stack = OpTreeNode({"op": "assign"}, out, expr).traverse([])
+        st = Statement(stack)
+        rounding = self._rounding_bits(out)
+        self._scratch.reset()
+        passes = self._planner.plan(st, self._scratch, rounding=rounding)
+        for pz in passes:
+            kernel = self._kernels.get(pz.source)
+            if kernel is None:
+                kernel = self._kernels[pz.source] = rt.kernel_get(pz.source)
+            if pz.uses_rng:
+                k0, k1 = rt.rng_next_key()
+                pz.fields.values["rk0"] = k0
+                pz.fields.values["rk1"] = k1
+            rt.launch(kernel, pz.grid, pz.block, pz.fields.pack(), stream=self.stream)
+            self.launches += 1
+            if self.launch_log is not None:
+                self.launch_log.append((pz.kind, pz.desc))
+
+    def _rounding_bits(self, out):
+        """Mantissa bits for a stochastic store, 0 for nearest (float_ew.py:827-844)."""
+        rounding = out.rounding
+        if not rounding:
+            return 0
+        if rounding is True:
+            rounding = 10
+        elif out.dtype.type is np.float32:
+            rounding = min(int(rounding), 15)
+        elif out.dtype.type is np.float16:
+            rounding = min(int(rounding), 10)
+        return max(int(rounding), 1)
+
+    # ------------------------------------------------------------------ factories (nervanagpu.py:1285-1439)
+    def empty(self, shape, dtype=None, name=None, persist_values=True,
+              parallel=False, distributed=False, allocator=None):
+        dtype = self.default_dtype if dtype is None else dtype
+        return B200Tensor(self, shape, dtype=dtype, name=name, persist_values=persist_values,
+                          rounding=self.round_mode)
+
+    def array(self, ary, dtype=None, name=None, persist_values=True,
+              parallel=False, distributed=False, allocator=None):
+        dtype = self.default_dtype if dtype is None else dtype
+        ary = np.asarray(ary)
+        if ary.ndim < self._min_dims:
+            ary = ary.reshape(ary.size, 1)
+        if ary.dtype != np.dtype(dtype):
+            ary = ary.astype(dtype)
+        return B200Tensor(self, ary.shape, dtype=dtype, name=name, persist_values=persist_values,
+                          rounding=self.round_mode).set(ary)
+
+    def zeros(self, shape, dtype=None, name=None, persist_values=True,
+              parallel=False, distributed=False, allocator=None):
+        t = self.empty(shape, dtype=dtype, name=name, persist_values=persist_values)
+        return t._assign(0)
+
+    def ones(self, shape, dtype=None, name=None, persist_values=True,
+             parallel=False, distributed=False, allocator=None):
+        t = self.empty(shape, dtype=dtype, name=name, persist_values=persist_values)
+        return t._assign(1)
+
+    def empty_like(self, other, name=None, persist_values=True):
+        return B200Tensor(self, other.shape, dtype=other.dtype, name=name,
+                          persist_values=persist_values, rounding=self.round_mode)
+
+    def zeros_like(self, other, name=None, persist_values=True):
+        return self.empty_like(other, name=name, persist_values=persist_values)._assign(0)
+
+    # ------------------------------------------------------------------ random ops (nervanagpu.py:1825-1861)
+    def rand(self, out=None):
+        return OpTreeNode.build("rand", None, None, out=out)
+
+    def dropout(self, keep=0.5, out=None):
+        return self.less_equal(self.rand(), keep, out=out)
+
+    def make_binary_mask(self, out, keepthresh=0.5):
+        self.dropout(keep=keepthresh, out=out)
+
+    def fill_normal(self, ary, mean=0, stdv=1):
+        ary[:] = (self.rng.standard_normal(ary.shape) * stdv + mean).astype(ary.dtype)
+
+    # ------------------------------------------------------------------ thin op-tree wrappers (nervanagpu.py:3179-3231)
+    def fprop_relu(self, layer, x, slope):
+        return self.maximum(x, 0) + slope * self.minimum(0, x)
+
+    def bprop_relu(self, layer, x, error, deltas, slope):
+        return self.greater(x, 0) + slope * self.less(x, 0)
+
+    def fprop_softmax(self, x, axis):
+        return (self.reciprocal(self.sum(self.exp(x - self.max(x, axis=axis)), axis=axis)) *
+                self.exp(x - self.max(x, axis=axis)))
+
+    def fprop_skipnode(self, x, y, beta):
+        y[:] = y * beta + x
+
+    def bprop_skipnode(self, error, deltas, alpha, beta):
+        deltas[:] = deltas * beta + alpha * error
+
+    # ------------------------------------------------------------------ timing marks (nervanagpu.py:3138-3177)
+    def init_mark(self):
+        ev = rt.event_create()
+        self._marks.append(ev)
+        return ev
+
+    def record_mark(self, marker):
+        rt.event_record(marker, self.stream)
+
+    def synchronize_mark(self, marker):
+        rt.event_sync(marker)
+
+    def get_time(self, start, end):
+        return rt.event_elapsed_ms(start, end)
+
+    def synchronize(self):
+        rt.stream_sync(self.stream)
+
+    # ------------------------------------------------------------------ not on the op-tree path
+    def _off_path(self, *a, **k):
+        raise NotImplementedError("outside the compound op-tree path of the b200 backend")
+
+    compound_dot = batched_dot = conv_layer = deconv_layer = fprop_conv = bprop_conv = _off_path
+    update_conv = pool_layer = fprop_pool = bprop_pool = compound_bprop_lut = _off_path
+
+
+def gen_backend(backend="b200", rng_seed=None, datatype=np.float32, batch_size=0,
+                stochastic_round=False, device_id=0, max_devices=None, compat_mode=None,
+                deterministic_update=None, deterministic=None):
+    """Same call as ``neon.backends.gen_backend`` (neon/backends/__init__.py:49-120)
+    for the one backend this package provides."""
+    if backend != "b200":
+        raise ValueError("backend must be one of ('b200')")
+    be = B200Backend(rng_seed=rng_seed, default_dtype=datatype, stochastic_round=stochastic_round,
+                     device_id=device_id, compat_mode=compat_mode, deterministic=deterministic)
+    be.bsz = batch_size
+    return be

@@ -1,0 +1,114 @@
+// Kernels that are compiled into libb200ew.so at build time (no NVRTC needed):
+// pattern fills behind b200_memset, and the whole-tensor reduction behind
+// b200_reduce_full, which instantiates the same red_rows_kernel skeleton the
+// run-time generated op-tree kernels use.
+
+#include "b200ew.h"
+#include "optree_templates.cuh"
+
+#include <cuda_runtime.h>
+
+namespace {
+
+template <typename T>
+__global__ void __launch_bounds__(256) fill_kernel(T* dst, T value, u64 count) {
+    u64 i = (u64)blockIdx.x * blockDim.x + threadIdx.x;
+    const u64 step = (u64)gridDim.x * blockDim.x;
+    for (; i < count; i += step) dst[i] = value;
+}
+
+// ---- whole-tensor reduction: one kept index (K = 1), row = all elements
+struct RP {
+    u64 t0, part_v, part_i, counters, o;
+    i64 K, N, nvec, seg;
+    int split, pad_;
+};
+
+template <int DT, int OP, bool ABS>
+struct FullRed {
+    template <int V>
+    struct S {
+        enum { NRED = 1 };
+        static DEV constexpr int op(int) { return OP; }
+        struct H { int unused_; };
+        struct L { u32 a0[(b200::dt_size<DT>::value * V + 3) / 4]; };
+        static DEV void load_h(const RP&, i64, H&) {}
+        static DEV void load_l(const RP& p, i64, i64 n, L& l) { b200::ld_w<DT, V, true>(p.t0, n, l.a0); }
+        static DEV void eval(const RP&, const H&, const L& l, i64, i64, float (&out)[1][V]) {
+            float a0[V];
+            b200::cvt_in<DT, V>(l.a0, a0);
+#pragma unroll
+            for (int i = 0; i < V; ++i) out[0][i] = ABS ? fabsf(a0[i]) : a0[i];
+        }
+        static DEV void epilogue(const RP& p, i64, const float* r, const int*) {
+            *reinterpret_cast<float*>(p.o) = r[0];
+        }
+    };
+};
+
+template <int DT, int OP, bool ABS, int V>
+__global__ void __launch_bounds__(256) full_reduce_kernel(const __grid_constant__ RP p) {
+    b200::red_rows_kernel<FullRed<DT, OP, ABS>::template S, RP, V, 256, 256, 4>(p);
+}
+
+template <int DT, int OP, bool ABS>
+cudaError_t launch_full(const RP& p, bool vec, unsigned grid, cudaStream_t s) {
+    constexpr int V = 16 / b200::dt_size<DT>::value;
+    if (vec) full_reduce_kernel<DT, OP, ABS, V><<<grid, 256, 0, s>>>(p);
+    else full_reduce_kernel<DT, OP, ABS, 1><<<grid, 256, 0, s>>>(p);
+    return cudaGetLastError();
+}
+
+template <int DT>
+cudaError_t launch_full_dt(const RP& p, int op, bool absolute, bool vec, unsigned grid, cudaStream_t s) {
+    if (op == B200_SUM) return absolute ? launch_full<DT, b200::OP_SUM, true>(p, vec, grid, s) : launch_full<DT, b200::OP_SUM, false>(p, vec, grid, s);
+    if (op == B200_MAX) return absolute ? launch_full<DT, b200::OP_MAX, true>(p, vec, grid, s) : launch_full<DT, b200::OP_MAX, false>(p, vec, grid, s);
+    return absolute ? launch_full<DT, b200::OP_MIN, true>(p, vec, grid, s) : launch_full<DT, b200::OP_MIN, false>(p, vec, grid, s);
+}
+
+}  // namespace
+
+enum { kMaxSplit = 4096, kCounterBytes = 256 };
+
+// used by runtime.cpp
+extern "C" int b200_detail_fill(void* dst, uint32_t value, int width, uint64_t count, void* stream) {
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    u64 blocks = (count + 255) / 256;
+    if (blocks > 148 * 16) blocks = 148 * 16;
+    if (width == 2) fill_kernel<u16><<<(unsigned)blocks, 256, 0, s>>>(static_cast<u16*>(dst), (u16)value, count);
+    else fill_kernel<u32><<<(unsigned)blocks, 256, 0, s>>>(static_cast<u32*>(dst), value, count);
+    return (int)cudaGetLastError();
+}
+
+extern "C" uint64_t b200_reduce_scratch_bytes(void) { return kCounterBytes + 4ull * kMaxSplit; }
+
+// Fills the parameter block and picks the grid; shared with the variant that
+// keeps its scratch in a static device array.
+extern "C" int b200_detail_reduce_full(uint64_t in, int32_t dtype, uint64_t count, int32_t op, int32_t absolute,
+                                       uint64_t out, uint64_t scratch, int sm_count, void* stream) {
+    RP p;
+    const int isz = dtype == B200_F32 ? 4 : 2;
+    const int V = 16 / isz;
+    const bool vec = (in % 16) == 0 && count >= (uint64_t)V;
+    const int v = vec ? V : 1;
+    p.t0 = in; p.o = out;
+    p.counters = scratch;
+    p.part_v = scratch + kCounterBytes;
+    p.part_i = 0;
+    p.K = 1; p.N = (i64)count; p.nvec = (i64)(count / v);
+    i64 split = p.nvec / (256 * 4);
+    const i64 target = (i64)sm_count * 8;
+    if (split > target) split = target;
+    if (split > kMaxSplit) split = kMaxSplit;
+    if (split < 1) split = 1;
+    p.seg = (p.nvec + split - 1) / split;
+    split = (p.nvec + p.seg - 1) / p.seg;
+    if (split < 1) split = 1;
+    p.split = (int)split; p.pad_ = 0;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    cudaError_t e;
+    if (dtype == B200_F32) e = launch_full_dt<b200::F32>(p, op, absolute != 0, vec, (unsigned)split, s);
+    else if (dtype == B200_F16) e = launch_full_dt<b200::F16>(p, op, absolute != 0, vec, (unsigned)split, s);
+    else e = launch_full_dt<b200::BF16>(p, op, absolute != 0, vec, (unsigned)split, s);
+    return (int)e;
+}

@@ -1,0 +1,601 @@
+// Kernel skeletons of the compound-optree engine for sm_100a.
+//
+// One op-tree assignment is lowered on the host into one or more *passes*; for
+// each pass the code generator emits a small struct `S<V>` (operand loads, the
+// fused element expression, the store or the reduction epilogue) and one of the
+// skeletons below supplies everything else: the thread mapping, 128-bit
+// vectorised coalesced access, warp-shuffle / shared-memory block reductions,
+// split reductions finished by the last block to arrive, and the conversions
+// and rounding on store.  The file is self-contained (no system headers) so the
+// same text compiles under NVRTC at run time and under nvcc at build time.
+//
+// Frame.  A pass sees every tensor as (K, N): K = extent of the axis that is
+// kept, N = extent of the axis the loop runs along (the reduced axis, or the
+// contiguous axis of an element-wise pass).  Strides are in elements.
+// "Lanes" are the V elements one thread handles per step: along N in
+// ew_kernel / red_rows_kernel, along K in red_cols_kernel.
+//
+// What replaces what in neon (neon/backends/cuda_templates.py):
+//   ew_kernel        -- _ew_template + "loop" stage with ew_out  (:45-86)
+//   red_rows_kernel  -- "loop" + "red32"/"red" + "red_out" stages (:88-135);
+//                       one block (or sub-warp) per kept index, optionally
+//                       several blocks per index
+//   red_cols_kernel  -- the same stages when the reduced axis is the strided
+//                       one (axis 0 of a row-major tensor): threads map to
+//                       neighbouring kept indices so every load is coalesced,
+//                       where the reference walks down columns
+//   conversions      -- _common_round / _common_fp16_to_fp32 (:189-372)
+//   rng_bits, frand  -- _common_urand_gen / _common_frand (:165-186), replaced
+//                       by a counter-based generator (no state pool, no race)
+//   red_* helpers    -- _reduction_ops (:577-613)
+#pragma once
+
+typedef long long i64;
+typedef unsigned long long u64;
+typedef unsigned int u32;
+typedef unsigned short u16;
+typedef unsigned char u8;
+
+#define DEV __device__ __forceinline__
+#define B200_FLT_MAX 3.402823466e+38f
+
+namespace b200 {
+
+enum { F32 = 0, F16 = 1, BF16 = 2, I32 = 3, U32 = 4, I16 = 5, U16 = 6, I8 = 7, U8 = 8 };
+enum { OP_SUM = 0, OP_MAX = 1, OP_MIN = 2, OP_ARGMAX = 3, OP_ARGMIN = 4 };
+
+template <int DT> struct dt_size { enum { value = (DT == F32 || DT == I32 || DT == U32) ? 4 : (DT == I8 || DT == U8) ? 1 : 2 }; };
+
+// ------------------------------------------------------------------ raw access
+// BYTES in {1,2,4,8,16,32}; data lands in 32-bit words (sub-word loads zero-extend).
+template <int BYTES, bool NC> DEV void ld_raw(const char* p, u32* w) {
+    if constexpr (BYTES == 32) {
+        uint4 a, b;
+        if constexpr (NC) { a = __ldg(reinterpret_cast<const uint4*>(p)); b = __ldg(reinterpret_cast<const uint4*>(p) + 1); }
+        else { a = *reinterpret_cast<const uint4*>(p); b = *(reinterpret_cast<const uint4*>(p) + 1); }
+        w[0] = a.x; w[1] = a.y; w[2] = a.z; w[3] = a.w; w[4] = b.x; w[5] = b.y; w[6] = b.z; w[7] = b.w;
+    } else if constexpr (BYTES == 16) {
+        uint4 a;
+        if constexpr (NC) a = __ldg(reinterpret_cast<const uint4*>(p)); else a = *reinterpret_cast<const uint4*>(p);
+        w[0] = a.x; w[1] = a.y; w[2] = a.z; w[3] = a.w;
+    } else if constexpr (BYTES == 8) {
+        uint2 a;
+        if constexpr (NC) a = __ldg(reinterpret_cast<const uint2*>(p)); else a = *reinterpret_cast<const uint2*>(p);
+        w[0] = a.x; w[1] = a.y;
+    } else if constexpr (BYTES == 4) {
+        if constexpr (NC) w[0] = __ldg(reinterpret_cast<const u32*>(p)); else w[0] = *reinterpret_cast<const u32*>(p);
+    } else if constexpr (BYTES == 2) {
+        if constexpr (NC) w[0] = __ldg(reinterpret_cast<const u16*>(p)); else w[0] = *reinterpret_cast<const u16*>(p);
+    } else {
+        if constexpr (NC) w[0] = __ldg(reinterpret_cast<const u8*>(p)); else w[0] = *reinterpret_cast<const u8*>(p);
+    }
+}
+
+template <int BYTES> DEV void st_raw(char* p, const u32* w) {
+    if constexpr (BYTES == 32) {
+        *reinterpret_cast<uint4*>(p) = make_uint4(w[0], w[1], w[2], w[3]);
+        *(reinterpret_cast<uint4*>(p) + 1) = make_uint4(w[4], w[5], w[6], w[7]);
+    } else if constexpr (BYTES == 16) {
+        *reinterpret_cast<uint4*>(p) = make_uint4(w[0], w[1], w[2], w[3]);
+    } else if constexpr (BYTES == 8) {
+        *reinterpret_cast<uint2*>(p) = make_uint2(w[0], w[1]);
+    } else if constexpr (BYTES == 4) {
+        *reinterpret_cast<u32*>(p) = w[0];
+    } else if constexpr (BYTES == 2) {
+        *reinterpret_cast<u16*>(p) = (u16)w[0];
+    } else {
+        *reinterpret_cast<u8*>(p) = (u8)w[0];
+    }
+}
+
+// ------------------------------------------------------------------ conversions
+DEV float h2f(u32 h) { float f; asm("cvt.f32.f16 %0, %1;" : "=f"(f) : "h"((u16)h)); return f; }
+DEV void h2f2(u32 hh, float& lo, float& hi) {
+    asm("{.reg .b16 a, b; mov.b32 {a, b}, %2; cvt.f32.f16 %0, a; cvt.f32.f16 %1, b;}" : "=f"(lo), "=f"(hi) : "r"(hh));
+}
+DEV u32 f2h_rn(float f) { u16 r; asm("cvt.rn.f16.f32 %0, %1;" : "=h"(r) : "f"(f)); return r; }
+DEV u32 f2h_rz(float f) { u16 r; asm("cvt.rz.f16.f32 %0, %1;" : "=h"(r) : "f"(f)); return r; }
+DEV u32 f2h2_rn(float lo, float hi) { u32 r; asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo)); return r; }
+DEV float bf2f(u32 b) { return __uint_as_float(b << 16); }
+DEV u32 f2bf_rn(float f) { u16 r; asm("cvt.rn.bf16.f32 %0, %1;" : "=h"(r) : "f"(f)); return r; }
+DEV u32 f2bf2_rn(float lo, float hi) { u32 r; asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo)); return r; }
+
+// words of V stored elements -> V floats
+template <int DT, int V> DEV void cvt_in(const u32* w, float* out) {
+    if constexpr (DT == F32) {
+#pragma unroll
+        for (int i = 0; i < V; ++i) out[i] = __uint_as_float(w[i]);
+    } else if constexpr (DT == I32) {
+#pragma unroll
+        for (int i = 0; i < V; ++i) out[i] = (float)(int)w[i];
+    } else if constexpr (DT == U32) {
+#pragma unroll
+        for (int i = 0; i < V; ++i) out[i] = (float)w[i];
+    } else if constexpr (DT == F16) {
+        if constexpr (V == 1) out[0] = h2f(w[0]);
+        else {
+#pragma unroll
+            for (int i = 0; i < V / 2; ++i) h2f2(w[i], out[2 * i], out[2 * i + 1]);
+        }
+    } else if constexpr (DT == BF16) {
+        if constexpr (V == 1) out[0] = bf2f(w[0]);
+        else {
+#pragma unroll
+            for (int i = 0; i < V / 2; ++i) { out[2 * i] = __uint_as_float(w[i] << 16); out[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u); }
+        }
+    } else if constexpr (DT == I16 || DT == U16) {
+#pragma unroll
+        for (int i = 0; i < V; ++i) {
+            u32 x = (V == 1) ? w[0] : ((w[i / 2] >> (16 * (i & 1))) & 0xffffu);
+            out[i] = (DT == I16) ? (float)(short)x : (float)x;
+        }
+    } else {
+#pragma unroll
+        for (int i = 0; i < V; ++i) {
+            u32 x = (V == 1) ? w[0] : ((w[i / 4] >> (8 * (i & 3))) & 0xffu);
+            out[i] = (DT == I8) ? (float)(signed char)x : (float)x;
+        }
+    }
+}
+
+// typed vector load of V consecutive elements starting `off` elements after base
+template <int DT, int V, bool NC> DEV void ld_f(u64 base, i64 off, float* out) {
+    constexpr int B = dt_size<DT>::value * V;
+    u32 w[(B + 3) / 4];
+    ld_raw<B, NC>(reinterpret_cast<const char*>(base) + off * dt_size<DT>::value, w);
+    cvt_in<DT, V>(w, out);
+}
+template <int DT, int V, bool NC> DEV void ld_w(u64 base, i64 off, u32* w) {
+    ld_raw<dt_size<DT>::value * V, NC>(reinterpret_cast<const char*>(base) + off * dt_size<DT>::value, w);
+}
+// int32 index load (take / one-hot addressing)
+DEV int ld_idx(u64 base, i64 off) { return __ldg(reinterpret_cast<const int*>(base) + off); }
+
+// ------------------------------------------------------------------ random bits
+struct Rng { u32 k0, k1; };
+
+// 32 bits for element `idx`: one multiplicative hash of the counter, keyed per launch
+DEV u32 rng_bits(const Rng& g, u64 idx) {
+    u32 x = (u32)idx * 0x9E3779B1u + g.k0;
+    x ^= x >> 16; x *= 0x21F0AAADu;
+    x ^= x >> 15; x *= 0x735A2D97u;
+    x ^= x >> 15;
+    x ^= g.k1 + (u32)(idx >> 32) * 0x632BE5ABu;
+    return x;
+}
+DEV float frand(const Rng& g, u64 idx) { return __uint2float_rn(rng_bits(g, idx)) * 2.3283064365386963e-10f; }
+
+// ------------------------------------------------------------------ rounding on store
+// Stochastic rounding to `mb` mantissa bits: add a uniform fraction of one
+// mb-bit ulp away from zero, truncate.  scale = 2^(-32-mb), mask = ~0 << (23-mb).
+struct SrCtx { float scale; u32 mask; };
+DEV SrCtx sr_ctx(int mb) { SrCtx c; c.scale = __uint_as_float((u32)(127 - 32 - mb) << 23); c.mask = 0xffffffffu << (23 - mb); return c; }
+DEV float sr_f32(float v, u32 urand, const SrCtx& c) {
+    float e = __uint_as_float(__float_as_uint(v) & 0xff800000u) * c.scale;
+    float r = __fmaf_rz(e, __uint2float_rz(urand), v);
+    return __uint_as_float(__float_as_uint(r) & c.mask);
+}
+DEV float sr_int_pre(float v, u32 urand) {     // value to truncate for integer stores
+    float fr = copysignf(__uint2float_rz(urand), v);
+    fr = __fmul_rz(fr, 2.3283064365386963e-10f);
+    return __fadd_rz(fr, v);
+}
+template <int DT> DEV u32 f2i_rn(float v) {
+    if constexpr (DT == I32) { int r; asm("cvt.rni.sat.s32.f32 %0, %1;" : "=r"(r) : "f"(v)); return (u32)r; }
+    else if constexpr (DT == U32) { u32 r; asm("cvt.rni.sat.u32.f32 %0, %1;" : "=r"(r) : "f"(v)); return r; }
+    else if constexpr (DT == I16) { short r; asm("cvt.rni.sat.s16.f32 %0, %1;" : "=h"(r) : "f"(v)); return (u32)(u16)r; }
+    else if constexpr (DT == U16) { u16 r; asm("cvt.rni.sat.u16.f32 %0, %1;" : "=h"(r) : "f"(v)); return r; }
+    else if constexpr (DT == I8) { int r; asm("cvt.rni.sat.s8.f32 %0, %1;" : "=r"(r) : "f"(v)); return (u32)r & 0xffu; }
+    else { u32 r; asm("cvt.rni.sat.u8.f32 %0, %1;" : "=r"(r) : "f"(v)); return r & 0xffu; }
+}
+template <int DT> DEV u32 f2i_rz(float v) {
+    if constexpr (DT == I32) { int r; asm("cvt.rzi.sat.s32.f32 %0, %1;" : "=r"(r) : "f"(v)); return (u32)r; }
+    else if constexpr (DT == I16) { short r; asm("cvt.rzi.sat.s16.f32 %0, %1;" : "=h"(r) : "f"(v)); return (u32)(u16)r; }
+    else { int r; asm("cvt.rzi.sat.s8.f32 %0, %1;" : "=r"(r) : "f"(v)); return (u32)r & 0xffu; }
+}
+
+// V floats -> words of V stored elements.  SR: 0 nearest, else stochastic with
+// ctx `c` and per-lane random words `ur`.
+template <int DT, int V, bool SR> DEV void cvt_out(const float* v, u32* w, const SrCtx& c, const u32* ur) {
+    if constexpr (DT == F32) {
+#pragma unroll
+        for (int i = 0; i < V; ++i) w[i] = __float_as_uint(SR ? sr_f32(v[i], ur[i], c) : v[i]);
+    } else if constexpr (DT == F16) {
+        if constexpr (SR) {
+            if constexpr (V == 1) w[0] = f2h_rz(sr_f32(v[0], ur[0], c));
+            else {
+#pragma unroll
+                for (int i = 0; i < V / 2; ++i)
+                    w[i] = f2h_rz(sr_f32(v[2 * i], ur[2 * i], c)) | (f2h_rz(sr_f32(v[2 * i + 1], ur[2 * i + 1], c)) << 16);
+            }
+        } else {
+            if constexpr (V == 1) w[0] = f2h_rn(v[0]);
+            else {
+#pragma unroll
+                for (int i = 0; i < V / 2; ++i) w[i] = f2h2_rn(v[2 * i], v[2 * i + 1]);
+            }
+        }
+    } else if constexpr (DT == BF16) {
+        if constexpr (V == 1) w[0] = f2bf_rn(v[0]);
+        else {
+#pragma unroll
+            for (int i = 0; i < V / 2; ++i) w[i] = f2bf2_rn(v[2 * i], v[2 * i + 1]);
+        }
+    } else {
+        constexpr bool SRI = SR && (DT == I32 || DT == I16 || DT == I8);   // unsigned: nearest only
+        constexpr int PER = 4 / dt_size<DT>::value;
+#pragma unroll
+        for (int i = 0; i < (V + PER - 1) / PER; ++i) w[i] = 0;
+#pragma unroll
+        for (int i = 0; i < V; ++i) {
+            u32 x;
+            if constexpr (SRI) x = f2i_rz<DT>(sr_int_pre(v[i], ur[i])); else x = f2i_rn<DT>(v[i]);
+            if constexpr (PER == 1) w[i] = x;
+            else w[i / PER] |= x << ((32 / PER) * (i % PER));
+        }
+    }
+}
+
+template <int DT, int V, bool SR> DEV void st_f(u64 base, i64 off, const float* v, const SrCtx& c, const u32* ur) {
+    constexpr int B = dt_size<DT>::value * V;
+    u32 w[(B + 3) / 4];
+    cvt_out<DT, V, SR>(v, w, c, ur);
+    st_raw<B>(reinterpret_cast<char*>(base) + off * dt_size<DT>::value, w);
+}
+template <int DT> DEV void st_one(u64 base, i64 off, float v) {
+    SrCtx c; c.scale = 0.f; c.mask = 0;
+    st_f<DT, 1, false>(base, off, &v, c, nullptr);
+}
+// arg-reduction index straight into an integer tensor (float_ew.py:451-454)
+template <int DT> DEV void st_index(u64 base, i64 off, int idx) {
+    if constexpr (DT == F32 || DT == F16 || DT == BF16) st_one<DT>(base, off, (float)idx);
+    else { u32 w = (u32)idx; st_raw<dt_size<DT>::value>(reinterpret_cast<char*>(base) + off * dt_size<DT>::value, &w); }
+}
+
+// ------------------------------------------------------------------ reduction algebra
+DEV float red_init(int op) { return op == OP_SUM ? 0.f : (op == OP_MAX || op == OP_ARGMAX) ? -B200_FLT_MAX : B200_FLT_MAX; }
+DEV bool red_is_arg(int op) { return op >= OP_ARGMAX; }
+// fold one element in; strict comparison keeps the first index a thread sees
+DEV void red_acc(int op, float& a, int& ai, float v, int vi) {
+    switch (op) {
+        case OP_SUM: a += v; break;
+        case OP_MAX: a = fmaxf(a, v); break;
+        case OP_MIN: a = fminf(a, v); break;
+        case OP_ARGMAX: if (v > a) { a = v; ai = vi; } break;
+        default: if (v < a) { a = v; ai = vi; } break;
+    }
+}
+// merge two partial results; equal extrema resolve to the smaller index
+DEV void red_merge(int op, float& a, int& ai, float b, int bi) {
+    switch (op) {
+        case OP_SUM: a += b; break;
+        case OP_MAX: a = fmaxf(a, b); break;
+        case OP_MIN: a = fminf(a, b); break;
+        case OP_ARGMAX: if (b > a || (b == a && (unsigned)bi < (unsigned)ai)) { a = b; ai = bi; } break;
+        default: if (b < a || (b == a && (unsigned)bi < (unsigned)ai)) { a = b; ai = bi; } break;
+    }
+}
+
+// ================================================================== element-wise
+// grid.x * BLOCK * UNROLL >= number of V-wide vectors (+ scalar tail in FLAT mode).
+template <template <int> class SV, class P, int V, int BLOCK, int UNROLL, bool FLAT>
+DEV void ew_kernel(const P& p) {
+    typedef SV<V> S;
+    const i64 nvec = p.nvec;                     // vectors per row (FLAT: all vectors)
+    const i64 total = FLAT ? nvec : p.K * nvec;
+    const i64 base = (i64)blockIdx.x * (BLOCK * UNROLL) + threadIdx.x;
+    typename S::L l[UNROLL];
+    typename S::H h[UNROLL];
+    i64 kk[UNROLL], nn[UNROLL];
+#pragma unroll
+    for (int u = 0; u < UNROLL; ++u) {
+        i64 g = base + (i64)u * BLOCK;
+        if (g < total) {
+            if constexpr (FLAT) { kk[u] = 0; nn[u] = g * V; }
+            else if (nvec <= 0x7fffffffLL && g <= 0x7fffffffLL) {
+                u32 q = (u32)g / (u32)nvec; kk[u] = q; nn[u] = (i64)((u32)g - q * (u32)nvec) * V;
+            } else { kk[u] = g / nvec; nn[u] = (g - kk[u] * nvec) * V; }
+            S::load_l(p, kk[u], nn[u], l[u]);
+            S::load_h(p, kk[u], h[u]);
+        }
+    }
+#pragma unroll
+    for (int u = 0; u < UNROLL; ++u) {
+        i64 g = base + (i64)u * BLOCK;
+        if (g < total) {
+            float out[1][V];
+            S::eval(p, h[u], l[u], kk[u], nn[u], out);
+            S::store(p, kk[u], nn[u], out[0]);
+        }
+    }
+    if constexpr (FLAT && V > 1) {               // scalar tail: N % V elements
+        typedef SV<1> S1;
+        const i64 t = nvec * V + (i64)blockIdx.x * BLOCK + threadIdx.x;
+        if (blockIdx.x == 0 && t < p.N) {
+            typename S1::L l1; typename S1::H h1;
+            S1::load_l(p, 0, t, l1); S1::load_h(p, 0, h1);
+            float out[1][1];
+            S1::eval(p, h1, l1, 0, t, out);
+            S1::store(p, 0, t, out[0]);
+        }
+    }
+}
+
+// ================================================================== split-reduction finish
+// Partials of reduction r, kept index k, split j live at r*K*SPLIT + j*pj + k*pk.
+template <class S, class P>
+DEV void write_partial(const P& p, i64 k, int j, i64 pj, i64 pk, const float* a, const int* ai) {
+    float* pv = reinterpret_cast<float*>(p.part_v);
+    int* pi = reinterpret_cast<int*>(p.part_i);
+#pragma unroll
+    for (int r = 0; r < S::NRED; ++r) {
+        i64 o = (i64)r * p.K * p.split + j * pj + k * pk;
+        pv[o] = a[r];
+        if (red_is_arg(S::op(r))) pi[o] = ai[r];
+    }
+}
+
+// ================================================================== reduce along lanes (rows)
+// TPR threads cooperate on one kept index; BLOCK/TPR indices per block.
+// TPR == BLOCK: one index per block and the row may be split over p.split blocks.
+template <template <int> class SV, class P, int V, int BLOCK, int TPR, int UNROLL>
+DEV void red_rows_kernel(const P& p) {
+    typedef SV<V> S;
+    constexpr int NR = S::NRED;
+    constexpr int RPC = BLOCK / TPR;
+    const int tid = threadIdx.x;
+    const int sub = tid % TPR;
+    i64 k; int j;
+    if constexpr (RPC == 1) { k = (i64)blockIdx.x / p.split; j = (int)((i64)blockIdx.x - k * p.split); }
+    else { k = (i64)blockIdx.x * RPC + tid / TPR; j = 0; }
+    const bool live = k < p.K;
+    const i64 nvec = p.nvec;
+    i64 v0 = 0, v1 = nvec;
+    if constexpr (RPC == 1) { v0 = (i64)j * p.seg; v1 = v0 + p.seg < nvec ? v0 + p.seg : nvec; }
+
+    float acc[NR][V]; int acci[NR][V];
+#pragma unroll
+    for (int r = 0; r < NR; ++r)
+#pragma unroll
+        for (int i = 0; i < V; ++i) { acc[r][i] = red_init(S::op(r)); acci[r][i] = -1; }
+
+    if (live) {
+        typename S::H h;
+        S::load_h(p, k, h);
+        for (i64 v = v0 + sub; v < v1; v += (i64)TPR * UNROLL) {
+            typename S::L l[UNROLL];
+#pragma unroll
+            for (int u = 0; u < UNROLL; ++u) if (v + (i64)u * TPR < v1) S::load_l(p, k, (v + (i64)u * TPR) * V, l[u]);
+#pragma unroll
+            for (int u = 0; u < UNROLL; ++u) {
+                if (v + (i64)u * TPR < v1) {
+                    const i64 n = (v + (i64)u * TPR) * V;
+                    float out[NR][V];
+                    S::eval(p, h, l[u], k, n, out);
+#pragma unroll
+                    for (int r = 0; r < NR; ++r)
+#pragma unroll
+                        for (int i = 0; i < V; ++i) red_acc(S::op(r), acc[r][i], acci[r][i], out[r][i], (int)(n + i));
+                }
+            }
+        }
+        // scalar tail of the row (N % V elements), first split only
+        if constexpr (V > 1) {
+            typedef SV<1> S1;
+            if (j == 0) {
+                typename S1::H h1;
+                S1::load_h(p, k, h1);
+                for (i64 n = nvec * V + sub; n < p.N; n += TPR) {
+                    typename S1::L l1;
+                    S1::load_l(p, k, n, l1);
+                    float out[NR][1];
+                    S1::eval(p, h1, l1, k, n, out);
+#pragma unroll
+                    for (int r = 0; r < NR; ++r) red_acc(S::op(r), acc[r][0], acci[r][0], out[r][0], (int)n);
+                }
+            }
+        }
+    }
+    // lanes -> one value per thread
+    float a[NR]; int ai[NR];
+#pragma unroll
+    for (int r = 0; r < NR; ++r) {
+        a[r] = acc[r][0]; ai[r] = acci[r][0];
+#pragma unroll
+        for (int i = 1; i < V; ++i) red_merge(S::op(r), a[r], ai[r], acc[r][i], acci[r][i]);
+    }
+    // threads of one index -> one value
+    constexpr int W = TPR < 32 ? TPR : 32;
+#pragma unroll
+    for (int r = 0; r < NR; ++r)
+#pragma unroll
+        for (int o = W / 2; o > 0; o >>= 1) {
+            float b = __shfl_xor_sync(0xffffffffu, a[r], o);
+            int bi = __shfl_xor_sync(0xffffffffu, ai[r], o);
+            red_merge(S::op(r), a[r], ai[r], b, bi);
+        }
+    if constexpr (TPR > 32) {
+        __shared__ float sv[NR][BLOCK / 32];
+        __shared__ int si[NR][BLOCK / 32];
+        const int warp = tid >> 5, lane = tid & 31;
+        if (lane == 0) {
+#pragma unroll
+            for (int r = 0; r < NR; ++r) { sv[r][warp] = a[r]; si[r][warp] = ai[r]; }
+        }
+        __syncthreads();
+        if (warp == 0) {
+#pragma unroll
+            for (int r = 0; r < NR; ++r) {
+                a[r] = lane < BLOCK / 32 ? sv[r][lane] : red_init(S::op(r));
+                ai[r] = lane < BLOCK / 32 ? si[r][lane] : -1;
+#pragma unroll
+                for (int o = (BLOCK / 32) / 2; o > 0; o >>= 1) {
+                    float b = __shfl_xor_sync(0xffffffffu, a[r], o);
+                    int bi = __shfl_xor_sync(0xffffffffu, ai[r], o);
+                    red_merge(S::op(r), a[r], ai[r], b, bi);
+                }
+            }
+        }
+    }
+    if constexpr (RPC > 1) {
+        if (live && sub == 0) S::epilogue(p, k, a, ai);
+        return;
+    } else {
+        if (p.split == 1) {
+            if (tid == 0) S::epilogue(p, k, a, ai);
+            return;
+        }
+        // several blocks per index: publish, count arrivals, last one combines in split order
+        __shared__ int s_last;
+        if (tid == 0) {
+            write_partial<S>(p, k, j, 1, p.split, a, ai);
+            __threadfence();
+            int* cnt = reinterpret_cast<int*>(p.counters) + k;
+            int seen = atomicAdd(cnt, 1);
+            s_last = (seen == p.split - 1);
+            if (s_last) *cnt = 0;                      // leave the counter clean for the next launch
+        }
+        __syncthreads();
+        if (!s_last) return;
+        __threadfence();
+        if (tid < 32) {
+            const float* pv = reinterpret_cast<const float*>(p.part_v);
+            const int* pi = reinterpret_cast<const int*>(p.part_i);
+#pragma unroll
+            for (int r = 0; r < NR; ++r) {
+                a[r] = red_init(S::op(r)); ai[r] = -1;
+                const i64 o = ((i64)r * p.K + k) * p.split;
+                for (int s = tid; s < p.split; s += 32) {
+                    float b = __ldcg(pv + o + s);
+                    int bi = red_is_arg(S::op(r)) ? __ldcg(pi + o + s) : -1;
+                    red_merge(S::op(r), a[r], ai[r], b, bi);
+                }
+#pragma unroll
+                for (int o2 = 16; o2 > 0; o2 >>= 1) {
+                    float b = __shfl_xor_sync(0xffffffffu, a[r], o2);
+                    int bi = __shfl_xor_sync(0xffffffffu, ai[r], o2);
+                    red_merge(S::op(r), a[r], ai[r], b, bi);
+                }
+            }
+            if (tid == 0) S::epilogue(p, k, a, ai);
+        }
+    }
+}
+
+// ================================================================== reduce across lanes (cols)
+// Block = CW x RH threads (CW*RH == BLOCK).  threadIdx % CW picks V neighbouring
+// kept indices, threadIdx / CW a residue class of the reduced axis.
+// grid = (tiles of CW*V kept indices, p.split slices of the reduced axis).
+template <template <int> class SV, class P, int V, int BLOCK, int CW, int UNROLL>
+DEV void red_cols_kernel(const P& p) {
+    typedef SV<V> S;
+    constexpr int NR = S::NRED;
+    constexpr int RH = BLOCK / CW;
+    const int tx = threadIdx.x % CW, ty = threadIdx.x / CW;
+    const i64 k0 = ((i64)blockIdx.x * CW + tx) * V;
+    const int j = blockIdx.y;
+    const bool live = k0 < p.K;
+    const i64 n0 = (i64)j * p.seg;
+    const i64 n1 = n0 + p.seg < p.N ? n0 + p.seg : p.N;
+
+    float acc[NR][V]; int acci[NR][V];
+#pragma unroll
+    for (int r = 0; r < NR; ++r)
+#pragma unroll
+        for (int i = 0; i < V; ++i) { acc[r][i] = red_init(S::op(r)); acci[r][i] = -1; }
+
+    if (live) {
+        typename S::H h;
+        S::load_h(p, k0, h);
+        for (i64 n = n0 + ty; n < n1; n += (i64)RH * UNROLL) {
+            typename S::L l[UNROLL];
+#pragma unroll
+            for (int u = 0; u < UNROLL; ++u) if (n + (i64)u * RH < n1) S::load_l(p, k0, n + (i64)u * RH, l[u]);
+#pragma unroll
+            for (int u = 0; u < UNROLL; ++u) {
+                if (n + (i64)u * RH < n1) {
+                    float out[NR][V];
+                    S::eval(p, h, l[u], k0, n + (i64)u * RH, out);
+#pragma unroll
+                    for (int r = 0; r < NR; ++r)
+#pragma unroll
+                        for (int i = 0; i < V; ++i) red_acc(S::op(r), acc[r][i], acci[r][i], out[r][i], (int)(n + (i64)u * RH));
+                }
+            }
+        }
+    }
+    // combine the RH residue classes through shared memory, in class order
+    __shared__ float sv[NR][RH][CW * V + 1];
+    __shared__ int si[NR][RH][CW * V + 1];
+    __shared__ int s_last;
+#pragma unroll
+    for (int r = 0; r < NR; ++r)
+#pragma unroll
+        for (int i = 0; i < V; ++i) {
+            sv[r][ty][tx * V + i] = acc[r][i];
+            if (red_is_arg(S::op(r))) si[r][ty][tx * V + i] = acci[r][i];
+        }
+    __syncthreads();
+    // thread t finishes kept index (tile base + t) for t < CW*V
+    const int t = threadIdx.x;
+    const i64 kt = (i64)blockIdx.x * CW * V + t;
+    const bool owner = t < CW * V && kt < p.K;
+    float a[NR]; int ai[NR];
+    if (owner) {
+#pragma unroll
+        for (int r = 0; r < NR; ++r) {
+            a[r] = sv[r][0][t]; ai[r] = red_is_arg(S::op(r)) ? si[r][0][t] : -1;
+            for (int y = 1; y < RH; ++y) red_merge(S::op(r), a[r], ai[r], sv[r][y][t], red_is_arg(S::op(r)) ? si[r][y][t] : -1);
+        }
+    }
+    if (p.split == 1) {
+        if (owner) S::epilogue(p, kt, a, ai);
+        return;
+    }
+    if (owner) write_partial<S>(p, kt, j, p.K, 1, a, ai);
+    __threadfence();
+    __syncthreads();
+    if (t == 0) {
+        int* cnt = reinterpret_cast<int*>(p.counters) + blockIdx.x;
+        int seen = atomicAdd(cnt, 1);
+        s_last = (seen == p.split - 1);
+        if (s_last) *cnt = 0;
+    }
+    __syncthreads();
+    if (!s_last) return;
+    __threadfence();
+    // last block of this tile: every thread folds a residue class of the splits, then as above
+    {
+        const float* pv = reinterpret_cast<const float*>(p.part_v);
+        const int* pi = reinterpret_cast<const int*>(p.part_i);
+        const int cx = threadIdx.x % (CW * V), cy = threadIdx.x / (CW * V);
+        constexpr int CH = BLOCK / (CW * V) > 0 ? BLOCK / (CW * V) : 1;
+        const i64 kc = (i64)blockIdx.x * CW * V + cx;
+        __syncthreads();
+        if (cy < CH && threadIdx.x < CH * CW * V) {
+#pragma unroll
+            for (int r = 0; r < NR; ++r) {
+                float b = red_init(S::op(r)); int bi = -1;
+                if (kc < p.K)
+                    for (int s = cy; s < p.split; s += CH) {
+                        const i64 o = (i64)r * p.K * p.split + (i64)s * p.K + kc;
+                        red_merge(S::op(r), b, bi, __ldcg(pv + o), red_is_arg(S::op(r)) ? __ldcg(pi + o) : -1);
+                    }
+                sv[r][cy % RH][cx] = b;
+                if (red_is_arg(S::op(r))) si[r][cy % RH][cx] = bi;
+            }
+        }
+        __syncthreads();
+        if (owner) {
+            constexpr int CHR = CH < RH ? CH : RH;
+#pragma unroll
+            for (int r = 0; r < NR; ++r) {
+                a[r] = sv[r][0][t]; ai[r] = red_is_arg(S::op(r)) ? si[r][0][t] : -1;
+                for (int y = 1; y < CHR; ++y) red_merge(S::op(r), a[r], ai[r], sv[r][y][t], red_is_arg(S::op(r)) ? si[r][y][t] : -1);
+            }
+            S::epilogue(p, kt, a, ai);
+        }
+    }
+}
+
+}  // namespace b200

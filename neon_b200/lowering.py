@@ -1,0 +1,861 @@
+"""
+Host lowering of one op-tree assignment into kernel passes.
+
+Takes the postfix program an ``OpTreeNode`` flattens to
+(``[out, operands..., op dicts..., {'op': 'assign'}]``) and produces a list of
+``Pass`` objects: which skeleton of ``csrc/optree_templates.cuh`` runs, the
+generated ``S<V>`` struct that plugs into it, the launch geometry and the
+parameter block.  This is the job ``call_compound_kernel`` and
+``_get_compound_kernel`` do in neon (neon/backends/float_ew.py:644-940 and
+:268-617, with the stage split of :59-257); the semantics kept from there:
+
+* one reduction axis per statement, 0 or 1 (:682-693); stride-0 broadcast of
+  (n,1)/(1,n)/(1,1) operands (:751-763); operand de-duplication by tensor
+  identity and constants by value (:735-749, :788-800); shape algebra and the
+  ``TypeError``/``ValueError`` it raises (:810-825, :682-690, :724-726, :899-906);
+* identical reduction sub-trees are evaluated once (:147-190);
+* python numbers reach the kernel as fp32 run-time arguments, so changing a
+  learning rate does not compile a new kernel (:788-800);
+* rounding on store follows the output tensor's ``rounding`` attribute (:827-844).
+
+What is different by design: a reduction level is a grid-wide pass (its result
+is stored in fp32 scratch and re-read by later passes) instead of a loop inside
+a single block per row, so every pass can use all SMs and coalesced loads
+whichever axis is reduced; sub-trees made of constants only are folded on the
+host in fp32.
+"""
+
+import struct
+
+import numpy as np
+
+from .optree import OpCollection, Tensor
+
+DT_CODES = {"f4": 0, "f2": 1, "bf2": 2, "i4": 3, "u4": 4, "i2": 5, "u2": 6, "i1": 7, "u1": 8}
+DT_NAMES = ["F32", "F16", "BF16", "I32", "U32", "I16", "U16", "I8", "U8"]
+DT_SIZE = [4, 2, 2, 4, 4, 2, 2, 1, 1]
+RED_CODE = {"sum": "OP_SUM", "max": "OP_MAX", "min": "OP_MIN", "argmax": "OP_ARGMAX", "argmin": "OP_ARGMIN"}
+
+BLOCK = 256
+
+# fp32 expressions of the element-wise vocabulary (neon/backends/cuda_templates.py:542-574)
+UNARY_C = {
+    "neg": "-{0}",
+    "abs": "fabsf({0})",
+    "sgn": "(({0} == 0.0f) ? 0.0f : copysignf(1.0f, {0}))",
+    "sqrt": "sqrtf({0})",
+    "sqr": "({0} * {0})",
+    "exp": "expf({0})",
+    "log": "logf({0})",
+    "safelog": "(({0} > 0.0f) ? logf({0}) : -50.0f)",
+    "exp2": "exp2f({0})",
+    "log2": "log2f({0})",
+    "sig": "(1.0f / (1.0f + expf(-{0})))",
+    "sig2": "(1.0f / (1.0f + exp2f(-{0})))",
+    "tanh": "tanhf({0})",
+    "tanh2": "((exp2f(2.0f * {0}) - 1.0f) / (exp2f(2.0f * {0}) + 1.0f))",
+    "finite": "(isfinite({0}) ? 1.0f : 0.0f)",
+}
+BINARY_C = {
+    "add": "({0} + {1})", "sub": "({0} - {1})", "mul": "({0} * {1})", "div": "({0} / {1})",
+    "eq": "(({0} == {1}) ? 1.0f : 0.0f)", "ne": "(({0} != {1}) ? 1.0f : 0.0f)",
+    "lt": "(({0} < {1}) ? 1.0f : 0.0f)", "le": "(({0} <= {1}) ? 1.0f : 0.0f)",
+    "gt": "(({0} > {1}) ? 1.0f : 0.0f)", "ge": "(({0} >= {1}) ? 1.0f : 0.0f)",
+    "minimum": "fminf({0}, {1})", "maximum": "fmaxf({0}, {1})", "pow": "powf({0}, {1})",
+}
+# the same ops on host fp32 scalars, for folding constant-only sub-trees
+_f = np.float32
+UNARY_HOST = {
+    "neg": lambda a: -a, "abs": np.abs, "sgn": np.sign, "sqrt": np.sqrt, "sqr": lambda a: a * a,
+    "exp": np.exp, "log": np.log, "safelog": lambda a: np.log(a) if a > 0 else _f(-50.0),
+    "exp2": np.exp2, "log2": np.log2, "sig": lambda a: _f(1) / (_f(1) + np.exp(-a)),
+    "sig2": lambda a: _f(1) / (_f(1) + np.exp2(-a)), "tanh": np.tanh,
+    "tanh2": lambda a: (np.exp2(_f(2) * a) - _f(1)) / (np.exp2(_f(2) * a) + _f(1)),
+    "finite": lambda a: _f(np.isfinite(a)),
+}
+BINARY_HOST = {
+    "add": lambda a, b: a + b, "sub": lambda a, b: a - b, "mul": lambda a, b: a * b,
+    "div": lambda a, b: a / b, "eq": lambda a, b: _f(a == b), "ne": lambda a, b: _f(a != b),
+    "lt": lambda a, b: _f(a < b), "le": lambda a, b: _f(a <= b), "gt": lambda a, b: _f(a > b),
+    "ge": lambda a, b: _f(a >= b), "minimum": min, "maximum": max, "pow": np.power,
+}
+
+
+def dtype_code(dtype):
+    dtype = np.dtype(dtype)
+    key = dtype.str[1:]
+    if key not in DT_CODES:
+        raise TypeError("unsupported tensor dtype %s" % dtype)
+    return DT_CODES[key]
+
+
+# --------------------------------------------------------------------------- DAG
+class Node(object):
+    __slots__ = ("kind", "op", "args", "shape", "tix", "value", "axis", "level", "nid", "extra")
+
+    def __init__(self, kind, op=None, args=(), shape=(1, 1), tix=None, value=None, axis=None, extra=None):
+        self.kind = kind        # 't' tensor, 'c' const, 'u' unary, 'b' binary, 'r' reduction, 'z' zero-operand
+        self.op = op
+        self.args = args
+        self.shape = shape
+        self.tix = tix
+        self.value = value
+        self.axis = axis
+        self.level = 0
+        self.nid = -1
+        self.extra = extra
+
+
+class Operand(object):
+    """A distinct tensor of the statement: pointer, dtype, 2-d shape, element strides."""
+    __slots__ = ("tensor", "ptr", "dt", "shape", "strides", "alias_out", "span", "_frame_strides")
+
+    def __init__(self, tensor, shape, strides):
+        self.tensor = tensor
+        self.ptr = int(tensor.ptr)
+        self.dt = dtype_code(tensor.dtype)
+        self.shape = tuple(shape)
+        self.strides = tuple(int(s) for s in strides)
+        lo = hi = 0
+        for d, s in zip(self.shape, self.strides):
+            if d > 1:
+                if s >= 0:
+                    hi += (d - 1) * s
+                else:
+                    lo += (d - 1) * s
+        isz = DT_SIZE[self.dt]
+        self.span = (self.ptr + lo * isz, self.ptr + (hi + 1) * isz)
+        self.alias_out = False
+
+
+class _Pseudo(object):
+    """Operand-like view of a reduction result held in scratch."""
+    __slots__ = ("ptr", "dt", "shape", "strides", "alias_out", "_frame_strides")
+
+    def __init__(self, ptr, dt, shape):
+        self.ptr, self.dt, self.shape = ptr, dt, tuple(shape)
+        self.strides = (1, 1)           # a vector: the extent-1 axis is zeroed by the frame
+        self.alias_out = True           # written by an earlier launch: plain loads
+
+
+def _fast_flat_ok(t, out_shape):
+    return len(t.shape) >= 1 and tuple(t.shape) == tuple(out_shape) and t.is_contiguous and not t.take_array
+
+
+class Statement(object):
+    """The DAG of one assignment plus everything ``plan`` needs to lower it."""
+
+    def __init__(self, stack):
+        self.nodes = []
+        self._memo = {}
+        self.operands = []          # Operand list (inputs)
+        self._tensor_ix = {}
+        out = stack[0]
+        if not isinstance(out, Tensor):
+            raise TypeError("first element of the program must be the output tensor")
+        if out.take_array:
+            raise NotImplementedError("assignment into a fancy-indexed view")
+        self.out_tensor = out
+
+        # ---- pass 1 (float_ew.py:672-707): reduction axis and simple-elementwise test
+        axis = None
+        has_red = False
+        flat_ok = True
+        for s in stack:
+            if type(s) is dict:
+                op = s["op"]
+                if op in OpCollection.reduction_ops:
+                    if s.get("axis", None) not in (0, 1):
+                        raise ValueError("Only reduction along an axis currently supported")
+                    if has_red and s["axis"] != axis:
+                        raise ValueError("Reduction only allowed along one axis per kernel.")
+                    has_red, axis = True, s["axis"]
+                elif op in ("onehot", "rand"):
+                    flat_ok = False
+            elif isinstance(s, Tensor):
+                if s.take_array:
+                    raise NotImplementedError("fancy-indexed operands")
+                if not _fast_flat_ok(s, out.shape):
+                    if not (tuple(s.shape) == (1, 1) and s is not out):
+                        flat_ok = False
+        self.axis = 1 if axis is None else axis
+        self.has_red = has_red
+        self.flat = flat_ok and not has_red
+        if not self.flat:
+            for s in stack:
+                if isinstance(s, Tensor) and len(s.shape) != 2:
+                    raise ValueError("Operations that are not simple elementwise are only "
+                                     "currently supported in 2 dimensions.")
+        if self.flat:
+            self.out_shape = (1, int(out.size))
+        else:
+            self.out_shape = tuple(out.shape)
+
+        # ---- pass 2: postfix -> DAG with shape algebra (float_ew.py:713-906)
+        st = []
+        first = True
+        for s in stack:
+            if isinstance(s, Tensor):
+                if first:
+                    first = False
+                    st.append("OUT")
+                    continue
+                st.append(self._tensor_node(s))
+            elif type(s) in (int, float) or isinstance(s, (np.floating, np.integer)):
+                st.append(self._const(float(s)))
+            elif type(s) is dict:
+                op = s["op"]
+                if op == "assign":
+                    rhs = st.pop()
+                    dst = st.pop()
+                    if dst != "OUT" or st:
+                        raise TypeError("malformed program: assign must close it")
+                    self._check_assign(rhs)
+                    self.root = rhs
+                elif op in OpCollection.reduction_ops:
+                    st.append(self._reduce(op, st.pop()))
+                elif op in ("rand", "onehot"):
+                    st.append(self._zero_op(s))
+                elif op in UNARY_C:
+                    st.append(self._unary(op, st.pop()))
+                elif op in BINARY_C:
+                    b = st.pop()
+                    a = st.pop()
+                    st.append(self._binary(op, a, b))
+                else:
+                    raise TypeError("%s is not a valid operation" % op)
+            else:
+                raise TypeError("args must be instance of Tensor, int, float, or dict (for operators)")
+        self.out = Operand(out, self.out_shape,
+                           (0, 1) if self.flat else out.strides)
+        for o in self.operands:
+            o.alias_out = not (o.span[1] <= self.out.span[0] or self.out.span[1] <= o.span[0])
+
+    # -- node constructors (hash-consed)
+    def _intern(self, key, make):
+        n = self._memo.get(key)
+        if n is None:
+            n = make()
+            n.nid = len(self.nodes)
+            self.nodes.append(n)
+            self._memo[key] = n
+        return n
+
+    def _tensor_node(self, t):
+        ix = self._tensor_ix.get(id(t))
+        if ix is None:
+            if self.flat:
+                shape = (1, 1) if tuple(t.shape) == (1, 1) and t.size == 1 and self.out_shape != (1, 1) \
+                    else (1, int(t.size))
+                strides = (0, 1)
+            else:
+                shape, strides = tuple(t.shape), tuple(t.strides)
+            ix = self._tensor_ix[id(t)] = len(self.operands)
+            self.operands.append(Operand(t, shape, strides))
+        shape = self.operands[ix].shape
+        return self._intern(("t", ix), lambda: Node("t", tix=ix, shape=shape))
+
+    def _const(self, v):
+        v = float(np.float32(v))
+        return self._intern(("c", v), lambda: Node("c", value=v))
+
+    @staticmethod
+    def _bshape(shapes):
+        out = [1, 1]
+        for s in shapes:
+            for i in range(2):
+                if s[i] != out[i]:
+                    if s[i] == 1 or out[i] == 1:
+                        out[i] = max(out[i], s[i])
+                    else:
+                        raise TypeError("Input shape:%s not compatible" % (tuple(s),))
+        return tuple(out)
+
+    def _unary(self, op, a):
+        if a.kind == "c":
+            with np.errstate(all="ignore"):
+                return self._const(UNARY_HOST[op](np.float32(a.value)))
+        return self._intern(("u", op, a.nid),
+                            lambda: self._lvl(Node("u", op=op, args=(a,), shape=a.shape)))
+
+    def _binary(self, op, a, b):
+        if a.kind == "c" and b.kind == "c":
+            with np.errstate(all="ignore"):
+                return self._const(BINARY_HOST[op](np.float32(a.value), np.float32(b.value)))
+        shape = self._bshape((b.shape, a.shape))
+        return self._intern(("b", op, a.nid, b.nid),
+                            lambda: self._lvl(Node("b", op=op, args=(a, b), shape=shape)))
+
+    def _reduce(self, op, a):
+        ax = self.axis
+        if a.shape[ax] == 1:
+            # reducing an extent of one: the value itself, or index 0
+            return self._const(0.0) if op.startswith("arg") else a
+        shape = list(a.shape)
+        shape[ax] = 1
+        shape = tuple(shape)
+
+        def make():
+            n = Node("r", op=op, args=(a,), shape=shape, axis=ax)
+            n.level = a.level + 1
+            return n
+        return self._intern(("r", op, a.nid), make)
+
+    def _zero_op(self, info):
+        if info["op"] == "rand":
+            # every rand() in a tree is its own stream
+            k = ("z", "rand", len(self.nodes))
+            return self._intern(k, lambda: Node("z", op="rand", shape=self.out_shape, extra=len(self.nodes)))
+        idx = info["idx"]
+        ix_node = self._tensor_node(idx)
+        hot = info["axis"]
+        n_hot = self.out_shape[hot]
+        count = max(idx.shape)
+        shape = [0, 0]
+        shape[hot] = n_hot
+        shape[1 - hot] = count
+        return self._intern(("z", "onehot", ix_node.tix, hot),
+                            lambda: Node("z", op="onehot", shape=tuple(shape), tix=ix_node.tix, axis=hot))
+
+    @staticmethod
+    def _lvl(n):
+        n.level = max(a.level for a in n.args)
+        return n
+
+    def _check_assign(self, rhs):
+        self._bshape((rhs.shape, self.out_shape))
+        for i in range(2):
+            if rhs.shape[i] != 1 and rhs.shape[i] != self.out_shape[i]:
+                raise TypeError("Input shape:%s not compatible" % (tuple(rhs.shape),))
+
+
+# --------------------------------------------------------------------------- code generation
+class _Fields(object):
+    """Parameter-block layout: 8-byte members first, then 4-byte ones."""
+
+    def __init__(self):
+        self.f8 = []
+        self.f4 = []
+        self.values = {}
+
+    def u64(self, name, v):
+        self._add(self.f8, ("u64", "Q", name), v)
+
+    def i64(self, name, v):
+        self._add(self.f8, ("i64", "q", name), v)
+
+    def i32(self, name, v):
+        self._add(self.f4, ("int", "i", name), v)
+
+    def u32(self, name, v):
+        self._add(self.f4, ("u32", "I", name), v)
+
+    def f32(self, name, v):
+        self._add(self.f4, ("float", "f", name), v)
+
+    def _add(self, lst, decl, v):
+        if decl[2] not in self.values:
+            lst.append(decl)
+        self.values[decl[2]] = v
+
+    def decl(self):
+        lines = ["    %s %s;" % (c, n) for c, _, n in self.f8 + self.f4]
+        if len(self.f4) % 2:
+            lines.append("    int pad_;")
+        return "struct P {\n%s\n};" % "\n".join(lines)
+
+    def names(self):
+        return [n for _, _, n in self.f8 + self.f4]
+
+    def fmt(self):
+        f = "<" + "".join(c for _, c, _ in self.f8 + self.f4)
+        if len(self.f4) % 2:
+            f += "i"
+        return f
+
+    def pack(self, values=None):
+        values = self.values if values is None else values
+        vals = [values[n] for n in self.names()]
+        if len(self.f4) % 2:
+            vals.append(0)
+        return struct.pack(self.fmt(), *vals)
+
+
+class Pass(object):
+    """One kernel launch of a statement."""
+    __slots__ = ("source", "name", "grid", "block", "fields", "kernel", "uses_rng", "desc",
+                 "bytes_moved", "result_slots", "kind")
+
+    def __init__(self):
+        self.kernel = None
+        self.uses_rng = False
+
+
+def _pow2ceil(x):
+    p = 1
+    while p < x:
+        p *= 2
+    return p
+
+
+class Planner(object):
+    """
+    Lowers a Statement to passes.  ``scratch(nbytes, zero)`` must return a device
+    address valid until the statement's launches have been issued; ``sm_count``
+    sizes the grids.
+    """
+
+    def __init__(self, sm_count=148, target_blocks_per_sm=8):
+        self.sm_count = sm_count
+        self.target = sm_count * target_blocks_per_sm
+
+    # ---- helpers on the frame: K = kept axis, N = loop axis
+    def plan(self, st, scratch, rounding=0, rng_key=None, lin=None):
+        """Return the list of Pass objects for Statement ``st``."""
+        ra = st.axis                # reduced / loop axis in tensor coordinates
+        ka = 1 - ra
+        reds = [n for n in st.nodes if n.kind == "r" and self._reachable(st, n)]
+        levels = sorted(set(n.level for n in reds))
+        passes = []
+        res_buf = {}                # reduction nid -> (addr_val, addr_idx or 0)
+        full_shape = self._full_shape(st)
+        root_is_k = st.root.shape[ra] == 1
+        out_is_k = st.out_shape[ra] == 1
+        for li, lv in enumerate(levels):
+            rs = [n for n in reds if n.level == lv]
+            final = (lv == levels[-1]) and root_is_k and out_is_k and st.root.level == lv
+            K = full_shape[ka]
+            if not final:
+                for r in rs:
+                    res_buf[r.nid] = (scratch(4 * K, False),
+                                      scratch(4 * K, False) if r.op.startswith("arg") else 0)
+            passes.append(self._reduction_pass(st, rs, res_buf, ka, ra, full_shape, scratch, final))
+            if final:
+                return passes
+        passes.append(self._ew_pass(st, res_buf, ka, ra, rounding))
+        return passes
+
+    @staticmethod
+    def _reachable(st, node):
+        seen = set()
+        stack = [st.root]
+        while stack:
+            n = stack.pop()
+            if n.nid in seen:
+                continue
+            seen.add(n.nid)
+            if n is node:
+                return True
+            stack.extend(n.args)
+        return False
+
+    @staticmethod
+    def _full_shape(st):
+        shp = list(st.out_shape)
+        for n in st.nodes:
+            for i in range(2):
+                shp[i] = max(shp[i], n.shape[i])
+        return tuple(shp)
+
+    # ---- expression emission ------------------------------------------------
+    class _Emit(object):
+        """Collects code for one pass in a given orientation."""
+
+        def __init__(self, st, fields, ka, ra, lanes_on_k, res_buf, avail_level):
+            self.st = st
+            self.f = fields
+            self.ka, self.ra = ka, ra
+            self.lk = lanes_on_k
+            self.res_buf = res_buf
+            self.avail = avail_level          # reductions of level <= avail come from scratch
+            self.h_lines, self.h_decl = [], []
+            self.l_lines, self.l_decl = [], []
+            self.e_pre, self.e_lines = [], []
+            self.names = {}                    # nid -> (expr string in eval scope, is hoisted)
+            self.hoisted = {}                  # nid -> name in H
+            self.loop_ops = {}                 # tix -> array name in eval
+            self.uses_rng = False
+            self.lane_ops = []                 # (operand, lane axis) of every vector access
+            self.pseudo = {}
+
+        def var_k(self, n):
+            return n.shape[self.ka] > 1
+
+        def var_n(self, n):
+            return n.shape[self.ra] > 1
+
+        def _leaf(self, n):
+            """Operand record and parameter-field prefix of a tensor node, or of a
+            reduction result an earlier pass left in scratch (a length-K fp32/int32
+            vector, seen as a tensor of the node's shape)."""
+            if n.kind == "t":
+                o, pre = self.st.operands[n.tix], "t%d" % n.tix
+            else:
+                assert n.level <= self.avail, "reduction not yet available"
+                pre = "r%d" % n.nid
+                o = self.pseudo.get(n.nid)
+                if o is None:
+                    av, ai = self.res_buf[n.nid]
+                    o = _Pseudo(ai if n.op.startswith("arg") else av,
+                                DT_CODES["i4"] if n.op.startswith("arg") else DT_CODES["f4"], n.shape)
+                    self.pseudo[n.nid] = o
+            sk, sn = o.strides[self.ka], o.strides[self.ra]
+            if o.shape[self.ka] == 1:
+                sk = 0
+            if o.shape[self.ra] == 1:
+                sn = 0
+            o._frame_strides = (sk, sn)
+            self.f.u64(pre, o.ptr)
+            self.f.i64(pre + "_sk", sk)
+            self.f.i64(pre + "_sn", sn)
+            return o, pre
+
+        # value of node for use in hoisted (per-k) code; scope 'h'
+        def hoist(self, n):
+            """Emit per-kept-index code for K-only node n; returns its name in load_h scope."""
+            key = ("h", n.nid)
+            if key in self.names:
+                return self.names[key]
+            W = "V" if self.lk else "1"
+            idx = "[i]" if self.lk else "[0]"
+            if n.kind == "c":
+                self.f.f32("c%d" % n.nid, n.value)
+                name = "p.c%d" % n.nid
+                self.names[key] = name
+                return name
+            name = "k%d" % n.nid
+            if n.kind in ("t", "r"):
+                o, pre = self._leaf(n)
+                nc = "false" if o.alias_out else "true"
+                if self.lk and self.var_k(n):
+                    self.lane_ops.append((o, "k"))
+                    self.h_lines.append("float %s[V]; ld_f<%s, V, %s>(p.%s, k * p.%s_sk, %s);"
+                                        % (name, DT_NAMES[o.dt], nc, pre, pre, name))
+                    ref = name + "[i]"
+                else:
+                    self.h_lines.append("float %s[1]; ld_f<%s, 1, %s>(p.%s, k * p.%s_sk, %s);"
+                                        % (name, DT_NAMES[o.dt], nc, pre, pre, name))
+                    ref = name + "[0]"
+                self.names[key] = ref
+                return ref
+            # computed K-only node
+            args = [self.hoist(a) for a in n.args]
+            expr = (UNARY_C[n.op] if n.kind == "u" else BINARY_C[n.op]).format(*args)
+            if self.lk:
+                self.h_lines.append("float %s[V];\n        _Pragma(\"unroll\") for (int i = 0; i < V; ++i) %s[i] = %s;"
+                                    % (name, name, expr))
+                ref = name + "[i]"
+            else:
+                self.h_lines.append("float %s[1]; { const int i = 0; (void)i; %s[0] = %s; }" % (name, name, expr))
+                ref = name + "[0]"
+            self.names[key] = ref
+            return ref
+
+        def elem(self, n):
+            """Emit per-element code for node n; returns the expression naming its value in eval scope."""
+            key = ("e", n.nid)
+            if key in self.names:
+                return self.names[key]
+            if n.kind == "c":
+                self.f.f32("c%d" % n.nid, n.value)
+                self.names[key] = "p.c%d" % n.nid
+                return self.names[key]
+            if n.kind == "z":
+                return self._zero(n, key)
+            if not self.var_n(n):
+                # K-only: computed in load_h, carried in H
+                ref = self.hoist(n)
+                if ref.startswith("p.c"):
+                    self.names[key] = ref
+                    return ref
+                hname = "h%d" % n.nid
+                if n.nid not in self.hoisted:
+                    self.hoisted[n.nid] = hname
+                    if self.lk:
+                        self.h_decl.append("float %s[V];" % hname)
+                        self.h_lines.append("_Pragma(\"unroll\") for (int i = 0; i < V; ++i) h.%s[i] = %s;" % (hname, ref))
+                    else:
+                        self.h_decl.append("float %s;" % hname)
+                        self.h_lines.append("{ const int i = 0; (void)i; h.%s = %s; }" % (hname, ref))
+                self.names[key] = ("h.%s[i]" % hname) if self.lk else ("h.%s" % hname)
+                return self.names[key]
+            if n.kind in ("t", "r"):
+                o, pre = self._leaf(n)
+                nc = "false" if o.alias_out else "true"
+                lane_var = self.var_k(n) if self.lk else True     # var_n holds here
+                aname = "a_" + pre
+                if lane_var:
+                    self.lane_ops.append((o, "k" if self.lk else "n"))
+                    self.l_decl.append("u32 %s[(%d * V + 3) / 4];" % (aname, DT_SIZE[o.dt]))
+                    self.l_lines.append("ld_w<%s, V, %s>(p.%s, k * p.%s_sk + n * p.%s_sn, l.%s);"
+                                        % (DT_NAMES[o.dt], nc, pre, pre, pre, aname))
+                    self.e_pre.append("float %s[V]; cvt_in<%s, V>(l.%s, %s);" % (aname, DT_NAMES[o.dt], aname, aname))
+                    ref = aname + "[i]"
+                else:
+                    self.l_decl.append("u32 %s[1];" % aname)
+                    self.l_lines.append("ld_w<%s, 1, %s>(p.%s, k * p.%s_sk + n * p.%s_sn, l.%s);"
+                                        % (DT_NAMES[o.dt], nc, pre, pre, pre, aname))
+                    self.e_pre.append("float %s[1]; cvt_in<%s, 1>(l.%s, %s);" % (aname, DT_NAMES[o.dt], aname, aname))
+                    ref = aname + "[0]"
+                self.names[key] = ref
+                return ref
+            args = [self.elem(a) for a in n.args]
+            expr = (UNARY_C[n.op] if n.kind == "u" else BINARY_C[n.op]).format(*args)
+            name = "x%d" % n.nid
+            self.e_lines.append("const float %s = %s;" % (name, expr))
+            self.names[key] = name
+            return name
+
+        def coords(self):
+            """(row, col) expressions of lane i in eval scope."""
+            kk = "(k + i)" if self.lk else "k"
+            nn = "n" if self.lk else "(n + i)"
+            return (kk, nn) if self.ka == 0 else (nn, kk)
+
+        def lin_index(self):
+            row, col = self.coords()
+            self.f.i64("lin_r", 0)
+            self.f.i64("lin_c", 0)
+            self.f.i64("lin_0", 0)
+            return "(u64)(p.lin_0 + %s * p.lin_r + %s * p.lin_c)" % (row, col)
+
+        def _zero(self, n, key):
+            name = "x%d" % n.nid
+            if n.op == "rand":
+                self.uses_rng = True
+                self.f.u32("rk0", 0)
+                self.f.u32("rk1", 0)
+                sid = 1 + sum(1 for m in self.st.nodes[:n.nid] if m.kind == "z" and m.op == "rand")
+                self.e_lines.append("const float %s = frand(Rng{p.rk0 + %uu, p.rk1}, %s);"
+                                    % (name, (sid * 0x68E31DA4) & 0xFFFFFFFF, self.lin_index()))
+            else:
+                o, _ = self._leaf(self.st._memo[("t", n.tix)])
+                row, col = self.coords()
+                hot, other = (row, col) if n.axis == 0 else (col, row)
+                # index tensor is a vector: address it by its longer dimension
+                step = "p.t%d_sk" % n.tix if o.shape[self.ka] > 1 else "p.t%d_sn" % n.tix
+                self.e_lines.append("const float %s = (ld_idx(p.t%d, (i64)%s * %s) == (int)%s) ? 1.0f : 0.0f;"
+                                    % (name, n.tix, other, step, hot))
+            self.names[key] = name
+            return name
+
+    # ---- vector width ---------------------------------------------------------
+    @staticmethod
+    def _pick_v(lane_ops, lane_extent, need_divisible, extra=()):
+        ops = list(lane_ops) + list(extra)
+        if not ops:
+            return 1
+        vmax = min(8, 16 // min(DT_SIZE[o.dt] for o, _ in ops))
+        v = vmax
+        while v > 1:
+            ok = (lane_extent % v == 0) if need_divisible else (lane_extent >= v)
+            for o, lane_axis in ops:
+                isz = DT_SIZE[o.dt]
+                align = min(16, v * isz)
+                sk, sn = o._frame_strides
+                lane_stride, other_stride = (sk, sn) if lane_axis == "k" else (sn, sk)
+                if lane_stride != 1:
+                    ok = False
+                if o.ptr % align or (other_stride * isz) % align:
+                    ok = False
+            if ok:
+                return v
+            v //= 2
+        return 1
+
+    def _frame(self, st, ka, ra):
+        for o in st.operands + [st.out]:
+            sk, sn = o.strides[ka], o.strides[ra]
+            if o.shape[ka] == 1:
+                sk = 0
+            if o.shape[ra] == 1:
+                sn = 0
+            o._frame_strides = (sk, sn)
+
+    # ---- passes -----------------------------------------------------------------
+    def _reduction_pass(self, st, reds, res_buf, ka, ra, full_shape, scratch, final):
+        K, N = full_shape[ka], full_shape[ra]
+        self._frame(st, ka, ra)
+        # orientation: lanes along N when the loop axis is the contiguous one
+        def lanes_ok(axis_name):
+            for o in st.operands:
+                sk, sn = o._frame_strides
+                var_k, var_n = o.shape[ka] > 1, o.shape[ra] > 1
+                if var_k and var_n:
+                    if (sn if axis_name == "n" else sk) != 1:
+                        return False
+            return True
+        lanes_on_k = (not lanes_ok("n")) and lanes_ok("k") and K > 1
+        f = _Fields()
+        em = self._Emit(st, f, ka, ra, lanes_on_k, res_buf, reds[0].level - 1)
+        outs = []
+        for r in reds:
+            outs.append(em.elem(r.args[0]))
+        eval_tail = ["out[%d][i] = %s;" % (i, e) for i, e in enumerate(outs)]
+
+        # epilogue: raw results to scratch, or the root expression into the output
+        ep = self._Emit(st, f, ka, ra, False, res_buf, reds[0].level - 1)
+        ep_lines = []
+        fresh = {r.nid: i for i, r in enumerate(reds)}
+        if final:
+            for r in reds:
+                ep.names[("h", r.nid)] = "(float)ri[%d]" % fresh[r.nid] if r.op.startswith("arg") else "r[%d]" % fresh[r.nid]
+            odt = st.out.dt
+            f.u64("o", st.out.ptr)
+            f.i64("o_sk", st.out._frame_strides[0])
+            if st.root.kind == "r" and st.root.op.startswith("arg"):
+                val = None
+                store = "st_index<%s>(p.o, k * p.o_sk, ri[%d]);" % (DT_NAMES[odt], fresh[st.root.nid])
+            else:
+                val = ep.hoist(st.root)
+                store = "{ const int i = 0; (void)i; st_one<%s>(p.o, k * p.o_sk, %s); }" % (DT_NAMES[odt], val)
+            ep_lines = ep.h_lines + [store]
+        else:
+            for r in reds:
+                av, ai = res_buf[r.nid]
+                i = fresh[r.nid]
+                if r.op.startswith("arg"):
+                    f.u64("r%dv" % r.nid, ai)
+                    ep_lines.append("reinterpret_cast<int*>(p.r%dv)[k] = ri[%d];" % (r.nid, i))
+                else:
+                    f.u64("r%dv" % r.nid, av)
+                    ep_lines.append("reinterpret_cast<float*>(p.r%dv)[k] = r[%d];" % (r.nid, i))
+
+        # geometry
+        pz = Pass()
+        if lanes_on_k:
+            V = self._pick_v(em.lane_ops, K, True)
+            CW = min(32, _pow2ceil((K + V - 1) // V))
+            RH = BLOCK // CW
+            tiles = (K + CW * V - 1) // (CW * V)
+            split = max(1, min((self.target + tiles - 1) // tiles, (N + RH * 4 - 1) // (RH * 4)))
+            seg = (N + split - 1) // split
+            split = (N + seg - 1) // seg
+            grid = (tiles, split, 1)
+            unroll = 4 if seg >= RH * 8 else 1
+            call = "red_cols_kernel<S, P, %d, %d, %d, %d>(p);" % (V, BLOCK, CW, unroll)
+            ncount = tiles
+            pz.kind = "red_cols"
+        else:
+            V = self._pick_v(em.lane_ops, N, False)
+            nvec = N // V
+            if nvec >= 2 * BLOCK or (K * 8 <= self.target and nvec > 32):
+                TPR = BLOCK
+                split = max(1, min((self.target + K - 1) // K, nvec // (BLOCK * 4)))
+                seg = (nvec + split - 1) // split
+                split = max(1, (nvec + seg - 1) // seg)
+                grid = (K * split, 1, 1)
+                unroll = 4 if seg >= BLOCK * 8 else (2 if seg >= BLOCK * 2 else 1)
+            else:
+                TPR = max(1, min(32, _pow2ceil(max(nvec, 1))))
+                split, seg = 1, nvec
+                grid = ((K + (BLOCK // TPR) - 1) // (BLOCK // TPR), 1, 1)
+                unroll = 1
+            call = "red_rows_kernel<S, P, %d, %d, %d, %d>(p);" % (V, BLOCK, TPR, unroll)
+            f.i64("nvec", nvec)
+            ncount = K
+            pz.kind = "red_rows"
+        f.i64("K", K)
+        f.i64("N", N)
+        f.i64("seg", seg)
+        f.i32("split", split)
+        nr = len(reds)
+        has_arg = any(r.op.startswith("arg") for r in reds)
+        if split > 1:
+            f.u64("part_v", scratch(4 * nr * K * split, False))
+            f.u64("part_i", scratch(4 * nr * K * split, False) if has_arg else 0)
+            f.u64("counters", scratch(4 * ncount, True))
+        else:
+            f.u64("part_v", 0)
+            f.u64("part_i", 0)
+            f.u64("counters", 0)
+        ops = " : ".join("r == %d ? %s" % (i, RED_CODE[r.op]) for i, r in enumerate(reds[:-1]))
+        ops = (ops + " : " if ops else "") + RED_CODE[reds[-1].op]
+        src = self._source(f, em, eval_tail, nr, ops, ep_lines, None, call)
+        pz.source, pz.fields, pz.grid, pz.block = src, f, grid, (BLOCK, 1, 1)
+        pz.uses_rng = em.uses_rng
+        pz.desc = "%s V=%d K=%d N=%d split=%d grid=%s" % (pz.kind, V, K, N, split, grid)
+        return pz
+
+    def _ew_pass(self, st, res_buf, ka0, ra0, rounding):
+        # an element-wise pass is free to pick its frame: prefer the one whose loop axis is contiguous
+        best = None
+        for ka, ra in ((0, 1), (1, 0)):
+            self._frame(st, ka, ra)
+            f = _Fields()
+            em = self._Emit(st, f, ka, ra, False, res_buf, 1 << 30)
+            val = em.elem(st.root)
+            K, N = st.out_shape[ka], st.out_shape[ra]
+            V = self._pick_v(em.lane_ops, N, not st.flat, extra=[(st.out, "n")])
+            cand = (V, ka, ra, f, em, val, K, N)
+            if best is None or V > best[0]:
+                best = cand
+            if st.flat:
+                break
+        V, ka, ra, f, em, val, K, N = best
+        self._frame(st, ka, ra)
+        odt = st.out.dt
+        f.u64("o", st.out.ptr)
+        f.i64("o_sk", st.out._frame_strides[0])
+        f.i64("o_sn", st.out._frame_strides[1])
+        f.i64("K", K)
+        f.i64("N", N)
+        nvec = N // V
+        f.i64("nvec", nvec)
+        sr = bool(rounding)
+        st_lines = []
+        if sr:
+            em.uses_rng = True
+            f.u32("rk0", 0)
+            f.u32("rk1", 0)
+            f.i32("sr_mb", int(rounding))
+            lin = em.lin_index()
+            st_lines.append("const SrCtx c = sr_ctx(p.sr_mb); const Rng g{p.rk0, p.rk1}; u32 ur[V];")
+            st_lines.append("_Pragma(\"unroll\") for (int i = 0; i < V; ++i) ur[i] = rng_bits(g, %s);" % lin)
+            st_lines.append("st_f<%s, V, true>(p.o, k * p.o_sk + n * p.o_sn, v, c, ur);" % DT_NAMES[odt])
+        else:
+            st_lines.append("SrCtx c; c.scale = 0.f; c.mask = 0;")
+            st_lines.append("st_f<%s, V, false>(p.o, k * p.o_sk + n * p.o_sn, v, c, nullptr);" % DT_NAMES[odt])
+        total = nvec if st.flat else K * nvec
+        unroll = 4 if total >= self.target * BLOCK * 4 else (2 if total >= self.target * BLOCK else 1)
+        grid = (max(1, (total + BLOCK * unroll - 1) // (BLOCK * unroll)), 1, 1)
+        call = "ew_kernel<S, P, %d, %d, %d, %s>(p);" % (V, BLOCK, unroll, "true" if st.flat else "false")
+        src = self._source(f, em, ["out[0][i] = %s;" % val], 0, "OP_SUM", None, st_lines, call)
+        pz = Pass()
+        pz.kind = "ew_flat" if st.flat else "ew_2d"
+        pz.source, pz.fields, pz.grid, pz.block = src, f, grid, (BLOCK, 1, 1)
+        pz.uses_rng = em.uses_rng
+        pz.desc = "%s V=%d K=%d N=%d grid=%s" % (pz.kind, V, K, N, grid)
+        if "lin_r" in f.values:
+            # linear element index = row * ncols + col of the output tensor
+            f.values["lin_r"] = st.out_shape[1] if not st.flat else 0
+            f.values["lin_c"] = 1
+        return pz
+
+    @staticmethod
+    def _source(f, em, eval_tail, nred, ops, ep_lines, st_lines, call):
+        ind = "\n        "
+        nout = max(nred, 1)
+        parts = ['#include "optree_templates.cuh"', "using namespace b200;", f.decl(), "template <int V> struct S {"]
+        parts.append("    enum { NRED = %d };" % nred)
+        parts.append("    static DEV constexpr int op(int r) { return %s; }" % ops)
+        parts.append("    struct H { %s int unused_; };" % " ".join(em.h_decl))
+        parts.append("    struct L { %s int unused_; };" % " ".join(em.l_decl))
+        parts.append("    static DEV void load_h(const P& p, i64 k, H& h) {" + ind + ind.join(em.h_lines) + "\n    }")
+        parts.append("    static DEV void load_l(const P& p, i64 k, i64 n, L& l) {" + ind + ind.join(em.l_lines) + "\n    }")
+        body = list(em.e_pre)
+        body.append("_Pragma(\"unroll\") for (int i = 0; i < V; ++i) {")
+        body.extend("    " + s for s in em.e_lines)
+        body.extend("    " + s for s in eval_tail)
+        body.append("}")
+        parts.append("    static DEV void eval(const P& p, const H& h, const L& l, i64 k, i64 n, float (&out)[%d][V]) {" % nout
+                     + ind + ind.join(body) + "\n    }")
+        if st_lines is not None:
+            parts.append("    static DEV void store(const P& p, i64 k, i64 n, const float* v) {" + ind + ind.join(st_lines) + "\n    }")
+        if ep_lines is not None:
+            parts.append("    static DEV void epilogue(const P& p, i64 k, const float* r, const int* ri) {"
+                         + ind + ind.join(ep_lines) + "\n    }")
+        parts.append("};")
+        parts.append('extern "C" __global__ void __launch_bounds__(%d) optree_kernel(const __grid_constant__ P p) { %s }'
+                     % (BLOCK, call))
+        return "\n".join(parts) + "\n"

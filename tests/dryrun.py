@@ -1,0 +1,89 @@
+"""
+A b200 backend that lowers and compiles but never touches a device: tensors get
+made-up (aligned) addresses and every kernel a statement needs is compiled to an
+sm_100a image with NVRTC instead of being launched.  Lets the CPU-only test run
+check the host lowering and that every generated kernel builds.
+"""
+import numpy as np
+
+from neon_b200 import runtime as rt
+from neon_b200.backend import B200Backend
+from neon_b200.lowering import Planner, Statement
+from neon_b200.optree import OpTreeNode
+from neon_b200.tensor import B200Tensor
+
+
+class DryTensor(B200Tensor):
+    """No device behind it: fills and copies go through the op-tree path too."""
+
+    def _assign(self, value):
+        if isinstance(value, np.ndarray):
+            return self
+        OpTreeNode.build("assign", self, value)
+        return self
+
+    def set(self, ary):
+        return self
+
+    def get(self, stream=None):
+        return np.zeros(self.shape, self.dtype)
+
+
+class DryRunBackend(B200Backend):
+
+    def __init__(self, default_dtype=np.float32, sm_count=148):
+        self.default_dtype = default_dtype
+        self.device_id = 0
+        self.sm_count = sm_count
+        self.stream = 0
+        self.round_mode = 0
+        self.bsz = None
+        self._min_dims = 2
+        self._planner = Planner(sm_count)
+        self._temps, self._temps_used = {}, {}
+        self._next = 0x7F0000000000
+        self.launches = 0
+        self.passes = []            # every Pass planned so far
+        self.sources = {}           # source -> image size
+        self.compile = True
+        self._scratch = None
+        self.rng = np.random.RandomState(0)
+
+    def cleanup_backend(self):
+        pass
+
+    def _fake(self, nbytes):
+        p = self._next
+        self._next += (nbytes + 255) & ~255
+        return p
+
+    def _scratch_alloc(self, nbytes, zero):
+        return self._fake(nbytes)
+
+    def empty(self, shape, dtype=None, name=None, persist_values=True, **kw):
+        dtype = self.default_dtype if dtype is None else dtype
+        if not isinstance(shape, (tuple, list)):
+            shape = (int(shape),)
+        size = int(np.prod(shape)) * np.dtype(dtype).itemsize
+        return DryTensor(self, shape, dtype=dtype, name=name, gpudata=self._fake(max(size, 1)),
+                         rounding=self.round_mode)
+
+    def array(self, ary, dtype=None, **kw):
+        return self.empty(np.asarray(ary).shape, dtype=dtype or self.default_dtype)
+
+    def zeros(self, shape, dtype=None, **kw):
+        return self.empty(shape, dtype=dtype)
+
+    ones = zeros
+
+    def _run(self, out, expr):
+        stack = OpTreeNode({"op": "assign"}, out, expr).traverse([])
+        st = Statement(stack)
+        passes = self._planner.plan(st, self._scratch_alloc, rounding=self._rounding_bits(out))
+        for pz in passes:
+            pz.fields.pack()
+            self.passes.append(pz)
+            self.launches += 1
+            if self.compile and pz.source not in self.sources:
+                img, _ = rt.nvrtc_compile(pz.source)
+                self.sources[pz.source] = len(img)

@@ -1,0 +1,46 @@
+"""Comparison rules of the parity tests (the bar the backend is held to):
+integer / index outputs bit-exact; fp32 within 1e-5 relative of the float64
+checker; fp16 within one unit in the last place of the float64 checker."""
+import numpy as np
+
+RTOL_F32 = 1e-5
+
+
+def ulp16(x):
+    """Spacing of fp16 at |x| (float64 array), never below the smallest subnormal step."""
+    h = np.abs(np.asarray(x, np.float64)).astype(np.float16)
+    h = np.where(np.isfinite(h), h, np.float16(65504))
+    return np.maximum(np.spacing(h).astype(np.float64), 2.0 ** -24)
+
+
+def check_output(name, got, want64, dtype, scale=None):
+    """Assert ``got`` (device result, storage dtype) matches ``want64`` (checker run in float64)."""
+    dtype = np.dtype(dtype)
+    want64 = np.asarray(want64)
+    assert got.shape == want64.shape, (name, got.shape, want64.shape)
+    if dtype.kind in "iu":
+        assert np.array_equal(got.astype(np.int64), want64.astype(np.int64)), \
+            "%s: %d of %d indices differ" % (name, int((got != want64).sum()), got.size)
+        return
+    g = got.astype(np.float64)
+    w = want64.astype(np.float64)
+    if dtype == np.float16:
+        err = np.abs(g - w) / ulp16(w)
+        assert np.all(err <= 1.0 + 1e-3), "%s: fp16 error %.3f ulp" % (name, err.max())
+        return
+    mag = float(np.max(np.abs(w))) if w.size else 0.0
+    atol = RTOL_F32 * (scale if scale is not None else max(mag, 1e-30)) * 0.1
+    bad = np.abs(g - w) > RTOL_F32 * np.abs(w) + atol
+    assert not bad.any(), "%s: %d of %d fp32 values off; worst rel %.3g" % (
+        name, int(bad.sum()), g.size, float(np.max(np.abs(g - w) / np.maximum(np.abs(w), 1e-30))))
+
+
+def check_fingerprint(name, got, golden, prefix):
+    """Compare a device result with the committed fingerprint of neon's NervanaCPU result."""
+    from tests.cases import summarize
+    fp = summarize(got)
+    if "full" in fp:
+        want = golden[prefix + "/full"]
+        return fp["full"], want
+    step = int(golden[prefix + "/step"])
+    return got.reshape(-1)[::step], golden[prefix + "/sample"]

@@ -1,0 +1,80 @@
+"""CPU tests of the host lowering: every statement of the standard cases plans,
+every generated kernel compiles for sm_100a, and the reference's error behaviour
+for malformed programs is kept."""
+import numpy as np
+import pytest
+
+from tests.cases import cfg2, cfg4, standard_cases
+from tests.dryrun import DryRunBackend
+
+
+def _run_dry(be, case):
+    arrays = case.inputs(np.random.RandomState(0))
+    t = {k: be.empty(a.shape, a.dtype) for k, a in arrays.items()}
+    for k, (shape, dt) in case.outputs.items():
+        t[k] = be.empty(shape, dt)
+    case.run(be, t)
+    return t
+
+
+@pytest.fixture(scope="module")
+def dry():
+    return DryRunBackend()
+
+
+@pytest.mark.parametrize("case", standard_cases(), ids=lambda c: c.name)
+def test_case_lowers_and_compiles(case, dry):
+    before = len(dry.passes)
+    _run_dry(dry, case)
+    assert len(dry.passes) > before
+
+
+def test_softmax_is_three_passes_with_deduplicated_max(dry):
+    dry2 = DryRunBackend()
+    dry2.compile = False
+    x = dry2.empty((32000, 256))
+    y = dry2.empty((32000, 256))
+    y[:] = dry2.exp(x - dry2.max(x, axis=0)) / dry2.sum(dry2.exp(x - dry2.max(x, axis=0)), axis=0)
+    kinds = [p.kind for p in dry2.passes]
+    assert kinds == ["red_cols", "red_cols", "ew_2d"]          # max computed once
+
+
+def test_axis1_statistics_use_row_kernels_and_vector_width_8_for_fp16():
+    be = DryRunBackend()
+    be.compile = False
+    _run_dry(be, cfg4(256, 401408))
+    assert [p.kind for p in be.passes] == ["red_rows", "red_rows", "ew_2d"]
+    assert all("V=8" in p.desc for p in be.passes)
+
+
+def test_whole_tensor_reduction_is_one_flat_pass():
+    be = DryRunBackend()
+    be.compile = False
+    z = be.empty((512, 384), np.float16)
+    tot = be.empty((1, 1))
+    tot[:] = be.sum(z)
+    tot[:] = be.max(be.absolute(z))
+    assert [p.kind for p in be.passes] == ["red_rows", "red_rows"]
+    assert "K=1 N=196608" in be.passes[0].desc
+
+
+def test_reference_error_behaviour():
+    be = DryRunBackend()
+    be.compile = False
+    a, b = be.empty((4, 6)), be.empty((5, 6))
+    out = be.empty((4, 6))
+    with pytest.raises(TypeError):
+        out[:] = a + b                                   # float_ew.py:824-825
+    with pytest.raises(TypeError):
+        out[:] = be.rint(a)                              # not in the kernel vocabulary
+    with pytest.raises(ValueError):
+        be.onehot(be.empty((1, 6), np.int32), axis=2)
+
+
+def test_unaligned_views_fall_back_to_narrower_vectors():
+    be = DryRunBackend()
+    be.compile = False
+    x = be.empty((64, 100))
+    out = be.empty((64, 99))
+    out[:] = x[:, 1:] * 2.0                              # 4-byte aligned only, odd row length
+    assert "V=1" in be.passes[-1].desc

@@ -1,0 +1,190 @@
+"""GPU parity tests: the CUDA backend against the numpy checker and against the
+committed NervanaCPU fingerprints, on the same seeded inputs.  Every call goes
+python -> ctypes -> libb200ew.so."""
+import numpy as np
+import pytest
+
+from oracle import sround
+from oracle.numpy_backend import OracleBackend
+from tests import cases
+from tests.parity import check_fingerprint, check_output
+
+pytestmark = pytest.mark.gpu
+
+STANDARD = cases.standard_cases()
+
+
+def _oracle64(case):
+    with np.errstate(all="ignore"):
+        return cases.run_case(OracleBackend(default_dtype=np.float64), case, compute_dtype=np.float64)
+
+
+def _compare(case, got, want):
+    for k, (shape, dt) in case.outputs.items():
+        check_output("%s/%s" % (case.name, k), got[k], want[k], dt)
+    for k in got:
+        if k in case.outputs or k.startswith("grad"):
+            continue
+        check_output("%s/%s(in place)" % (case.name, k), got[k], want[k], got[k].dtype)
+
+
+@pytest.mark.parametrize("case", STANDARD, ids=lambda c: c.name)
+def test_case_matches_checker(case, b200):
+    got = cases.run_case(b200, case)
+    _compare(case, got, _oracle64(case))
+
+
+@pytest.mark.parametrize("case", STANDARD[:5], ids=lambda c: c.name)
+def test_benchmark_configs_match_nervanacpu_golden(case, b200, golden):
+    """The five configurations against fingerprints made by neon's own NervanaCPU."""
+    got = cases.run_case(b200, case)
+    for k, (shape, dt) in case.outputs.items():
+        g, w = check_fingerprint(k, got[k], golden, "%s/float64/%s" % (case.name, k))
+        check_output("%s/%s vs golden" % (case.name, k), np.asarray(g), np.asarray(w), dt)
+
+
+@pytest.mark.parametrize("case", [cases.cfg2(), cases.cfg4(256, 56 * 56 * 16),
+                                  cases.cfg5(2048, 2048), cases.cfg3(n=1000000, steps=3)],
+                         ids=lambda c: c.name)
+def test_large_configs_match_checker(case, b200):
+    """Benchmark shapes at (or scaled towards) their quoted sizes: split reductions,
+    several blocks per row/column, more than one wave of blocks."""
+    got = cases.run_case(b200, case)
+    _compare(case, got, _oracle64(case))
+
+
+def test_full_size_properties_cfg5(b200):
+    """2^28 elements of the fp16 chain with stochastic rounding: size-independent checks.
+    total must equal the float64 sum of the device-produced z (relative to sum|z|),
+    peak must equal max|z| exactly, and the rounding must be unbiased."""
+    be = b200
+    rows = cols = 16384
+    rng = np.random.RandomState(5)
+    xh = rng.uniform(-4, 4, (rows, cols)).astype(np.float16)
+    yh = rng.uniform(-4, 4, (rows, cols)).astype(np.float16)
+    x, y = be.array(xh, dtype=np.float16), be.array(yh, dtype=np.float16)
+    z = be.empty((rows, cols), dtype=np.float16)
+    z.rounding = True
+    total, peak = be.empty((1, 1)), be.empty((1, 1))
+    z[:] = be.tanh(x) * be.sqrt(be.absolute(y)) + 0.5 * x * y
+    total[:] = be.sum(z)
+    peak[:] = be.max(be.absolute(z))
+    zh = z.get()
+    z64 = zh.astype(np.float64)
+    assert abs(float(total.get()[0, 0]) - z64.sum()) <= 1e-5 * np.abs(z64).sum()
+    assert float(peak.get()[0, 0]) == float(np.abs(zh).max())
+    # rounding: stored value is one of the two fp16 neighbours of the exact value ...
+    sl = slice(0, 1 << 22)
+    xf = xh.reshape(-1)[sl].astype(np.float64)
+    yf = yh.reshape(-1)[sl].astype(np.float64)
+    exact = np.tanh(xf) * np.sqrt(np.abs(yf)) + 0.5 * xf * yf
+    from tests.parity import ulp16
+    err = (z64.reshape(-1)[sl] - exact) / ulp16(exact)
+    assert np.abs(err).max() <= 1.0 + 1e-2
+    # ... and the mean signed error over 2^28 samples is far below one ulp
+    xf = xh.astype(np.float32)
+    yf = yh.astype(np.float32)
+    bias = 0.0
+    chunk = 1 << 24
+    zf, xr, yr = zh.reshape(-1), xf.reshape(-1), yf.reshape(-1)
+    for s in range(0, zf.size, chunk):
+        a = xr[s:s + chunk].astype(np.float64)
+        b = yr[s:s + chunk].astype(np.float64)
+        ex = np.tanh(a) * np.sqrt(np.abs(b)) + 0.5 * a * b
+        bias += ((zf[s:s + chunk].astype(np.float64) - ex) / ulp16(ex)).sum()
+    bias /= zf.size
+    assert abs(bias) < 1e-4, "mean rounding bias %.3g ulp" % bias
+
+
+def test_stochastic_rounding_bit_exact_against_restated_rule(b200):
+    """z = 0.5*x + y is exact in fp32 for these inputs, so the stored fp16 must equal
+    the restated rounding rule applied to the same random words, bit for bit."""
+    be = b200
+    rng = np.random.RandomState(11)
+    shape = (300, 1000)
+    xh = rng.uniform(-4, 4, shape).astype(np.float16)
+    yh = (rng.uniform(-1, 1, shape) * 2.0 ** -6).astype(np.float16)
+    x, y = be.array(xh, dtype=np.float16), be.array(yh, dtype=np.float16)
+    for bits in (True, 5, 1):
+        z = be.empty(shape, dtype=np.float16)
+        z.rounding = bits
+        seed, launch = be.rng_get_state()[1]
+        z[:] = 0.5 * x + y
+        val = (np.float32(0.5) * xh.astype(np.float32) + yh.astype(np.float32)).astype(np.float32)
+        key = sround.launch_key(int(seed), int(launch))
+        ur = sround.rng_bits(key[0], key[1], np.arange(val.size, dtype=np.uint64)).reshape(shape)
+        want = sround.store(val, np.float16, bits, ur)
+        got = z.get()
+        assert np.array_equal(got.view(np.uint16), want.view(np.uint16)), bits
+    # fp32 output, 12 bits
+    zf = be.empty(shape, dtype=np.float32)
+    zf.rounding = 12
+    seed, launch = be.rng_get_state()[1]
+    zf[:] = 0.5 * x + y
+    key = sround.launch_key(int(seed), int(launch))
+    ur = sround.rng_bits(key[0], key[1], np.arange(val.size, dtype=np.uint64)).reshape(shape)
+    assert np.array_equal(zf.get().view(np.uint32), sround.store(val, np.float32, 12, ur).view(np.uint32))
+
+
+def test_stochastic_rounding_one_bit_distribution(b200):
+    """neon tests/test_backend_sr.py:52-71: ones + 0.1 at one mantissa bit gives only
+    1.0 and 1.5, more than 10% of them 1.5 and more than 70% 1.0."""
+    be = b200
+    n = 10
+    a = be.ones((n * n * 100, 1), dtype=np.float16) if False else be.ones((1000, 100))
+    c = be.empty((1000, 100), dtype=np.float16)
+    c.rounding = 1
+    c[:] = a + 0.1
+    got = c.get()
+    assert set(np.unique(got).tolist()) <= {1.0, 1.5}
+    frac = float((got == 1.5).mean())
+    assert 0.1 < frac < 0.3
+
+
+def test_integer_stores_round_to_nearest_even_and_saturate(b200):
+    be = b200
+    vals = np.array([[0.5, 1.5, 2.5, -0.5, -1.5, 126.6, 127.5, 300.0, -129.0, -1000.0, 3.49, -3.51]], np.float32)
+    x = be.array(vals)
+    for dt in (np.int8, np.uint8, np.int16, np.uint16, np.int32, np.uint32):
+        out = be.empty(vals.shape, dtype=dt)
+        out[:] = x * 1.0
+        assert np.array_equal(out.get(), sround.nearest_int(vals, dt)), dt
+
+
+def test_rng_reproducible_after_reset_and_state_restore(b200):
+    """neon tests/test_backend_randomstate.py:23-74,145-178 for the device generator."""
+    be = b200
+    be.rng_reset()
+    a = be.empty((200, 300))
+    a[:] = be.rand()
+    first = a.get()
+    assert 0.0 <= first.min() and first.max() <= 1.0 and abs(first.mean() - 0.5) < 0.01
+    state = be.rng_get_state()
+    a[:] = be.rand()
+    second = a.get()
+    assert not np.array_equal(first, second)
+    be.rng_set_state(state)
+    a[:] = be.rand()
+    assert np.array_equal(a.get(), second)
+    be.rng_reset()
+    a[:] = be.rand()
+    assert np.array_equal(a.get(), first)
+    mask = be.empty((200, 300))
+    be.make_binary_mask(mask, keepthresh=0.3)
+    m = mask.get()
+    assert set(np.unique(m).tolist()) <= {0.0, 1.0} and abs(m.mean() - 0.3) < 0.02
+
+
+def test_onehot_and_views(b200):
+    be = b200
+    idx = np.random.RandomState(3).randint(0, 10, (1, 64)).astype(np.int32)
+    out = be.zeros((10, 64))
+    out[:] = be.onehot(be.array(idx, dtype=np.int32), axis=0)
+    want = np.zeros((10, 64), np.float32)
+    want[idx[0], np.arange(64)] = 1
+    assert np.array_equal(out.get(), want)
+    x = be.array(np.arange(48, dtype=np.float32).reshape(6, 8))
+    assert np.array_equal(x[1:5, 2:7].get(), np.arange(48).reshape(6, 8)[1:5, 2:7])
+    assert np.array_equal(x.T.get(), np.arange(48).reshape(6, 8).T)
+    assert np.array_equal(x.reshape(8, 6).get(), np.arange(48).reshape(8, 6))
+    assert np.array_equal(x[3].get(), np.arange(48).reshape(6, 8)[3:4])
