@@ -1,0 +1,307 @@
+#!/usr/bin/env python
+"""
+Benchmark of the compound-optree engine.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
+
+Workload (config 5 of the baseline list, the largest single-GPU one): per GPU,
+x, y fp16 of shape (32768, 32768) ~U(-4,4) and one step =
+
+    z[:]     = tanh(x) * sqrt(|y|) + 0.5 * x * y       stored as fp16 with stochastic rounding
+    total[:] = sum(z)                                   over all elements
+    peak[:]  = max(|z|)                                 over all elements
+
+The metric is effective HBM bandwidth: algorithmic bytes (every distinct input of
+a statement read once, its output written once: 6 + 2 + 2 bytes per element)
+divided by device time.  With N > 1 every rank holds a (32768, 32768) column
+shard of a (32768, N*32768) tensor (weak scaling), the element-wise statement is
+shard-local and the two whole-tensor reductions end with an NCCL all-reduce.
+
+Prints one JSON line.  `value` times the statements with inputs resident in HBM;
+`e2e` repeats them with the host->device copy of x and y (pinned memory) and the
+device->host read of total and peak inside the timed region.
+"""
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+ROWS = COLS = 32768
+BYTES_PER_ELEMENT = 6 + 2 + 2          # z statement, total, peak (algorithmic)
+Z_BYTES_PER_ELEMENT = 6                # dominant kernel: read x, y (fp16), write z (fp16)
+METRIC = "compound-optree effective HBM GB/s"
+# dram__bytes_read.sum + dram__bytes_write.sum of the z kernel divided by its elements,
+# from the ncu capture summarised in profiles/ (None until one has been taken)
+Z_DRAM_BYTES_PER_ELEMENT = None
+
+
+def measured_peak():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    try:
+        with open(path) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured"
+    except Exception:
+        return 6650.0, "fallback"
+
+
+class ClockSampler(object):
+    """nvidia-smi SM clock / throttle-reason samples while the timed region runs."""
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+         "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, device):
+        self.device = device
+        self.lines = []
+        self.proc = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.device), "--query-gpu=" + self.Q,
+                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except Exception:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            pass
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for ln in self.lines:
+            f = [s.strip() for s in ln.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1]))
+                mx.append(float(f[2]))
+            except ValueError:
+                continue
+            for n, v in zip(names, f[5:9]):
+                if v.lower().startswith("active"):
+                    reasons.add(n)
+        return {"sm_mhz": float(np.median(sm)) if sm else None,
+                "sm_max_mhz": float(max(mx)) if mx else None,
+                "samples": len(sm), "reasons": sorted(reasons)}
+
+
+def fill_uniform_f16(dst, seed, lo=-4.0, hi=4.0, chunk=1 << 24):
+    """Seeded U(lo,hi) into the fp16 array dst, chunked to bound host memory."""
+    rng = np.random.default_rng(seed)
+    flat = dst.reshape(-1)
+    for s in range(0, flat.size, chunk):
+        n = min(chunk, flat.size - s)
+        flat[s:s + n] = (rng.random(n, dtype=np.float32) * np.float32(hi - lo) + np.float32(lo)).astype(np.float16)
+
+
+def statements(be, x, y, z, total, peak):
+    z[:] = be.tanh(x) * be.sqrt(be.absolute(y)) + 0.5 * x * y
+    total[:] = be.sum(z)
+    peak[:] = be.max(be.absolute(z))
+
+
+def cpu_port_rate(elements, reps):
+    """The numpy checker (restatement of NervanaCPU) on a bounded sample: GB/s, seconds per pass."""
+    from oracle.numpy_backend import OracleBackend
+    be = OracleBackend(default_dtype=np.float32)
+    cols = 4096
+    rows = elements // cols
+    rng = np.random.default_rng(0)
+    xh = (rng.random((rows, cols), dtype=np.float32) * 8 - 4)
+    yh = (rng.random((rows, cols), dtype=np.float32) * 8 - 4)
+    x, y = be.array(xh), be.array(yh)          # fp16 storage is upcast for the CPU run
+    z, total, peak = be.zeros((rows, cols)), be.zeros((1, 1)), be.zeros((1, 1))
+    best = None
+    for _ in range(reps):
+        t0 = time.perf_counter()
+        statements(be, x, y, z, total, peak)
+        dt = time.perf_counter() - t0
+        best = dt if best is None else min(best, dt)
+    return rows * cols * BYTES_PER_ELEMENT / best / 1e9, best
+
+
+def run_reference(args, rank, world):
+    """Reference arm: the CPU implementation of the path (numpy checker, the port of
+    neon's NervanaCPU, which is single threaded) on this box's host cores."""
+    if rank != 0:
+        return
+    sample = 1 << 24
+    for _ in range(args.warmup):
+        cpu_port_rate(sample, 1)
+    t0 = time.perf_counter()
+    rates = [cpu_port_rate(sample, 1) for _ in range(args.steps)]
+    wall = time.perf_counter() - t0
+    gbs = float(np.mean([r[0] for r in rates]))
+    ms = float(np.mean([r[1] for r in rates])) * 1e3
+    line = {
+        "impl": "reference", "metric": METRIC, "value": gbs, "unit": "GB/s", "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": "cfg5 fp16 chain + sum + max|z|", "rows": sample // 4096, "cols": 4096},
+        "cpu_baseline": {"value": gbs, "unit": "GB/s", "cores": 1, "kind": "port",
+                         "sample": "%d of 2^30 elements per step, numpy restatement of NervanaCPU, "
+                                   "fp16 inputs upcast to fp32" % sample},
+        "e2e": {"value": gbs, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "host_cores": os.cpu_count(), "wall_s": wall,
+    }
+    print(json.dumps(line))
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="b200")
+    ap.add_argument("--rows", type=int, default=ROWS)
+    ap.add_argument("--cols", type=int, default=COLS)
+    ap.add_argument("--e2e-steps", type=int, default=3)
+    ap.add_argument("--no-cpu", action="store_true")
+    args = ap.parse_args()
+
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if args.impl == "reference":
+        return run_reference(args, rank, world)
+    if world != args.gpus:
+        raise SystemExit("--gpus %d but WORLD_SIZE=%d: launch with torch.distributed.run" % (args.gpus, world))
+
+    from neon_b200 import runtime as rt
+    if world > 1:
+        from neon_b200.sharded import gen_sharded_backend
+        be = gen_sharded_backend(rank=rank, world_size=world, device_id=local_rank, rng_seed=0)
+        barrier, max_over_ranks = be.host_barrier, be.host_max
+    else:
+        from neon_b200 import gen_backend
+        be = gen_backend(backend="b200", rng_seed=0, device_id=local_rank)
+        barrier, max_over_ranks = (lambda: None), (lambda v: v)
+
+    rows, cols = args.rows, args.cols
+    n_local = rows * cols
+    # pinned host copies of this rank's shard (also the source of the e2e copies)
+    nbytes = n_local * 2
+    hx_p, hy_p = rt.host_alloc(nbytes), rt.host_alloc(nbytes)
+    import ctypes
+    hx = np.frombuffer((ctypes.c_char * nbytes).from_address(hx_p), dtype=np.float16).reshape(rows, cols)
+    hy = np.frombuffer((ctypes.c_char * nbytes).from_address(hy_p), dtype=np.float16).reshape(rows, cols)
+    fill_uniform_f16(hx, 100 + rank)
+    fill_uniform_f16(hy, 200 + rank)
+
+    kw = {"parallel": True} if world > 1 else {}
+    gshape = (rows, cols * world)
+    x = be.empty(gshape, dtype=np.float16, **kw)
+    y = be.empty(gshape, dtype=np.float16, **kw)
+    z = be.empty(gshape, dtype=np.float16, **kw)
+    z.rounding = True
+    total, peak = be.empty((1, 1)), be.empty((1, 1))
+    rt.memcpy_h2d(x.ptr, hx_p, nbytes, be.stream, sync=True)
+    rt.memcpy_h2d(y.ptr, hy_p, nbytes, be.stream, sync=True)
+
+    for _ in range(max(args.warmup, 3)):
+        statements(be, x, y, z, total, peak)
+    be.synchronize()
+
+    # ---- timed region: K steps, inputs resident in HBM (4 GiB of inputs per step >> L2)
+    ev0, ev1 = be.init_mark(), be.init_mark()
+    kz = [(be.init_mark(), be.init_mark()) for _ in range(args.steps)]
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+        time.sleep(0.3)
+    launches0 = be.launches
+    barrier()
+    be.synchronize()
+    be.record_mark(ev0)
+    for s in range(args.steps):
+        be.record_mark(kz[s][0])
+        z[:] = be.tanh(x) * be.sqrt(be.absolute(y)) + 0.5 * x * y
+        be.record_mark(kz[s][1])
+        total[:] = be.sum(z)
+        peak[:] = be.max(be.absolute(z))
+    be.record_mark(ev1)
+    be.synchronize()
+    barrier()
+    ms_total = max_over_ranks(be.get_time(ev0, ev1))
+    launches = be.launches - launches0
+    clocks = sampler.stop() if rank == 0 else None
+    z_ms = float(np.mean([be.get_time(a, b) for a, b in kz]))
+    res_total, res_peak = float(total.get()[0, 0]), float(peak.get()[0, 0])
+
+    # ---- end to end: host buffers in, host scalars out, every step
+    e2e_steps = max(1, args.e2e_steps)
+    barrier()
+    be.synchronize()
+    t0 = time.perf_counter()
+    be.record_mark(ev0)
+    for s in range(e2e_steps):
+        rt.memcpy_h2d(x.ptr, hx_p, nbytes, be.stream, sync=False)
+        rt.memcpy_h2d(y.ptr, hy_p, nbytes, be.stream, sync=False)
+        statements(be, x, y, z, total, peak)
+        total.get()
+        peak.get()
+    be.record_mark(ev1)
+    be.synchronize()
+    barrier()
+    e2e_ms = max_over_ranks(be.get_time(ev0, ev1))
+
+    if rank != 0:
+        return
+    n_global = n_local * world
+    ms_step = ms_total / args.steps
+    value = n_global * BYTES_PER_ELEMENT / (ms_step * 1e-3) / 1e9
+    e2e_value = n_global * BYTES_PER_ELEMENT / (e2e_ms / e2e_steps * 1e-3) / 1e9
+    peak_gbs, peak_kind = measured_peak()
+    z_gbs = n_local * Z_BYTES_PER_ELEMENT / (z_ms * 1e-3) / 1e9
+    line = {
+        "metric": METRIC, "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps,
+        "warmup": max(args.warmup, 3), "ms_per_step": ms_step, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": "cfg5: z=tanh(x)*sqrt(|y|)+0.5*x*y (fp16, stochastic rounding), "
+                               "total=sum(z), peak=max|z|",
+                   "rows": rows, "cols_per_gpu": cols, "elements_per_gpu": n_local,
+                   "sharding": "columns" if world > 1 else "none",
+                   "l2": "inputs (4 GiB per step) exceed L2; no flush needed",
+                   "algorithmic_bytes_per_element": BYTES_PER_ELEMENT},
+        "elements_per_s": n_global / (ms_step * 1e-3),
+        "pct_of_8TBps_per_gpu": 100.0 * value / world / 8000.0,
+        "roofline": {"bound": "hbm", "kernel": "ew_flat (z statement)", "achieved": z_gbs,
+                     "peak": peak_gbs, "peak_kind": peak_kind, "unit": "GB/s",
+                     "frac": z_gbs / peak_gbs, "ms_per_launch": z_ms,
+                     "algorithmic_bytes_per_launch": n_local * Z_BYTES_PER_ELEMENT, "traffic": None},
+        "e2e": {"value": e2e_value, "unit": "GB/s", "h2d_bytes_per_step": 2 * nbytes,
+                "d2h_bytes_per_step": 8, "steps": e2e_steps, "ms_per_step": e2e_ms / e2e_steps},
+        "gpu_launches": launches, "clocks": clocks,
+        "results": {"total": res_total, "peak": res_peak},
+    }
+    if Z_DRAM_BYTES_PER_ELEMENT is not None:
+        line["roofline"]["traffic"] = Z_DRAM_BYTES_PER_ELEMENT * n_local
+    if not args.no_cpu:
+        gbs, sec = cpu_port_rate(1 << 24, 10)
+        line["cpu_baseline"] = {"value": gbs, "unit": "GB/s", "cores": 1, "kind": "port",
+                                "sample": "2^24 of 2^30 elements, best of 10 passes (%.2f s each), numpy "
+                                          "restatement of NervanaCPU, fp16 inputs upcast to fp32" % sec}
+    print(json.dumps(line))
+
+
+if __name__ == "__main__":
+    main()

@@ -283,7 +283,7 @@ class B200Backend(OpTreeBackend):
         for pz in passes:
             kernel = self._kernels.get(pz.source)
             if kernel is None:
-                kernel = self._kernels[pz.source] = rt.kernel_get(pz.source)
+                kernel = self._kernels[pz.source] = rt.kernel_get(pz.source, pz.name)
             if pz.uses_rng:
                 k0, k1 = rt.rng_next_key()
                 pz.fields.values["rk0"] = k0

@@ -771,7 +771,7 @@ class Planner(object):
             f.u64("counters", 0)
         ops = " : ".join("r == %d ? %s" % (i, RED_CODE[r.op]) for i, r in enumerate(reds[:-1]))
         ops = (ops + " : " if ops else "") + RED_CODE[reds[-1].op]
-        src = self._source(f, em, eval_tail, nr, ops, ep_lines, None, call)
+        src, pz.name = self._source(f, em, eval_tail, nr, ops, ep_lines, None, call)
         pz.source, pz.fields, pz.grid, pz.block = src, f, grid, (BLOCK, 1, 1)
         pz.uses_rng = em.uses_rng
         pz.desc = "%s V=%d K=%d N=%d split=%d grid=%s" % (pz.kind, V, K, N, split, grid)
@@ -820,8 +820,9 @@ class Planner(object):
         unroll = 4 if total >= self.target * BLOCK * 4 else (2 if total >= self.target * BLOCK else 1)
         grid = (max(1, (total + BLOCK * unroll - 1) // (BLOCK * unroll)), 1, 1)
         call = "ew_kernel<S, P, %d, %d, %d, %s>(p);" % (V, BLOCK, unroll, "true" if st.flat else "false")
-        src = self._source(f, em, ["out[0][i] = %s;" % val], 0, "OP_SUM", None, st_lines, call)
+        src, name = self._source(f, em, ["out[0][i] = %s;" % val], 0, "OP_SUM", None, st_lines, call)
         pz = Pass()
+        pz.name = name
         pz.kind = "ew_flat" if st.flat else "ew_2d"
         pz.source, pz.fields, pz.grid, pz.block = src, f, grid, (BLOCK, 1, 1)
         pz.uses_rng = em.uses_rng
@@ -856,6 +857,10 @@ class Planner(object):
             parts.append("    static DEV void epilogue(const P& p, i64 k, const float* r, const int* ri) {"
                          + ind + ind.join(ep_lines) + "\n    }")
         parts.append("};")
-        parts.append('extern "C" __global__ void __launch_bounds__(%d) optree_kernel(const __grid_constant__ P p) { %s }'
-                     % (BLOCK, call))
-        return "\n".join(parts) + "\n"
+        body = "\n".join(parts) + "\n"
+        # kernel name = skeleton + digest of the instance, so profiles can tell instances apart
+        import zlib
+        name = "ot_%s_%08x" % (call.split("<")[0], zlib.crc32(body.encode()) & 0xFFFFFFFF)
+        body += ('extern "C" __global__ void __launch_bounds__(%d) %s(const __grid_constant__ P p) { %s }\n'
+                 % (BLOCK, name, call))
+        return body, name

@@ -17,13 +17,16 @@ import numpy as np
 
 
 class Case(object):
-    def __init__(self, name, inputs, outputs, run, tol=None, gpu_semantics=False):
+    def __init__(self, name, inputs, outputs, run, tol=None, gpu_semantics=False, derived=None):
         self.name = name
         self.inputs = inputs      # callable(rng) -> {name: ndarray (storage dtype)}
         self.outputs = outputs    # {name: (shape, storage dtype)}
         self.run = run            # callable(be, t) -> None
         self.tol = tol or {}
         self.gpu_semantics = gpu_semantics   # True: result undefined on NervanaCPU
+        # outputs that are functions of another (rounded) output of the same run:
+        # {name: callable(results) -> (expected float64 array, magnitude for the tolerance)}
+        self.derived = derived or {}
 
     def __repr__(self):
         return "Case(%s)" % self.name
@@ -172,9 +175,21 @@ def cfg5(rows=32768, cols=32768, rounding=False):
         t["total"][:] = be.sum(z, axis=None)
         t["peak"][:] = be.max(be.absolute(z), axis=None)
 
+    # total and peak are reductions of the *stored* fp16 z, and total cancels heavily:
+    # they are checked against the float64 reduction of the z the same run produced,
+    # relative to sum|z| (a 1-ulp difference in z between two backends moves total by
+    # far more than 1e-5 of itself)
+    def want_total(res):
+        z64 = res["z"].astype(np.float64)
+        return np.array([[z64.sum()]]), float(np.abs(z64).sum())
+
+    def want_peak(res):
+        return np.array([[np.abs(res["z"].astype(np.float64)).max()]]), None
+
     return Case("cfg5_chain_%dx%d" % (rows, cols), inputs,
                 {"z": ((rows, cols), np.float16), "total": ((1, 1), np.float32),
-                 "peak": ((1, 1), np.float32)}, run)
+                 "peak": ((1, 1), np.float32)}, run,
+                derived={"total": want_total, "peak": want_peak})
 
 
 # ----------------------------------------------------------------------------
