@@ -65,7 +65,8 @@ class B200Backend(OpTreeBackend):
     def __init__(self, rng_seed=None, default_dtype=np.float32, stochastic_round=False,
                  deterministic_update=False, deterministic=None, device_id=0, bench=False,
                  scratch_size=0, hist_bins=64, hist_offset=-48, compat_mode=None,
-                 enable_winograd=True, cache_dir=None, num_devices=None, max_devices=None):
+                 enable_winograd=True, cache_dir=None, num_devices=None, max_devices=None,
+                 precise_math=False):
         if default_dtype not in (np.float16, np.float32):
             raise ValueError("Default data type for the b200 backend must be float16 or 32")
         if rt.device_count() <= int(device_id):
@@ -82,7 +83,7 @@ class B200Backend(OpTreeBackend):
         self.round_mode = None
         self.set_stochastic_round(stochastic_round)
         self._scratch = _Scratch()
-        self._planner = Planner(self.sm_count)
+        self._planner = Planner(self.sm_count, precise_math=precise_math)
         self._kernels = {}
         self._temps = {}
         self._temps_used = {}
@@ -304,6 +305,8 @@ class B200Backend(OpTreeBackend):
             rounding = min(int(rounding), 15)
         elif out.dtype.type is np.float16:
             rounding = min(int(rounding), 10)
+        elif out.dtype.kind != "f":
+            rounding = 1                       # integer stores: on/off only
         return max(int(rounding), 1)
 
     # ------------------------------------------------------------------ factories (nervanagpu.py:1285-1439)

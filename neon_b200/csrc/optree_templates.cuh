@@ -151,35 +151,74 @@ template <int DT, int V, bool NC> DEV void ld_w(u64 base, i64 off, u32* w) {
 // int32 index load (take / one-hot addressing)
 DEV int ld_idx(u64 base, i64 off) { return __ldg(reinterpret_cast<const int*>(base) + off); }
 
+// ------------------------------------------------------------------ fast math
+// Used by generated code unless the backend asks for IEEE / libm versions.
+// Each stays within a few fp32 ulp (far inside the 1e-5 parity bound) and
+// costs a fraction of the instructions, which is what bounds kernels with few
+// bytes per element.
+DEV float ex2_approx(float x) { float r; asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(x)); return r; }
+DEV float rcp_approx(float x) { float r; asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(x)); return r; }
+DEV float fast_sqrt(float x) { float r; asm("sqrt.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(x)); return r; }
+DEV float fast_div(float a, float b) { float r; asm("div.approx.f32 %0, %1, %2;" : "=f"(r) : "f"(a), "f"(b)); return r; }
+// tanh: odd polynomial x + x^3 Q(x^2) below 0.6 (least-squares fit, 1.2 ulp),
+// 1 - 2t/(1+t) with t = e^(-2|x|) above it
+DEV float fast_tanh(float x) {
+    const float ax = fabsf(x);
+    const float t = ex2_approx(ax * -2.885390082f);
+    float big = __fmaf_rn(t * -2.0f, rcp_approx(1.0f + t), 1.0f);
+    big = copysignf(big, x);
+    const float u = x * x;
+    float q = __fmaf_rn(u, -0.005895146634429693f, 0.02079596184194088f);
+    q = __fmaf_rn(q, u, -0.053783826529979706f);
+    q = __fmaf_rn(q, u, 0.13331924378871918f);
+    q = __fmaf_rn(q, u, -0.33333298563957214f);
+    const float small = __fmaf_rn(x * u, q, x);
+    return ax < 0.6f ? small : big;
+}
+
 // ------------------------------------------------------------------ random bits
 struct Rng { u32 k0, k1; };
 
-// 32 bits for element `idx`: one multiplicative hash of the counter, keyed per launch
-DEV u32 rng_bits(const Rng& g, u64 idx) {
-    u32 x = (u32)idx * 0x9E3779B1u + g.k0;
+// 32 random bits for a 64-bit counter: one multiplicative hash, keyed per launch
+DEV u32 rng_hash(const Rng& g, u32 lo, u32 hi) {
+    u32 x = lo * 0x9E3779B1u + g.k0;
     x ^= x >> 16; x *= 0x21F0AAADu;
     x ^= x >> 15; x *= 0x735A2D97u;
     x ^= x >> 15;
-    x ^= g.k1 + (u32)(idx >> 32) * 0x632BE5ABu;
+    x ^= g.k1 + hi * 0x632BE5ABu;
     return x;
+}
+DEV u32 rng_bits(const Rng& g, u64 idx) { return rng_hash(g, (u32)idx, (u32)(idx >> 32)); }
+// 16-bit float stores share one hash between elements 2q and 2q+1: the even one
+// reads it as is, the odd one with its halves swapped
+DEV u32 rng_bits_pair(const Rng& g, u64 idx) {
+    const u32 h = rng_bits(g, idx >> 1);
+    return (idx & 1) ? __funnelshift_l(h, h, 16) : h;
 }
 DEV float frand(const Rng& g, u64 idx) { return __uint2float_rn(rng_bits(g, idx)) * 2.3283064365386963e-10f; }
 
 // ------------------------------------------------------------------ rounding on store
-// Stochastic rounding to `mb` mantissa bits: add a uniform fraction of one
-// mb-bit ulp away from zero, truncate.  scale = 2^(-32-mb), mask = ~0 << (23-mb).
-struct SrCtx { float scale; u32 mask; };
-DEV SrCtx sr_ctx(int mb) { SrCtx c; c.scale = __uint_as_float((u32)(127 - 32 - mb) << 23); c.mask = 0xffffffffu << (23 - mb); return c; }
+// Stochastic rounding of an fp32 value to `mb` mantissa bits: add a uniform
+// fraction of one mb-bit ulp to the magnitude, truncate.  Done on the bit
+// pattern: the top (23-mb) bits of the random word are added below the kept
+// mantissa and the discarded bits cleared; a carry rounds the magnitude up with
+// probability equal to the discarded fraction.  (Same stored value as the
+// float formulation e = val & 0xff800000; e *= 2^(-32-mb); fma.rz(e, rz(urand),
+// val) & mask: only the carry out of the discarded bits matters, and that is
+// decided by the top 23-mb bits of urand.)
+struct SrCtx { u32 shift; u32 mask; };
+DEV SrCtx sr_ctx(int mb) { SrCtx c; c.shift = (u32)(9 + mb); c.mask = 0xffffffffu << (23 - mb); return c; }
 DEV float sr_f32(float v, u32 urand, const SrCtx& c) {
-    float e = __uint_as_float(__float_as_uint(v) & 0xff800000u) * c.scale;
-    float r = __fmaf_rz(e, __uint2float_rz(urand), v);
-    return __uint_as_float(__float_as_uint(r) & c.mask);
+    return __uint_as_float((__float_as_uint(v) + (urand >> c.shift)) & c.mask);
 }
 DEV float sr_int_pre(float v, u32 urand) {     // value to truncate for integer stores
     float fr = copysignf(__uint2float_rz(urand), v);
     fr = __fmul_rz(fr, 2.3283064365386963e-10f);
     return __fadd_rz(fr, v);
 }
+DEV u32 f2h2_rz(float lo, float hi) { u32 r; asm("cvt.rz.f16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo)); return r; }
+DEV u32 f2bf2_rz(float lo, float hi) { u32 r; asm("cvt.rz.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo)); return r; }
+DEV u32 f2bf_rz(float f) { u16 r; asm("cvt.rz.bf16.f32 %0, %1;" : "=h"(r) : "f"(f)); return r; }
 template <int DT> DEV u32 f2i_rn(float v) {
     if constexpr (DT == I32) { int r; asm("cvt.rni.sat.s32.f32 %0, %1;" : "=r"(r) : "f"(v)); return (u32)r; }
     else if constexpr (DT == U32) { u32 r; asm("cvt.rni.sat.u32.f32 %0, %1;" : "=r"(r) : "f"(v)); return r; }
@@ -206,7 +245,7 @@ template <int DT, int V, bool SR> DEV void cvt_out(const float* v, u32* w, const
             else {
 #pragma unroll
                 for (int i = 0; i < V / 2; ++i)
-                    w[i] = f2h_rz(sr_f32(v[2 * i], ur[2 * i], c)) | (f2h_rz(sr_f32(v[2 * i + 1], ur[2 * i + 1], c)) << 16);
+                    w[i] = f2h2_rz(sr_f32(v[2 * i], ur[2 * i], c), sr_f32(v[2 * i + 1], ur[2 * i + 1], c));
             }
         } else {
             if constexpr (V == 1) w[0] = f2h_rn(v[0]);
@@ -216,10 +255,19 @@ template <int DT, int V, bool SR> DEV void cvt_out(const float* v, u32* w, const
             }
         }
     } else if constexpr (DT == BF16) {
-        if constexpr (V == 1) w[0] = f2bf_rn(v[0]);
-        else {
+        if constexpr (SR) {
+            if constexpr (V == 1) w[0] = f2bf_rz(sr_f32(v[0], ur[0], c));
+            else {
 #pragma unroll
-            for (int i = 0; i < V / 2; ++i) w[i] = f2bf2_rn(v[2 * i], v[2 * i + 1]);
+                for (int i = 0; i < V / 2; ++i)
+                    w[i] = f2bf2_rz(sr_f32(v[2 * i], ur[2 * i], c), sr_f32(v[2 * i + 1], ur[2 * i + 1], c));
+            }
+        } else {
+            if constexpr (V == 1) w[0] = f2bf_rn(v[0]);
+            else {
+#pragma unroll
+                for (int i = 0; i < V / 2; ++i) w[i] = f2bf2_rn(v[2 * i], v[2 * i + 1]);
+            }
         }
     } else {
         constexpr bool SRI = SR && (DT == I32 || DT == I16 || DT == I8);   // unsigned: nearest only
@@ -236,6 +284,35 @@ template <int DT, int V, bool SR> DEV void cvt_out(const float* v, u32* w, const
     }
 }
 
+// Random words for the V lanes of a store whose lane i has element index idx0 + i*step.
+// PAIR: 16-bit float stores (two elements per hash).  ALIGNED: idx0 % V == 0 and
+// step == 1, so a vector never straddles a pair or a 2^32 boundary and the
+// 64-bit arithmetic is done once per vector instead of once per lane.
+template <int V, bool PAIR, bool ALIGNED> DEV void rng_lanes(const Rng& g, u64 idx0, i64 step, u32* ur) {
+    if constexpr (ALIGNED && V > 1) {
+        if constexpr (PAIR) {
+            const u64 q0 = idx0 >> 1;
+            const u32 lo = (u32)q0, hi = (u32)(q0 >> 32);
+#pragma unroll
+            for (int j = 0; j < V / 2; ++j) {
+                const u32 h = rng_hash(g, lo + j, hi);
+                ur[2 * j] = h;
+                ur[2 * j + 1] = __funnelshift_l(h, h, 16);
+            }
+        } else {
+            const u32 lo = (u32)idx0, hi = (u32)(idx0 >> 32);
+#pragma unroll
+            for (int i = 0; i < V; ++i) ur[i] = rng_hash(g, lo + i, hi);
+        }
+    } else {
+#pragma unroll
+        for (int i = 0; i < V; ++i) {
+            const u64 idx = idx0 + (u64)(i * step);
+            ur[i] = PAIR ? rng_bits_pair(g, idx) : rng_bits(g, idx);
+        }
+    }
+}
+
 template <int DT, int V, bool SR> DEV void st_f(u64 base, i64 off, const float* v, const SrCtx& c, const u32* ur) {
     constexpr int B = dt_size<DT>::value * V;
     u32 w[(B + 3) / 4];
@@ -243,7 +320,7 @@ template <int DT, int V, bool SR> DEV void st_f(u64 base, i64 off, const float* 
     st_raw<B>(reinterpret_cast<char*>(base) + off * dt_size<DT>::value, w);
 }
 template <int DT> DEV void st_one(u64 base, i64 off, float v) {
-    SrCtx c; c.scale = 0.f; c.mask = 0;
+    SrCtx c; c.shift = 0; c.mask = 0;
     st_f<DT, 1, false>(base, off, &v, c, nullptr);
 }
 // arg-reduction index straight into an integer tensor (float_ew.py:451-454)

@@ -63,6 +63,17 @@ BINARY_C = {
     "gt": "(({0} > {1}) ? 1.0f : 0.0f)", "ge": "(({0} >= {1}) ? 1.0f : 0.0f)",
     "minimum": "fminf({0}, {1})", "maximum": "fmaxf({0}, {1})", "pow": "powf({0}, {1})",
 }
+# cheaper versions (a few ulp, see csrc/optree_templates.cuh) used unless precise math is asked for
+UNARY_FAST = dict(UNARY_C)
+UNARY_FAST.update({
+    "sqrt": "fast_sqrt({0})",
+    "tanh": "fast_tanh({0})",
+    "sig": "rcp_approx(1.0f + expf(-{0}))",
+    "sig2": "rcp_approx(1.0f + exp2f(-{0}))",
+    "tanh2": "fast_div(exp2f(2.0f * {0}) - 1.0f, exp2f(2.0f * {0}) + 1.0f)",
+})
+BINARY_FAST = dict(BINARY_C)
+BINARY_FAST.update({"div": "fast_div({0}, {1})"})
 # the same ops on host fp32 scalars, for folding constant-only sub-trees
 _f = np.float32
 UNARY_HOST = {
@@ -405,9 +416,11 @@ class Planner(object):
     sizes the grids.
     """
 
-    def __init__(self, sm_count=148, target_blocks_per_sm=8):
+    def __init__(self, sm_count=148, target_blocks_per_sm=8, precise_math=False):
         self.sm_count = sm_count
         self.target = sm_count * target_blocks_per_sm
+        self.unary = UNARY_C if precise_math else UNARY_FAST
+        self.binary = BINARY_C if precise_math else BINARY_FAST
 
     # ---- helpers on the frame: K = kept axis, N = loop axis
     def plan(self, st, scratch, rounding=0, rng_key=None, lin=None):
@@ -461,7 +474,8 @@ class Planner(object):
     class _Emit(object):
         """Collects code for one pass in a given orientation."""
 
-        def __init__(self, st, fields, ka, ra, lanes_on_k, res_buf, avail_level):
+        def __init__(self, st, fields, ka, ra, lanes_on_k, res_buf, avail_level, tables):
+            self.unary, self.binary = tables
             self.st = st
             self.f = fields
             self.ka, self.ra = ka, ra
@@ -540,7 +554,7 @@ class Planner(object):
                 return ref
             # computed K-only node
             args = [self.hoist(a) for a in n.args]
-            expr = (UNARY_C[n.op] if n.kind == "u" else BINARY_C[n.op]).format(*args)
+            expr = (self.unary[n.op] if n.kind == "u" else self.binary[n.op]).format(*args)
             if self.lk:
                 self.h_lines.append("float %s[V];\n        _Pragma(\"unroll\") for (int i = 0; i < V; ++i) %s[i] = %s;"
                                     % (name, name, expr))
@@ -600,7 +614,7 @@ class Planner(object):
                 self.names[key] = ref
                 return ref
             args = [self.elem(a) for a in n.args]
-            expr = (UNARY_C[n.op] if n.kind == "u" else BINARY_C[n.op]).format(*args)
+            expr = (self.unary[n.op] if n.kind == "u" else self.binary[n.op]).format(*args)
             name = "x%d" % n.nid
             self.e_lines.append("const float %s = %s;" % (name, expr))
             self.names[key] = name
@@ -687,14 +701,14 @@ class Planner(object):
             return True
         lanes_on_k = (not lanes_ok("n")) and lanes_ok("k") and K > 1
         f = _Fields()
-        em = self._Emit(st, f, ka, ra, lanes_on_k, res_buf, reds[0].level - 1)
+        em = self._Emit(st, f, ka, ra, lanes_on_k, res_buf, reds[0].level - 1, (self.unary, self.binary))
         outs = []
         for r in reds:
             outs.append(em.elem(r.args[0]))
         eval_tail = ["out[%d][i] = %s;" % (i, e) for i, e in enumerate(outs)]
 
         # epilogue: raw results to scratch, or the root expression into the output
-        ep = self._Emit(st, f, ka, ra, False, res_buf, reds[0].level - 1)
+        ep = self._Emit(st, f, ka, ra, False, res_buf, reds[0].level - 1, (self.unary, self.binary))
         ep_lines = []
         fresh = {r.nid: i for i, r in enumerate(reds)}
         if final:
@@ -783,7 +797,7 @@ class Planner(object):
         for ka, ra in ((0, 1), (1, 0)):
             self._frame(st, ka, ra)
             f = _Fields()
-            em = self._Emit(st, f, ka, ra, False, res_buf, 1 << 30)
+            em = self._Emit(st, f, ka, ra, False, res_buf, 1 << 30, (self.unary, self.binary))
             val = em.elem(st.root)
             K, N = st.out_shape[ka], st.out_shape[ra]
             V = self._pick_v(em.lane_ops, N, not st.flat, extra=[(st.out, "n")])
@@ -809,12 +823,19 @@ class Planner(object):
             f.u32("rk0", 0)
             f.u32("rk1", 0)
             f.i32("sr_mb", int(rounding))
-            lin = em.lin_index()
+            em.lin_index()
+            # element index of lane i = idx0 + i*step; row-major index of the output tensor
+            ncols = 0 if st.flat else st.out_shape[1]
+            step = "p.lin_c" if ra == 1 else "p.lin_r"
+            row, col = ("k", "n") if ka == 0 else ("n", "k")
+            pair = "true" if odt in (DT_CODES["f2"], DT_CODES["bf2"]) else "false"
+            aligned = "true" if (ra == 1 and (st.flat or ncols % V == 0)) else "false"
             st_lines.append("const SrCtx c = sr_ctx(p.sr_mb); const Rng g{p.rk0, p.rk1}; u32 ur[V];")
-            st_lines.append("_Pragma(\"unroll\") for (int i = 0; i < V; ++i) ur[i] = rng_bits(g, %s);" % lin)
+            st_lines.append("rng_lanes<V, %s, %s>(g, (u64)(p.lin_0 + %s * p.lin_r + %s * p.lin_c), %s, ur);"
+                            % (pair, aligned, row, col, step))
             st_lines.append("st_f<%s, V, true>(p.o, k * p.o_sk + n * p.o_sn, v, c, ur);" % DT_NAMES[odt])
         else:
-            st_lines.append("SrCtx c; c.scale = 0.f; c.mask = 0;")
+            st_lines.append("SrCtx c; c.shift = 0; c.mask = 0;")
             st_lines.append("st_f<%s, V, false>(p.o, k * p.o_sk + n * p.o_sn, v, c, nullptr);" % DT_NAMES[odt])
         total = nvec if st.flat else K * nvec
         unroll = 4 if total >= self.target * BLOCK * 4 else (2 if total >= self.target * BLOCK else 1)

@@ -23,8 +23,12 @@ with numpy integer / float64 arithmetic, exactly what that text computes:
 The random words themselves do NOT follow the reference: its 3-LFSR pool is
 indexed by launch geometry (cuda_templates.py:138-173) and races when more than
 65536 threads run.  The CUDA backend uses a counter-based generator keyed by
-(seed, launch number, element index) instead; ``rng_bits`` is the same
-generator in numpy so that stored values can be compared bit for bit.
+(seed, launch number, element index) instead; ``rng_bits`` (and ``rng_bits_pair``
+for 16-bit float stores) is the same generator in numpy so that stored values
+can be compared bit for bit.  The kernels apply the rounding rule on the bit
+pattern (integer add of the top random bits, mask) rather than with fma.rz;
+``sr_f32`` below keeps the reference's float formulation, and the bit-exact GPU
+test shows the two agree.
 
 Parity status: pinned by known answers in tests/test_sround.py, among them the
 case of neon's tests/test_backend_sr.py:52-71 (1.1 at one mantissa bit gives
@@ -67,6 +71,15 @@ def rng_bits(key0, key1, idx):
     x ^= x >> np.uint64(15)
     x ^= (np.uint64(key1) + hi * np.uint64(0x632BE5AB)) & m
     return x.astype(U32)
+
+
+def rng_bits_pair(key0, key1, idx):
+    """Random word of element ``idx`` of a 16-bit float store: elements 2q and 2q+1
+    share the hash of q, the odd one with its 16-bit halves swapped."""
+    idx = np.asarray(idx, dtype=np.uint64)
+    h = rng_bits(key0, key1, idx >> np.uint64(1))
+    swapped = ((h << U32(16)) | (h >> U32(16))).astype(U32)
+    return np.where((idx & np.uint64(1)).astype(bool), swapped, h).astype(U32)
 
 
 def frand(bits):

@@ -118,7 +118,7 @@ def test_stochastic_rounding_bit_exact_against_restated_rule(b200):
         z[:] = 0.5 * x + y
         val = (np.float32(0.5) * xh.astype(np.float32) + yh.astype(np.float32)).astype(np.float32)
         key = sround.launch_key(int(seed), int(launch))
-        ur = sround.rng_bits(key[0], key[1], np.arange(val.size, dtype=np.uint64)).reshape(shape)
+        ur = sround.rng_bits_pair(key[0], key[1], np.arange(val.size, dtype=np.uint64)).reshape(shape)
         want = sround.store(val, np.float16, bits, ur)
         got = z.get()
         assert np.array_equal(got.view(np.uint16), want.view(np.uint16)), bits
@@ -130,6 +130,55 @@ def test_stochastic_rounding_bit_exact_against_restated_rule(b200):
     key = sround.launch_key(int(seed), int(launch))
     ur = sround.rng_bits(key[0], key[1], np.arange(val.size, dtype=np.uint64)).reshape(shape)
     assert np.array_equal(zf.get().view(np.uint32), sround.store(val, np.float32, 12, ur).view(np.uint32))
+
+
+def test_stochastic_rounding_odd_width_uses_same_random_words(b200):
+    """A tensor whose row length is odd takes the per-lane path of the kernels; the
+    stored values must still be the restated rule on the words of the element indices."""
+    be = b200
+    rng = np.random.RandomState(12)
+    shape = (37, 333)
+    xh = rng.uniform(-4, 4, shape).astype(np.float16)
+    x = be.array(xh, dtype=np.float16)
+    c = be.array(rng.uniform(-1, 1, (shape[0], 1)).astype(np.float16).astype(np.float32))
+    z = be.empty(shape, dtype=np.float16)
+    z.rounding = True
+    seed, launch = be.rng_get_state()[1]
+    z[:] = 0.25 * x + c                       # broadcast operand: the 2-d kernel, exact in fp32
+    val = (np.float32(0.25) * xh.astype(np.float32) + c.get()).astype(np.float32)
+    key = sround.launch_key(int(seed), int(launch))
+    ur = sround.rng_bits_pair(key[0], key[1], np.arange(val.size, dtype=np.uint64)).reshape(shape)
+    assert np.array_equal(z.get().view(np.uint16), sround.store(val, np.float16, True, ur).view(np.uint16))
+
+
+def test_precise_math_mode_matches_checker():
+    """IEEE division / libm tanh, sqrt instead of the few-ulp fast versions."""
+    from neon_b200.backend import B200Backend
+    be = B200Backend(rng_seed=0, precise_math=True)
+    for case in (cases.cfg5(128, 192), cases.cfg4(32, 4096), cases.cfg2(2000, 96), cases.adam_small(),
+                 cases.unary_case("tanh"), cases.unary_case("sig"), cases.binary_case("div")):
+        got = cases.run_case(be, case)
+        _compare(case, got, _oracle64(case))
+
+
+def test_fast_math_stays_within_a_few_ulp(b200):
+    be = b200
+    xs = np.concatenate([np.linspace(-9, 9, 200001), np.linspace(-0.7, 0.7, 100001),
+                         np.array([0.0, 1e-6, -1e-6, 1e-20, 30.0, -30.0, 88.0])]).astype(np.float32)
+    xs = xs[: (xs.size // 8) * 8].reshape(8, -1)
+    x = be.array(xs)
+    out = be.empty(xs.shape)
+    out[:] = be.tanh(x)
+    ref = np.tanh(xs.astype(np.float64))
+    err = np.abs(out.get().astype(np.float64) - ref) / np.maximum(np.spacing(np.abs(ref).astype(np.float32)), 1e-45)
+    assert err.max() <= 4.0, err.max()
+    pos = np.abs(xs) + np.float32(1e-3)
+    out[:] = be.sqrt(be.array(pos))
+    ref = np.sqrt(pos.astype(np.float64))
+    assert (np.abs(out.get() - ref) / np.spacing(ref.astype(np.float32))).max() <= 2.0
+    out[:] = x / be.array(pos)
+    ref = xs.astype(np.float64) / pos.astype(np.float64)
+    assert (np.abs(out.get() - ref) / np.maximum(np.spacing(np.abs(ref).astype(np.float32)), 1e-45)).max() <= 3.0
 
 
 def test_stochastic_rounding_one_bit_distribution(b200):
