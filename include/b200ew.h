@@ -161,6 +161,27 @@ uint64_t    b200_reduce_scratch_bytes(void);
 b200_status b200_reduce_full(uint64_t in, int32_t dtype, uint64_t count, int32_t op, int32_t absolute,
                              uint64_t out, uint64_t scratch, uint64_t stream);
 
+/* ---- the same reduction for callers that cannot allocate device memory
+ * No counterpart in the reference.  Meant for hosts where cudaMalloc is off
+ * limits when the call is made (a framework pool owns the device, a latency-
+ * critical loop, memory already handed out): the split-reduction scratch is a
+ * fixed 16640-byte array inside the library image, resident on every GPU that
+ * loads the library until the process exits.  The call allocates nothing and
+ * takes no scratch argument; inputs and the 4-byte fp32 output are the
+ * caller's.  Limits and rules:
+ *   - count <= B200_NOALLOC_MAX_COUNT, larger inputs are refused with
+ *     B200_ERR_INVALID (use b200_reduce_full with your own scratch);
+ *   - the first call on a device looks up the array's device address (the
+ *     device must be current); make that call before starting a stream capture;
+ *   - all calls on a device share the one array: calls that can overlap on the
+ *     GPU (different streams, no ordering between them) race and give wrong
+ *     results; order them on one stream or with events;
+ *   - stream 0 means the library's stream after b200_init, else the default stream. */
+#define B200_NOALLOC_MAX_COUNT (1ull << 32)
+uint64_t    b200_reduce_full_noalloc_max_count(void);
+b200_status b200_reduce_full_noalloc(uint64_t in, int32_t dtype, uint64_t count, int32_t op, int32_t absolute,
+                                     uint64_t out, uint64_t stream);
+
 /* ---- collectives over NVLink (NCCL, loaded at run time)
  * no counterpart in the reference tree: its multi-GPU backend was a closed
  * package (neon/backends/__init__.py:42-46).  Used to finish reductions that

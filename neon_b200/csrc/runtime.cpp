@@ -148,6 +148,10 @@ extern "C" int b200_detail_fill(void *dst, uint32_t value, int width, uint64_t c
 extern "C" int b200_detail_reduce_full(uint64_t in, int32_t dtype, uint64_t count, int32_t op, int32_t absolute,
                                        uint64_t out, uint64_t scratch, int sm_count, void *stream);
 
+// helpers for the other translation units of the library
+extern "C" void *b200_detail_stream(uint64_t stream) { return stream ? reinterpret_cast<void *>(stream) : g.stream; }
+extern "C" int32_t b200_detail_fail(int32_t code, const char *message) { return fail(code, "%s", message); }
+
 extern "C" {
 
 int32_t b200_version(void) { return 100; }

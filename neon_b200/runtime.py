@@ -71,6 +71,8 @@ SIGNATURES = {
     "b200_rng_set_state": (i32, [P(u64)]),
     "b200_reduce_scratch_bytes": (u64, []),
     "b200_reduce_full": (i32, [u64, i32, u64, i32, i32, u64, u64, u64]),
+    "b200_reduce_full_noalloc_max_count": (u64, []),
+    "b200_reduce_full_noalloc": (i32, [u64, i32, u64, i32, i32, u64, u64]),
     "b200_comm_unique_id": (i32, [P(C.c_uint8)]),
     "b200_comm_init": (i32, [P(C.c_uint8), i32, i32, P(u64)]),
     "b200_comm_destroy": (i32, [u64]),
@@ -294,6 +296,11 @@ def reduce_scratch_bytes():
 
 def reduce_full(src, dtype, count, op, absolute, out, scratch, stream=0):
     check(lib().b200_reduce_full(src, dtype, count, op, 1 if absolute else 0, out, scratch, stream))
+
+
+def reduce_full_noalloc(src, dtype, count, op, absolute, out, stream=0):
+    """Whole-tensor reduction that allocates nothing (scratch is a static device array)."""
+    check(lib().b200_reduce_full_noalloc(src, dtype, count, op, 1 if absolute else 0, out, stream))
 
 
 def comm_unique_id():
