@@ -282,17 +282,20 @@ class B200Backend(OpTreeBackend):
         self._scratch.reset()
         passes = self._planner.plan(st, self._scratch, rounding=rounding)
         for pz in passes:
-            kernel = self._kernels.get(pz.source)
-            if kernel is None:
-                kernel = self._kernels[pz.source] = rt.kernel_get(pz.source, pz.name)
-            if pz.uses_rng:
-                k0, k1 = rt.rng_next_key()
-                pz.fields.values["rk0"] = k0
-                pz.fields.values["rk1"] = k1
-            rt.launch(kernel, pz.grid, pz.block, pz.fields.pack(), stream=self.stream)
-            self.launches += 1
-            if self.launch_log is not None:
-                self.launch_log.append((pz.kind, pz.desc))
+            self._launch(pz)
+
+    def _launch(self, pz):
+        kernel = self._kernels.get(pz.source)
+        if kernel is None:
+            kernel = self._kernels[pz.source] = rt.kernel_get(pz.source, pz.name)
+        if pz.uses_rng:
+            k0, k1 = rt.rng_next_key()
+            pz.fields.values["rk0"] = k0
+            pz.fields.values["rk1"] = k1
+        rt.launch(kernel, pz.grid, pz.block, pz.fields.pack(), stream=self.stream)
+        self.launches += 1
+        if self.launch_log is not None:
+            self.launch_log.append((pz.kind, pz.desc))
 
     def _rounding_bits(self, out):
         """Mantissa bits for a stochastic store, 0 for nearest (float_ew.py:827-844)."""

@@ -156,7 +156,7 @@ def _fast_flat_ok(t, out_shape):
 class Statement(object):
     """The DAG of one assignment plus everything ``plan`` needs to lower it."""
 
-    def __init__(self, stack):
+    def __init__(self, stack, allow_flat=True):
         self.nodes = []
         self._memo = {}
         self.operands = []          # Operand list (inputs)
@@ -191,7 +191,7 @@ class Statement(object):
                         flat_ok = False
         self.axis = 1 if axis is None else axis
         self.has_red = has_red
-        self.flat = flat_ok and not has_red
+        self.flat = flat_ok and not has_red and allow_flat
         if not self.flat:
             for s in stack:
                 if isinstance(s, Tensor) and len(s.shape) != 2:
@@ -395,11 +395,12 @@ class _Fields(object):
 class Pass(object):
     """One kernel launch of a statement."""
     __slots__ = ("source", "name", "grid", "block", "fields", "kernel", "uses_rng", "desc",
-                 "bytes_moved", "result_slots", "kind")
+                 "results", "kind")
 
     def __init__(self):
         self.kernel = None
         self.uses_rng = False
+        self.results = []      # (reduction op, fp32 result address, int32 index address or 0, count)
 
 
 def _pow2ceil(x):
@@ -423,8 +424,13 @@ class Planner(object):
         self.binary = BINARY_C if precise_math else BINARY_FAST
 
     # ---- helpers on the frame: K = kept axis, N = loop axis
-    def plan(self, st, scratch, rounding=0, rng_key=None, lin=None):
-        """Return the list of Pass objects for Statement ``st``."""
+    def plan(self, st, scratch, rounding=0, fuse_final=True, lin=None):
+        """Return the list of Pass objects for Statement ``st``.  ``fuse_final=False``
+        keeps every reduction result in scratch (for a caller that combines results
+        of several devices between passes); ``lin=(ncols, col0)`` makes element
+        indices for random numbers those of a wider tensor this one is a column
+        slice of."""
+        self._lin = lin
         ra = st.axis                # reduced / loop axis in tensor coordinates
         ka = 1 - ra
         reds = [n for n in st.nodes if n.kind == "r" and self._reachable(st, n)]
@@ -436,13 +442,16 @@ class Planner(object):
         out_is_k = st.out_shape[ra] == 1
         for li, lv in enumerate(levels):
             rs = [n for n in reds if n.level == lv]
-            final = (lv == levels[-1]) and root_is_k and out_is_k and st.root.level == lv
+            final = fuse_final and (lv == levels[-1]) and root_is_k and out_is_k and st.root.level == lv
             K = full_shape[ka]
             if not final:
                 for r in rs:
                     res_buf[r.nid] = (scratch(4 * K, False),
                                       scratch(4 * K, False) if r.op.startswith("arg") else 0)
-            passes.append(self._reduction_pass(st, rs, res_buf, ka, ra, full_shape, scratch, final))
+            pz = self._reduction_pass(st, rs, res_buf, ka, ra, full_shape, scratch, final)
+            if not final:
+                pz.results = [(r.op,) + res_buf[r.nid] + (K,) for r in rs]
+            passes.append(pz)
             if final:
                 return passes
         passes.append(self._ew_pass(st, res_buf, ka, ra, rounding))
@@ -826,6 +835,8 @@ class Planner(object):
             em.lin_index()
             # element index of lane i = idx0 + i*step; row-major index of the output tensor
             ncols = 0 if st.flat else st.out_shape[1]
+            if self._lin is not None:
+                ncols = self._lin[0] if self._lin[1] % V == 0 else 1      # 1: never aligned
             step = "p.lin_c" if ra == 1 else "p.lin_r"
             row, col = ("k", "n") if ka == 0 else ("n", "k")
             pair = "true" if odt in (DT_CODES["f2"], DT_CODES["bf2"]) else "false"
@@ -852,6 +863,8 @@ class Planner(object):
             # linear element index = row * ncols + col of the output tensor
             f.values["lin_r"] = st.out_shape[1] if not st.flat else 0
             f.values["lin_c"] = 1
+            if self._lin is not None:
+                f.values["lin_r"], f.values["lin_0"] = self._lin
         return pz
 
     @staticmethod

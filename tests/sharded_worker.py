@@ -1,0 +1,77 @@
+"""One rank of the multi-GPU parity run (started by tests/test_sharded_gpu.py through
+torch.distributed.run).  Compares column-sharded execution with the float64 checker
+on the global arrays and with unsharded execution on the same device."""
+import os
+import sys
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+sys.path.insert(0, ROOT)
+
+
+def main():
+    from neon_b200.sharded import gen_sharded_backend
+    from oracle.numpy_backend import OracleBackend
+    from tests.parity import check_output
+    rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+    be = gen_sharded_backend(rank, world, device_id=int(os.environ.get("LOCAL_RANK", rank)), rng_seed=0)
+    ob = OracleBackend(default_dtype=np.float64)
+    rng = np.random.RandomState(0)
+
+    # ---- batch-norm statistics + normalise (config 4 shape class), columns sharded
+    rows, cols = 64, 8192 * world
+    xh = (1.0 + 2.0 * rng.randn(rows, cols)).astype(np.float16)
+    gh = rng.uniform(0.5, 1.5, (rows, 1)).astype(np.float32)
+    bh = rng.uniform(0.5, 1.5, (rows, 1)).astype(np.float32)
+    x = be.array(xh, dtype=np.float16, parallel=True)
+    y = be.empty((rows, cols), dtype=np.float16, parallel=True)
+    g, b = be.array(gh), be.array(bh)
+    before = be.collectives
+    y[:] = (x - be.mean(x, axis=1)) / be.sqrt(be.var(x, axis=1) + 1e-5) * g + b
+    assert be.collectives - before == 2
+    ox, og, obt = ob.array(xh, dtype=np.float64), ob.array(gh, dtype=np.float64), ob.array(bh, dtype=np.float64)
+    oy = ob.zeros((rows, cols), dtype=np.float64)
+    oy[:] = (ox - ob.mean(ox, axis=1)) / ob.sqrt(ob.var(ox, axis=1) + 1e-5) * og + obt
+    check_output("sharded batchnorm y", y.get(), oy.get(), np.float16)
+    mean = be.empty((rows, 1))
+    mean[:] = be.mean(x, axis=1)
+    check_output("sharded mean", mean.get(), xh.astype(np.float64).mean(axis=1, keepdims=True), np.float32)
+    mx = be.empty((rows, 1))
+    mx[:] = be.max(x, axis=1) - be.min(x, axis=1)
+    x64 = xh.astype(np.float64)
+    check_output("sharded max-min", mx.get(), x64.max(1, keepdims=True) - x64.min(1, keepdims=True), np.float32)
+    s0 = be.empty((1, cols), parallel=True)
+    s0[:] = be.sum(x, axis=0)
+    check_output("sharded axis-0 sum", s0.get(), x64.sum(0, keepdims=True), np.float32)
+
+    # ---- fp16 chain with stochastic rounding + whole-tensor reductions (config 5 shape class)
+    rows, cols = 256, 1024 * world
+    xh = rng.uniform(-4, 4, (rows, cols)).astype(np.float16)
+    yh = rng.uniform(-4, 4, (rows, cols)).astype(np.float16)
+    xs, ys = be.array(xh, dtype=np.float16, parallel=True), be.array(yh, dtype=np.float16, parallel=True)
+    zs = be.empty((rows, cols), dtype=np.float16, parallel=True)
+    zs.rounding = True
+    total, peak = be.empty((1, 1)), be.empty((1, 1))
+    be.rng_reset()
+    zs[:] = be.tanh(xs) * be.sqrt(be.absolute(ys)) + 0.5 * xs * ys
+    total[:] = be.sum(zs)
+    peak[:] = be.max(be.absolute(zs))
+    z_sharded = zs.get()
+    # the same statements unsharded on this device, same generator state: identical bits
+    xf, yf = be.array(xh, dtype=np.float16), be.array(yh, dtype=np.float16)
+    zf = be.empty((rows, cols), dtype=np.float16)
+    zf.rounding = True
+    be.rng_reset()
+    zf[:] = be.tanh(xf) * be.sqrt(be.absolute(yf)) + 0.5 * xf * yf
+    assert np.array_equal(z_sharded.view(np.uint16), zf.get().view(np.uint16)), "rounding depends on sharding"
+    z64 = z_sharded.astype(np.float64)
+    check_output("sharded total", total.get(), np.array([[z64.sum()]]), np.float32, scale=float(np.abs(z64).sum()))
+    assert float(peak.get()[0, 0]) == float(np.abs(z_sharded).max())
+    be.host_barrier()
+    if rank == 0:
+        print("SHARDED-OK world=%d collectives=%d" % (world, be.collectives))
+
+
+if __name__ == "__main__":
+    main()

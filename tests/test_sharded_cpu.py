@@ -1,0 +1,131 @@
+"""
+CPU tests of the multi-GPU layer's host logic with two gloo ranks: the
+rendezvous that distributes the communicator id, the column partition, and the
+collective schedule each rank derives for sharded statements (un-fused final
+pass, one all-reduce per cross-shard reduction, global element indices for the
+random words).  Devices and NCCL are replaced by recording stand-ins.
+"""
+import os
+import socket
+
+import numpy as np
+import pytest
+import torch.multiprocessing as mp
+
+
+def _free_port():
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    port = s.getsockname()[1]
+    s.close()
+    return port
+
+
+def _worker(rank, world, port, out):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    import torch.distributed as dist
+    from neon_b200 import sharded
+    from neon_b200.sharded import ShardedBackend, ShardedTensor, bootstrap, shard_columns
+    from tests.dryrun import DryRunBackend, DryTensor
+
+    joined = {}
+    comm, barrier, host_max = bootstrap(rank, world, make_id=lambda: b"id-from-rank-0" + bytes(114),
+                                        init_comm=lambda uid, n, r: joined.setdefault("uid", uid) and 77)
+    assert joined["uid"].startswith(b"id-from-rank-0") and comm == 77
+    assert host_max(float(rank)) == float(world - 1)
+    barrier()
+
+    class DrySharded(ShardedBackend, DryRunBackend):
+        def __init__(self):
+            DryRunBackend.__init__(self)
+            self.compile = False
+            self.rank, self.world_size, self.comm = rank, world, comm
+            self.collectives = 0
+            self.calls = []
+            self.plans = []
+
+        def empty(self, shape, dtype=None, name=None, persist_values=True, parallel=False, **kw):
+            return self._make(lambda s, dtype=None, name=None: DryRunBackend.empty(self, s, dtype=dtype, name=name),
+                              shape, dtype, name, parallel)
+        zeros = ones = empty
+
+        class _Scr(object):
+            def __init__(self, be):
+                self.be = be
+
+            def reset(self):
+                pass
+
+            def __call__(self, n, zero):
+                return self.be._fake(n)
+
+        def _launch(self, pz):
+            pz.fields.pack()
+            self.plans.append(pz)
+
+        def _allreduce(self, addr, count, op):
+            self.calls.append((int(op), int(count)))
+            self.collectives += 1
+
+    be = DrySharded()
+    be._scratch = DrySharded._Scr(be)
+    rows, cols = 64, 4096
+    c0, c1 = shard_columns(cols, world, rank)
+    assert (c0, c1) == (rank * cols // world, (rank + 1) * cols // world)
+
+    # batch-norm statement: two cross-shard reductions, then a shard-local element-wise pass
+    x = be.empty((rows, cols), np.float16, parallel=True)
+    y = be.empty((rows, cols), np.float16, parallel=True)
+    gamma, beta = be.empty((rows, 1)), be.empty((rows, 1))
+    assert isinstance(x, ShardedTensor) and x.shape == (rows, cols) and x.local.shape == (rows, cols // world)
+    y[:] = (x - be.mean(x, axis=1)) / be.sqrt(be.var(x, axis=1) + 1e-5) * gamma + beta
+    kinds = [p.kind for p in be.plans]
+    assert kinds == ["red_rows", "red_rows", "ew_2d"], kinds
+    assert be.calls == [(0, rows), (0, rows)]
+    # mean used the global column count
+    consts = [v for p in be.plans for k, v in p.fields.values.items() if k.startswith("c")]
+    assert any(abs(v - 1.0 / cols) < 1e-12 for v in consts)
+
+    # replicated (rows,1) output of a cross-shard reduction: no fused final pass
+    be.plans, be.calls = [], []
+    m = be.empty((rows, 1))
+    m[:] = be.max(x, axis=1)
+    assert [p.kind for p in be.plans] == ["red_rows", "ew_2d"] and be.calls == [(1, rows)]
+
+    # axis-0 reductions and element-wise work stay local
+    be.plans, be.calls = [], []
+    s0 = be.empty((1, cols), parallel=True)
+    s0[:] = be.sum(x, axis=0)
+    y[:] = x * 2.0
+    assert be.calls == []
+
+    # whole-tensor reduction: flat local pass + one all-reduce; rounding uses global element indices
+    be.plans, be.calls = [], []
+    z = be.empty((rows, cols), np.float16, parallel=True)
+    z.rounding = True
+    z[:] = x * 0.5
+    total = be.empty((1, 1))
+    total[:] = be.sum(z)
+    ew = be.plans[0]
+    assert ew.kind == "ew_2d" and ew.fields.values["lin_r"] == cols and ew.fields.values["lin_0"] == c0
+    assert be.calls == [(0, 1)]
+    gathered = [None] * world
+    dist.all_gather_object(gathered, [(p.kind, p.grid) for p in be.plans] + be.calls)
+    assert all(g == gathered[0] for g in gathered)
+    out.put((rank, "ok"))
+
+
+@pytest.mark.timeout(180)
+def test_two_rank_host_logic_over_gloo():
+    world = 2
+    port = _free_port()
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    procs = [ctx.Process(target=_worker, args=(r, world, port, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(150)
+    assert all(p.exitcode == 0 for p in procs), [p.exitcode for p in procs]
+    got = sorted(q.get(timeout=5) for _ in range(world))
+    assert got == [(0, "ok"), (1, "ok")]
