@@ -166,6 +166,111 @@ def run_reference(args, rank, world):
     print(json.dumps(line))
 
 
+def other_workloads(name, be, world, rank):
+    """The remaining baseline configurations as (tensors, [(label, statement, algorithmic bytes)]).
+    Sizes per GPU; with world > 1 the column (batch) axis is sharded and grows with world."""
+    kw = {"parallel": True} if world > 1 else {}
+    rng = np.random.RandomState(7 + rank)
+    if name == "cfg1":
+        r, c = 4096, 128
+        a = be.array(rng.randn(r, c * world).astype(np.float32), **kw)
+        b = be.array(rng.randn(r, c * world).astype(np.float32), **kw)
+        bias = be.array(rng.uniform(-.5, .5, (r, 1)).astype(np.float32))
+        out = be.empty((r, c * world), **kw)
+        s = be.empty((1, c * world), **kw)
+        m = be.empty((1, c * world), dtype=np.int32, **kw)
+
+        def st_out(): out[:] = be.maximum(a * b + bias, 0)
+        def st_sum(): s[:] = be.sum(out, axis=0)
+        def st_arg(): m[:] = be.argmax(out, axis=0)
+        n = r * c
+        return [("bias+relu", st_out, 12 * n + 4 * r), ("sum axis0", st_sum, 4 * n + 4 * c),
+                ("argmax axis0", st_arg, 4 * n + 4 * c)], n
+    if name == "cfg2":
+        r, c = 32000, 256
+        x = be.array((3.0 * rng.randn(r, c * world)).astype(np.float32), **kw)
+        y = be.empty((r, c * world), **kw)
+        idx = be.empty((1, c * world), dtype=np.int32, **kw)
+
+        def st_y():
+            mx = be.max(x, axis=0)
+            e = be.exp(x - mx)
+            y[:] = e / be.sum(e, axis=0)
+        def st_idx(): idx[:] = be.argmax(x, axis=0)
+        n = r * c
+        return [("softmax axis0", st_y, 8 * n), ("argmax axis0", st_idx, 4 * n + 4 * c)], n
+    if name == "cfg3":
+        n = 100000000
+        shape = (100000, 1000 * world)
+        from tests.cases import adam_step
+        param = be.array((0.02 * rng.randn(*shape)).astype(np.float32), **kw)
+        grad = be.array((1e-3 * rng.randn(*shape)).astype(np.float16), dtype=np.float16, **kw)
+        mm, vv = be.zeros(shape, **kw), be.zeros(shape, **kw)
+        be.bsz = 1
+        step = [0]
+
+        def st_adam():
+            step[0] += 1
+            adam_step(be, param, grad, mm, vv, step[0])
+        return [("adam step (3 statements)", st_adam, 36 * n)], n
+    if name == "cfg4":
+        r, c = 256, 56 * 56 * 128
+        x = be.array((1.0 + 2.0 * rng.randn(r, c * world)).astype(np.float16), dtype=np.float16, **kw)
+        gamma = be.array(rng.uniform(.5, 1.5, (r, 1)).astype(np.float32))
+        beta = be.array(rng.uniform(.5, 1.5, (r, 1)).astype(np.float32))
+        y = be.empty((r, c * world), dtype=np.float16, **kw)
+
+        def st_bn():
+            y[:] = (x - be.mean(x, axis=1)) / be.sqrt(be.var(x, axis=1) + 1e-5) * gamma + beta
+        n = r * c
+        return [("batchnorm stats+normalise", st_bn, 4 * n + 2048)], n
+    raise SystemExit("unknown workload %s" % name)
+
+
+def run_other(args, be, rank, world, barrier, max_over_ranks):
+    stmts, n_local = other_workloads(args.workload, be, world, rank)
+    for _ in range(max(args.warmup, 3)):
+        for _, fn, _ in stmts:
+            fn()
+    be.synchronize()
+    marks = [[(be.init_mark(), be.init_mark()) for _ in stmts] for _ in range(args.steps)]
+    ev0, ev1 = be.init_mark(), be.init_mark()
+    be.launch_log = []
+    launches0 = be.launches
+    barrier()
+    be.synchronize()
+    be.record_mark(ev0)
+    for s in range(args.steps):
+        for i, (_, fn, _) in enumerate(stmts):
+            be.record_mark(marks[s][i][0])
+            fn()
+            be.record_mark(marks[s][i][1])
+    be.record_mark(ev1)
+    be.synchronize()
+    barrier()
+    ms_total = max_over_ranks(be.get_time(ev0, ev1))
+    if rank != 0:
+        return
+    per = []
+    for i, (label, _, nbytes) in enumerate(stmts):
+        ms = float(np.median([be.get_time(*marks[s][i]) for s in range(args.steps)]))
+        per.append({"statement": label, "ms": ms, "algorithmic_bytes": nbytes, "GBps": nbytes / ms / 1e6})
+    nbytes_step = sum(b for _, _, b in stmts) * world
+    ms_step = ms_total / args.steps
+    peak_gbs, peak_kind = measured_peak()
+    value = nbytes_step / ms_step / 1e6
+    kinds = be.launch_log[: (be.launches - launches0) // args.steps]
+    print(json.dumps({
+        "metric": METRIC, "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps,
+        "warmup": max(args.warmup, 3), "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": args.workload, "elements_per_gpu": n_local,
+                   "l2": "working set is L2-resident between steps" if n_local * 4 < 100e6 else "exceeds L2"},
+        "pct_of_measured_peak_per_gpu": 100.0 * value / world / peak_gbs, "peak_kind": peak_kind,
+        "statements": per, "gpu_launches": be.launches - launches0,
+        "launches_per_step": [k for k, _ in kinds]}))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -176,6 +281,7 @@ def main():
     ap.add_argument("--cols", type=int, default=COLS)
     ap.add_argument("--e2e-steps", type=int, default=3)
     ap.add_argument("--no-cpu", action="store_true")
+    ap.add_argument("--workload", default="cfg5", help="cfg5 (default, the reported metric) or cfg1..cfg4")
     args = ap.parse_args()
 
     rank = int(os.environ.get("RANK", "0"))
@@ -195,6 +301,9 @@ def main():
         from neon_b200 import gen_backend
         be = gen_backend(backend="b200", rng_seed=0, device_id=local_rank)
         barrier, max_over_ranks = (lambda: None), (lambda v: v)
+
+    if args.workload != "cfg5":
+        return run_other(args, be, rank, world, barrier, max_over_ranks)
 
     rows, cols = args.rows, args.cols
     n_local = rows * cols

@@ -12,7 +12,7 @@ lookup tables) raise ``NotImplementedError``.
 import numpy as np
 
 from . import runtime as rt
-from .lowering import Planner, Statement
+from .lowering import BoundPlan, Planner, Statement, program_key
 from .optree import OpCollection, OpTreeBackend, OpTreeNode, Tensor
 from .tensor import B200Tensor
 
@@ -85,6 +85,7 @@ class B200Backend(OpTreeBackend):
         self._scratch = _Scratch()
         self._planner = Planner(self.sm_count, precise_math=precise_math)
         self._kernels = {}
+        self._plans = {}                   # program_key -> BoundPlan
         self._temps = {}
         self._temps_used = {}
         self._marks = []
@@ -277,17 +278,25 @@ class B200Backend(OpTreeBackend):
     # -- one statement ------------------------------------------------------------
     def _run(self, out, expr):
         stack = OpTreeNode({"op": "assign"}, out, expr).traverse([])
-        st = Statement(stack)
         rounding = self._rounding_bits(out)
-        self._scratch.reset()
-        passes = self._planner.plan(st, self._scratch, rounding=rounding)
-        for pz in passes:
+        key = (program_key(stack), rounding)
+        plan = self._plans.get(key)
+        if plan is None:
+            st = Statement(stack)
+            self._scratch.reset()
+            plan = self._plans[key] = BoundPlan(st, self._planner.plan(st, self._scratch, rounding=rounding))
+        else:
+            plan.rebind(stack)
+        for pz in plan.passes:
             self._launch(pz)
 
     def _launch(self, pz):
-        kernel = self._kernels.get(pz.source)
+        kernel = pz.kernel
         if kernel is None:
-            kernel = self._kernels[pz.source] = rt.kernel_get(pz.source, pz.name)
+            kernel = self._kernels.get(pz.source)
+            if kernel is None:
+                kernel = self._kernels[pz.source] = rt.kernel_get(pz.source, pz.name)
+            pz.kernel = kernel
         if pz.uses_rng:
             k0, k1 = rt.rng_next_key()
             pz.fields.values["rk0"] = k0

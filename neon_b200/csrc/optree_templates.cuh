@@ -354,13 +354,18 @@ DEV void red_merge(int op, float& a, int& ai, float b, int bi) {
 }
 
 // ================================================================== element-wise
-// grid.x * BLOCK * UNROLL >= number of V-wide vectors (+ scalar tail in FLAT mode).
-template <template <int> class SV, class P, int V, int BLOCK, int UNROLL, bool FLAT>
+// MODE 0: 2-d, vector index -> (k, n) by division; grid.x * BLOCK * UNROLL >= K * nvec.
+// MODE 1: flat (K == 1, all operands contiguous), scalar tail of N % V elements.
+// MODE 2: 2-d with long rows: blockIdx.y/z select the row, blockIdx.x tiles it.
+template <template <int> class SV, class P, int V, int BLOCK, int UNROLL, int MODE>
 DEV void ew_kernel(const P& p) {
     typedef SV<V> S;
+    constexpr bool FLAT = MODE == 1;
     const i64 nvec = p.nvec;                     // vectors per row (FLAT: all vectors)
-    const i64 total = FLAT ? nvec : p.K * nvec;
+    const i64 total = MODE == 0 ? p.K * nvec : nvec;
     const i64 base = (i64)blockIdx.x * (BLOCK * UNROLL) + threadIdx.x;
+    const i64 krow = MODE == 2 ? (i64)blockIdx.y + (i64)blockIdx.z * gridDim.y : 0;
+    if (MODE == 2 && krow >= p.K) return;
     typename S::L l[UNROLL];
     typename S::H h[UNROLL];
     i64 kk[UNROLL], nn[UNROLL];
@@ -368,12 +373,12 @@ DEV void ew_kernel(const P& p) {
     for (int u = 0; u < UNROLL; ++u) {
         i64 g = base + (i64)u * BLOCK;
         if (g < total) {
-            if constexpr (FLAT) { kk[u] = 0; nn[u] = g * V; }
+            if constexpr (MODE != 0) { kk[u] = krow; nn[u] = g * V; }
             else if (nvec <= 0x7fffffffLL && g <= 0x7fffffffLL) {
                 u32 q = (u32)g / (u32)nvec; kk[u] = q; nn[u] = (i64)((u32)g - q * (u32)nvec) * V;
             } else { kk[u] = g / nvec; nn[u] = (g - kk[u] * nvec) * V; }
             S::load_l(p, kk[u], nn[u], l[u]);
-            S::load_h(p, kk[u], h[u]);
+            if (MODE != 2 || u == 0) S::load_h(p, kk[u], h[u]);
         }
     }
 #pragma unroll
@@ -381,7 +386,7 @@ DEV void ew_kernel(const P& p) {
         i64 g = base + (i64)u * BLOCK;
         if (g < total) {
             float out[1][V];
-            S::eval(p, h[u], l[u], kk[u], nn[u], out);
+            S::eval(p, MODE == 2 ? h[0] : h[u], l[u], kk[u], nn[u], out);
             S::store(p, kk[u], nn[u], out[0]);
         }
     }
@@ -653,11 +658,23 @@ DEV void red_cols_kernel(const P& p) {
 #pragma unroll
             for (int r = 0; r < NR; ++r) {
                 float b = red_init(S::op(r)); int bi = -1;
-                if (kc < p.K)
-                    for (int s = cy; s < p.split; s += CH) {
-                        const i64 o = (i64)r * p.K * p.split + (i64)s * p.K + kc;
-                        red_merge(S::op(r), b, bi, __ldcg(pv + o), red_is_arg(S::op(r)) ? __ldcg(pi + o) : -1);
+                if (kc < p.K) {
+                    const i64 o0 = (i64)r * p.K * p.split + kc;
+                    int s = cy;
+                    for (; s + 3 * CH < p.split; s += 4 * CH) {       // four loads in flight
+                        float v4[4]; int i4[4];
+#pragma unroll
+                        for (int q = 0; q < 4; ++q) {
+                            v4[q] = __ldcg(pv + o0 + (i64)(s + q * CH) * p.K);
+                            i4[q] = red_is_arg(S::op(r)) ? __ldcg(pi + o0 + (i64)(s + q * CH) * p.K) : -1;
+                        }
+#pragma unroll
+                        for (int q = 0; q < 4; ++q) red_merge(S::op(r), b, bi, v4[q], i4[q]);
                     }
+                    for (; s < p.split; s += CH)
+                        red_merge(S::op(r), b, bi, __ldcg(pv + o0 + (i64)s * p.K),
+                                  red_is_arg(S::op(r)) ? __ldcg(pi + o0 + (i64)s * p.K) : -1);
+                }
                 sv[r][cy % RH][cx] = b;
                 if (red_is_arg(S::op(r))) si[r][cy % RH][cx] = bi;
             }

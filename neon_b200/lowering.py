@@ -149,6 +149,78 @@ class _Pseudo(object):
         self.alias_out = True           # written by an earlier launch: plain loads
 
 
+def shares_memory(a, b):
+    """Conservative aliasing test: two tensors that live in the same allocation may
+    overlap, so reads of one must not use the read-only data path while the other
+    is written."""
+    ba, bb = getattr(a, "_block", None), getattr(b, "_block", None)
+    if ba is None or bb is None:
+        return a._original_base() is b._original_base()
+    return ba is bb
+
+
+def eval_recipe(recipe, stack):
+    kind = recipe[0]
+    if kind == "l":
+        return np.float32(float(stack[recipe[1]]))
+    if kind == "k":
+        return np.float32(recipe[1])
+    with np.errstate(all="ignore"):
+        if kind == "u":
+            return np.float32(UNARY_HOST[recipe[1]](eval_recipe(recipe[2], stack)))
+        return np.float32(BINARY_HOST[recipe[1]](eval_recipe(recipe[2], stack), eval_recipe(recipe[3], stack)))
+
+
+def program_key(stack):
+    """Hashable description of a postfix program with everything that shapes the
+    generated kernels and their geometry -- dtypes, shapes, strides, pointer
+    alignment, which operands are the same tensor or share the output's
+    allocation, ops and axes -- and nothing that is a run-time argument
+    (addresses, values of python numbers)."""
+    out = stack[0]
+    seen = {}
+    key = []
+    for s in stack:
+        if isinstance(s, Tensor):
+            ix = seen.setdefault(id(s), len(seen))
+            key.append((ix, s.dtype.char, s.shape, s.strides, s.ptr & 15, bool(s.take_array),
+                        s is not out and shares_memory(s, out)))
+        elif type(s) is dict:
+            idx = s.get("idx")
+            key.append((s["op"], s.get("axis"), None if idx is None else seen.setdefault(id(idx), len(seen))))
+        else:
+            key.append(None)
+    return tuple(key)
+
+
+class BoundPlan(object):
+    """Passes of a statement plus the recipe to re-aim them at new tensors and
+    numbers of a program with the same ``program_key``."""
+
+    def __init__(self, st, passes):
+        self.passes = passes
+        self.binds = []
+        for pz in passes:
+            ptrs, consts = [], []
+            for name in pz.fields.names():
+                if name == "o":
+                    ptrs.append((name, 0))
+                elif name[0] == "t" and name[1:].isdigit():
+                    ptrs.append((name, st.tensor_pos[int(name[1:])]))
+                elif name[0] == "c" and name[1:].isdigit():
+                    consts.append((name, st.nodes[int(name[1:])].extra))
+            self.binds.append((ptrs, consts))
+
+    def rebind(self, stack):
+        for pz, (ptrs, consts) in zip(self.passes, self.binds):
+            vals = pz.fields.values
+            for name, pos in ptrs:
+                obj = stack[pos]
+                vals[name] = (obj["idx"] if type(obj) is dict else obj).ptr
+            for name, recipe in consts:
+                vals[name] = float(eval_recipe(recipe, stack))
+
+
 def _fast_flat_ok(t, out_shape):
     return len(t.shape) >= 1 and tuple(t.shape) == tuple(out_shape) and t.is_contiguous and not t.take_array
 
@@ -205,15 +277,19 @@ class Statement(object):
         # ---- pass 2: postfix -> DAG with shape algebra (float_ew.py:713-906)
         st = []
         first = True
-        for s in stack:
+        self.tensor_pos = []        # operand index -> position in the program of its first use
+        for pos, s in enumerate(stack):
             if isinstance(s, Tensor):
                 if first:
                     first = False
                     st.append("OUT")
                     continue
+                known = len(self.operands)
                 st.append(self._tensor_node(s))
+                if len(self.operands) > known:
+                    self.tensor_pos.extend([pos] * (len(self.operands) - known))
             elif type(s) in (int, float) or isinstance(s, (np.floating, np.integer)):
-                st.append(self._const(float(s)))
+                st.append(self._const(float(s), ("l", pos)))
             elif type(s) is dict:
                 op = s["op"]
                 if op == "assign":
@@ -226,7 +302,10 @@ class Statement(object):
                 elif op in OpCollection.reduction_ops:
                     st.append(self._reduce(op, st.pop()))
                 elif op in ("rand", "onehot"):
+                    known = len(self.operands)
                     st.append(self._zero_op(s))
+                    if len(self.operands) > known:          # the index tensor of a one-hot
+                        self.tensor_pos.extend([pos] * (len(self.operands) - known))
                 elif op in UNARY_C:
                     st.append(self._unary(op, st.pop()))
                 elif op in BINARY_C:
@@ -240,7 +319,7 @@ class Statement(object):
         self.out = Operand(out, self.out_shape,
                            (0, 1) if self.flat else out.strides)
         for o in self.operands:
-            o.alias_out = not (o.span[1] <= self.out.span[0] or self.out.span[1] <= o.span[0])
+            o.alias_out = shares_memory(o.tensor, out)
 
     # -- node constructors (hash-consed)
     def _intern(self, key, make):
@@ -266,9 +345,12 @@ class Statement(object):
         shape = self.operands[ix].shape
         return self._intern(("t", ix), lambda: Node("t", tix=ix, shape=shape))
 
-    def _const(self, v):
+    def _const(self, v, recipe):
+        """Constant node.  ``recipe`` says how to recompute the value from the numbers
+        of a later program of the same structure: ("l", position), ("k", value),
+        ("u", op, recipe) or ("b", op, recipe, recipe)."""
         v = float(np.float32(v))
-        return self._intern(("c", v), lambda: Node("c", value=v))
+        return self._intern(("c", recipe), lambda: Node("c", value=v, extra=recipe))
 
     @staticmethod
     def _bshape(shapes):
@@ -285,14 +367,15 @@ class Statement(object):
     def _unary(self, op, a):
         if a.kind == "c":
             with np.errstate(all="ignore"):
-                return self._const(UNARY_HOST[op](np.float32(a.value)))
+                return self._const(UNARY_HOST[op](np.float32(a.value)), ("u", op, a.extra))
         return self._intern(("u", op, a.nid),
                             lambda: self._lvl(Node("u", op=op, args=(a,), shape=a.shape)))
 
     def _binary(self, op, a, b):
         if a.kind == "c" and b.kind == "c":
             with np.errstate(all="ignore"):
-                return self._const(BINARY_HOST[op](np.float32(a.value), np.float32(b.value)))
+                return self._const(BINARY_HOST[op](np.float32(a.value), np.float32(b.value)),
+                                   ("b", op, a.extra, b.extra))
         shape = self._bshape((b.shape, a.shape))
         return self._intern(("b", op, a.nid, b.nid),
                             lambda: self._lvl(Node("b", op=op, args=(a, b), shape=shape)))
@@ -301,7 +384,7 @@ class Statement(object):
         ax = self.axis
         if a.shape[ax] == 1:
             # reducing an extent of one: the value itself, or index 0
-            return self._const(0.0) if op.startswith("arg") else a
+            return self._const(0.0, ("k", 0.0)) if op.startswith("arg") else a
         shape = list(a.shape)
         shape[ax] = 1
         shape = tuple(shape)
@@ -748,10 +831,14 @@ class Planner(object):
         pz = Pass()
         if lanes_on_k:
             V = self._pick_v(em.lane_ops, K, True)
-            CW = min(32, _pow2ceil((K + V - 1) // V))
+            # narrow tiles (8 lanes x V = one 128-byte line of fp32/fp16 per row) keep the
+            # number of tiles up and the number of slices per tile -- which the last
+            # block of a tile has to combine -- down
+            CW = min(8, _pow2ceil((K + V - 1) // V))
             RH = BLOCK // CW
             tiles = (K + CW * V - 1) // (CW * V)
-            split = max(1, min((self.target + tiles - 1) // tiles, (N + RH * 4 - 1) // (RH * 4)))
+            want = self.sm_count * 4
+            split = max(1, min((want + tiles - 1) // tiles, (N + RH * 4 - 1) // (RH * 4)))
             seg = (N + split - 1) // split
             split = (N + seg - 1) // seg
             grid = (tiles, split, 1)
@@ -850,8 +937,14 @@ class Planner(object):
             st_lines.append("st_f<%s, V, false>(p.o, k * p.o_sk + n * p.o_sn, v, c, nullptr);" % DT_NAMES[odt])
         total = nvec if st.flat else K * nvec
         unroll = 4 if total >= self.target * BLOCK * 4 else (2 if total >= self.target * BLOCK else 1)
-        grid = (max(1, (total + BLOCK * unroll - 1) // (BLOCK * unroll)), 1, 1)
-        call = "ew_kernel<S, P, %d, %d, %d, %s>(p);" % (V, BLOCK, unroll, "true" if st.flat else "false")
+        if not st.flat and nvec >= BLOCK * unroll and K <= 65535 * 65535:
+            # long rows: blocks tile each row (block y/z = row), no index division
+            mode = 2
+            grid = ((nvec + BLOCK * unroll - 1) // (BLOCK * unroll), min(K, 65535), (K + 65534) // 65535)
+        else:
+            mode = 1 if st.flat else 0
+            grid = (max(1, (total + BLOCK * unroll - 1) // (BLOCK * unroll)), 1, 1)
+        call = "ew_kernel<S, P, %d, %d, %d, %d>(p);" % (V, BLOCK, unroll, mode)
         src, name = self._source(f, em, ["out[0][i] = %s;" % val], 0, "OP_SUM", None, st_lines, call)
         pz = Pass()
         pz.name = name
