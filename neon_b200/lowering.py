@@ -505,6 +505,10 @@ class Planner(object):
         self.target = sm_count * target_blocks_per_sm
         self.unary = UNARY_C if precise_math else UNARY_FAST
         self.binary = BINARY_C if precise_math else BINARY_FAST
+        # launch tuning (measured on B200, see profiles/): vectors per thread and
+        # minimum resident blocks per SM of the element-wise skeleton
+        self.ew_unroll = 4
+        self.ew_min_blocks = None          # None: 5 for instruction-heavy statements, else 4
 
     # ---- helpers on the frame: K = kept axis, N = loop axis
     def plan(self, st, scratch, rounding=0, fuse_final=True, lin=None):
@@ -539,6 +543,29 @@ class Planner(object):
                 return passes
         passes.append(self._ew_pass(st, res_buf, ka, ra, rounding))
         return passes
+
+    # rough instruction counts per element of the fast-math expansions
+    _OP_COST = {"tanh": 15, "tanh2": 16, "exp": 8, "exp2": 3, "log": 10, "log2": 8, "safelog": 12, "sig": 12,
+                "sig2": 7, "pow": 30, "div": 3, "sqrt": 2, "sgn": 3, "finite": 2, "rand": 12}
+
+    def _issue_bound(self, st, bytes_per_element, rounding):
+        """True when the statement's arithmetic, not its memory traffic, limits an
+        element-wise pass: more than ~3 instructions per byte moved."""
+        seen, cost, todo = set(), 0, [st.root]
+        while todo:
+            n = todo.pop()
+            if n.nid in seen:
+                continue
+            seen.add(n.nid)
+            if n.kind in ("u", "b", "z"):
+                cost += self._OP_COST.get(n.op, 1)
+            elif n.kind == "t":
+                cost += 1
+            if n.kind != "r":
+                todo.extend(n.args)
+        if rounding:
+            cost += 9
+        return cost > 3.0 * max(bytes_per_element, 1)
 
     @staticmethod
     def _reachable(st, node):
@@ -693,8 +720,14 @@ class Planner(object):
                 if lane_var:
                     self.lane_ops.append((o, "k" if self.lk else "n"))
                     self.l_decl.append("u32 %s[(%d * V + 3) / 4];" % (aname, DT_SIZE[o.dt]))
-                    self.l_lines.append("ld_w<%s, V, %s>(p.%s, k * p.%s_sk + n * p.%s_sn, l.%s);"
-                                        % (DT_NAMES[o.dt], nc, pre, pre, pre, aname))
+                    # with V > 1 the host guarantees unit stride along the lanes
+                    if self.lk:
+                        off = "(V > 1 ? k : k * p.%s_sk) + n * p.%s_sn" % (pre, pre)
+                    elif self.st.flat:
+                        off = "n"
+                    else:
+                        off = "k * p.%s_sk + (V > 1 ? n : n * p.%s_sn)" % (pre, pre)
+                    self.l_lines.append("ld_w<%s, V, %s>(p.%s, %s, l.%s);" % (DT_NAMES[o.dt], nc, pre, off, aname))
                     self.e_pre.append("float %s[V]; cvt_in<%s, V>(l.%s, %s);" % (aname, DT_NAMES[o.dt], aname, aname))
                     ref = aname + "[i]"
                 else:
@@ -914,6 +947,7 @@ class Planner(object):
         f.i64("nvec", nvec)
         sr = bool(rounding)
         st_lines = []
+        o_off = "n" if st.flat else "k * p.o_sk + (V > 1 ? n : n * p.o_sn)"
         if sr:
             em.uses_rng = True
             f.u32("rk0", 0)
@@ -931,12 +965,14 @@ class Planner(object):
             st_lines.append("const SrCtx c = sr_ctx(p.sr_mb); const Rng g{p.rk0, p.rk1}; u32 ur[V];")
             st_lines.append("rng_lanes<V, %s, %s>(g, (u64)(p.lin_0 + %s * p.lin_r + %s * p.lin_c), %s, ur);"
                             % (pair, aligned, row, col, step))
-            st_lines.append("st_f<%s, V, true>(p.o, k * p.o_sk + n * p.o_sn, v, c, ur);" % DT_NAMES[odt])
+            st_lines.append("st_f<%s, V, true>(p.o, %s, v, c, ur);" % (DT_NAMES[odt], o_off))
         else:
             st_lines.append("SrCtx c; c.shift = 0; c.mask = 0;")
-            st_lines.append("st_f<%s, V, false>(p.o, k * p.o_sk + n * p.o_sn, v, c, nullptr);" % DT_NAMES[odt])
+            st_lines.append("st_f<%s, V, false>(p.o, %s, v, c, nullptr);" % (DT_NAMES[odt], o_off))
         total = nvec if st.flat else K * nvec
-        unroll = 4 if total >= self.target * BLOCK * 4 else (2 if total >= self.target * BLOCK else 1)
+        big = self.ew_unroll
+        unroll = big if total >= self.target * BLOCK * big else (2 if total >= self.target * BLOCK else 1)
+        unroll = min(unroll, big)
         if not st.flat and nvec >= BLOCK * unroll and K <= 65535 * 65535:
             # long rows: blocks tile each row (block y/z = row), no index division
             mode = 2
@@ -945,7 +981,12 @@ class Planner(object):
             mode = 1 if st.flat else 0
             grid = (max(1, (total + BLOCK * unroll - 1) // (BLOCK * unroll)), 1, 1)
         call = "ew_kernel<S, P, %d, %d, %d, %d>(p);" % (V, BLOCK, unroll, mode)
-        src, name = self._source(f, em, ["out[0][i] = %s;" % val], 0, "OP_SUM", None, st_lines, call)
+        min_blocks = self.ew_min_blocks
+        if min_blocks is None:
+            moved = DT_SIZE[odt] + sum(DT_SIZE[o.dt] for o, _ in em.lane_ops)
+            min_blocks = 5 if self._issue_bound(st, moved, rounding) else 4
+        src, name = self._source(f, em, ["out[0][i] = %s;" % val], 0, "OP_SUM", None, st_lines, call,
+                                 min_blocks=min_blocks)
         pz = Pass()
         pz.name = name
         pz.kind = "ew_flat" if st.flat else "ew_2d"
@@ -961,7 +1002,7 @@ class Planner(object):
         return pz
 
     @staticmethod
-    def _source(f, em, eval_tail, nred, ops, ep_lines, st_lines, call):
+    def _source(f, em, eval_tail, nred, ops, ep_lines, st_lines, call, min_blocks=1):
         ind = "\n        "
         nout = max(nred, 1)
         parts = ['#include "optree_templates.cuh"', "using namespace b200;", f.decl(), "template <int V> struct S {"]
@@ -988,6 +1029,6 @@ class Planner(object):
         # kernel name = skeleton + digest of the instance, so profiles can tell instances apart
         import zlib
         name = "ot_%s_%08x" % (call.split("<")[0], zlib.crc32(body.encode()) & 0xFFFFFFFF)
-        body += ('extern "C" __global__ void __launch_bounds__(%d) %s(const __grid_constant__ P p) { %s }\n'
-                 % (BLOCK, name, call))
+        body += ('extern "C" __global__ void __launch_bounds__(%d, %d) %s(const __grid_constant__ P p) { %s }\n'
+                 % (BLOCK, min_blocks, name, call))
         return body, name
