@@ -84,6 +84,10 @@ class B200Backend(OpTreeBackend):
         self.set_stochastic_round(stochastic_round)
         self._scratch = _Scratch()
         self._planner = Planner(self.sm_count, precise_math=precise_math)
+        self._status = rt.malloc(256)          # kernels set it when a bounded wait gives up
+        rt.memset(self._status, 0, 1, 256)
+        self._planner.status_ptr = self._status
+        self._planner.smem_cap = min(200 * 1024, props.max_smem_per_block - 24 * 1024)
         self._kernels = {}
         self._plans = {}                   # program_key -> BoundPlan
         self._temps = {}
@@ -297,11 +301,14 @@ class B200Backend(OpTreeBackend):
             if kernel is None:
                 kernel = self._kernels[pz.source] = rt.kernel_get(pz.source, pz.name)
             pz.kernel = kernel
+            if pz.setup is not None:
+                pz.setup(rt, kernel, pz)
         if pz.uses_rng:
             k0, k1 = rt.rng_next_key()
             pz.fields.values["rk0"] = k0
             pz.fields.values["rk1"] = k1
-        rt.launch(kernel, pz.grid, pz.block, pz.fields.pack(), stream=self.stream)
+        rt.launch(kernel, pz.grid, pz.block, pz.fields.pack(), smem=pz.smem, stream=self.stream,
+                  cluster=pz.cluster)
         self.launches += 1
         if self.launch_log is not None:
             self.launch_log.append((pz.kind, pz.desc))
@@ -403,6 +410,15 @@ class B200Backend(OpTreeBackend):
 
     def synchronize(self):
         rt.stream_sync(self.stream)
+        self.check_status()
+
+    def check_status(self):
+        """Raise if a kernel reported that one of its bounded waits ran out."""
+        flag = np.zeros(1, np.int32)
+        rt.memcpy_d2h(flag.ctypes.data, self._status, 4, self.stream, sync=True)
+        if flag[0]:
+            rt.memset(self._status, 0, 1, 4, self.stream)
+            raise rt.B200Error(-6, "a kernel gave up waiting for its shared-memory staging copy")
 
     # ------------------------------------------------------------------ not on the op-tree path
     def _off_path(self, *a, **k):

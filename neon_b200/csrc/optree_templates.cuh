@@ -692,4 +692,205 @@ DEV void red_cols_kernel(const P& p) {
     }
 }
 
+
+// ================================================================== row-resident statements
+// A statement with several passes over the same rows (mean -> variance ->
+// normalise, row softmax ...) normally re-reads its operands from HBM once per
+// pass.  When a row of the full-size operands fits in the shared memory of a
+// thread-block cluster, the kernel below reads it from HBM exactly once: the
+// C blocks of a cluster each stage a contiguous slice of the row with TMA bulk
+// copies (cp.async.bulk, completion on an mbarrier), every pass then runs out
+// of shared memory, partial reductions are exchanged through distributed
+// shared memory between two hardware cluster barriers, and the last pass
+// streams the result to HBM.  Clusters walk over rows persistently.
+//
+// The generated driver calls the pieces in this order per row:
+//   rr_stage_begin / rr_stage_copy... / rr_stage_wait, then per reduction pass
+//   rr_reduce + rr_combine, finally rr_ew.
+// Waits are bounded: a bulk copy that never completes sets *status and the
+// kernel carries on to its end instead of spinning.
+
+DEV u32 smem_u32(const void* p) { return (u32)__cvta_generic_to_shared(p); }
+DEV u32 cluster_rank() { u32 r; asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r)); return r; }
+DEV u32 cluster_index() { u32 r; asm volatile("mov.u32 %0, %%clusterid.x;" : "=r"(r)); return r; }
+DEV u32 cluster_count() { u32 r; asm volatile("mov.u32 %0, %%nclusterid.x;" : "=r"(r)); return r; }
+DEV void cluster_barrier() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+DEV u32 dsmem_ld(const void* local, u32 rank) {
+    u32 addr, v;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(addr) : "r"(smem_u32(local)), "r"(rank));
+    asm volatile("ld.shared::cluster.u32 %0, [%1];" : "=r"(v) : "r"(addr) : "memory");
+    return v;
+}
+DEV void mbar_init(u64* bar, u32 count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+}
+DEV void mbar_expect_tx(u64* bar, u32 bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+DEV bool mbar_try_wait(u64* bar, u32 parity) {
+    u32 ok;
+    asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                 : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+    return ok != 0;
+}
+// global -> this block's shared memory, 16-byte aligned on both sides, bytes % 16 == 0
+DEV void bulk_g2s(void* dst, const void* src, u32 bytes, u64* bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(smem_u32(dst)), "l"(src), "r"(bytes), "r"(smem_u32(bar)) : "memory");
+}
+
+struct RowCtx {
+    u32 rank;            // block's rank in its cluster
+    i64 v0, v1;          // this block's slice of the row, in V-wide vectors
+    u32 phase;           // mbarrier parity of the next staging
+    u32 row_parity;      // which set of exchange slots this row uses
+    bool failed;
+};
+
+template <int C> DEV void rr_begin(RowCtx& cx, i64 nvec, u64* bar) {
+    cx.rank = C > 1 ? cluster_rank() : 0;
+    const i64 per = (nvec + C - 1) / C;
+    cx.v0 = (i64)cx.rank * per;
+    cx.v1 = cx.v0 + per < nvec ? cx.v0 + per : nvec;
+    if (cx.v0 > cx.v1) cx.v0 = cx.v1;
+    cx.phase = 0; cx.row_parity = 0; cx.failed = false;
+    if (threadIdx.x == 0) mbar_init(bar, 1);
+    __syncthreads();
+}
+// before the async copies overwrite the slice: all reads of the previous row are done
+DEV void rr_stage_begin(u64* bar, u32 total_bytes) {
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        mbar_expect_tx(bar, total_bytes);
+    }
+}
+DEV void rr_stage_copy(unsigned char* dst, u64 src, u32 bytes, u64* bar) {
+    if (threadIdx.x == 0) {
+        for (u32 off = 0; off < bytes; off += 32768u) {
+            const u32 n = bytes - off < 32768u ? bytes - off : 32768u;
+            bulk_g2s(dst + off, reinterpret_cast<const char*>(src) + off, n, bar);
+        }
+    }
+}
+DEV void rr_stage_wait(RowCtx& cx, u64* bar, u64 status) {
+    bool done = false;
+    for (int spin = 0; spin < (1 << 22); ++spin) {
+        if (mbar_try_wait(bar, cx.phase)) { done = true; break; }
+    }
+    if (!done) {
+        cx.failed = true;
+        if (threadIdx.x == 0 && status) atomicExch(reinterpret_cast<int*>(status), 1);
+    }
+    cx.phase ^= 1;
+}
+
+// one reduction pass over this block's slice (operands already point at shared memory)
+template <template <int> class SV, class P, int V, int THREADS, int UNROLL>
+DEV void rr_reduce(const P& q, i64 k, const RowCtx& cx, float* a, int* ai, float (*sv)[THREADS / 32], int (*si)[THREADS / 32]) {
+    typedef SV<V> S;
+    constexpr int NR = S::NRED;
+    const int tid = threadIdx.x;
+    float acc[NR][V]; int acci[NR][V];
+#pragma unroll
+    for (int r = 0; r < NR; ++r)
+#pragma unroll
+        for (int i = 0; i < V; ++i) { acc[r][i] = red_init(S::op(r)); acci[r][i] = -1; }
+    typename S::H h;
+    S::load_h(q, k, h);
+    for (i64 v = cx.v0 + tid; v < cx.v1; v += (i64)THREADS * UNROLL) {
+        typename S::L l[UNROLL];
+#pragma unroll
+        for (int u = 0; u < UNROLL; ++u) if (v + (i64)u * THREADS < cx.v1) S::load_l(q, k, (v + (i64)u * THREADS) * V, l[u]);
+#pragma unroll
+        for (int u = 0; u < UNROLL; ++u) {
+            if (v + (i64)u * THREADS < cx.v1) {
+                const i64 n = (v + (i64)u * THREADS) * V;
+                float out[NR][V];
+                S::eval(q, h, l[u], k, n, out);
+#pragma unroll
+                for (int r = 0; r < NR; ++r)
+#pragma unroll
+                    for (int i = 0; i < V; ++i) red_acc(S::op(r), acc[r][i], acci[r][i], out[r][i], (int)(n + i));
+            }
+        }
+    }
+#pragma unroll
+    for (int r = 0; r < NR; ++r) {
+        a[r] = acc[r][0]; ai[r] = acci[r][0];
+#pragma unroll
+        for (int i = 1; i < V; ++i) red_merge(S::op(r), a[r], ai[r], acc[r][i], acci[r][i]);
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            float b = __shfl_xor_sync(0xffffffffu, a[r], o);
+            int bi = __shfl_xor_sync(0xffffffffu, ai[r], o);
+            red_merge(S::op(r), a[r], ai[r], b, bi);
+        }
+    }
+    const int warp = tid >> 5, lane = tid & 31;
+    __syncthreads();                       // sv/si may still be read from the previous pass
+    if (lane == 0) {
+#pragma unroll
+        for (int r = 0; r < NR; ++r) { sv[r][warp] = a[r]; si[r][warp] = ai[r]; }
+    }
+    __syncthreads();
+#pragma unroll
+    for (int r = 0; r < NR; ++r) {          // every thread folds the warp results, in warp order
+        a[r] = sv[r][0]; ai[r] = si[r][0];
+        for (int w = 1; w < THREADS / 32; ++w) red_merge(S::op(r), a[r], ai[r], sv[r][w], si[r][w]);
+    }
+}
+
+// exchange the block results of one pass inside the cluster and leave the row's
+// result in res[0..NR): value bits, or the index for arg reductions
+template <template <int> class SV, int V, int C>
+DEV void rr_combine(const RowCtx& cx, float* a, int* ai, u32* slots /* [2 parities][NR][2] of this pass */, u32* res) {
+    typedef SV<V> S;
+    constexpr int NR = S::NRED;
+    if constexpr (C > 1) {
+        u32* mine = slots + cx.row_parity * NR * 2;
+        if (threadIdx.x == 0) {
+#pragma unroll
+            for (int r = 0; r < NR; ++r) { mine[2 * r] = __float_as_uint(a[r]); mine[2 * r + 1] = (u32)ai[r]; }
+        }
+        cluster_barrier();
+#pragma unroll
+        for (int r = 0; r < NR; ++r) {
+            a[r] = __uint_as_float(dsmem_ld(mine + 2 * r, 0)); ai[r] = (int)dsmem_ld(mine + 2 * r + 1, 0);
+            for (u32 c = 1; c < (u32)C; ++c)
+                red_merge(S::op(r), a[r], ai[r], __uint_as_float(dsmem_ld(mine + 2 * r, c)), (int)dsmem_ld(mine + 2 * r + 1, c));
+        }
+    }
+    if (threadIdx.x == 0) {
+#pragma unroll
+        for (int r = 0; r < NR; ++r) res[r] = red_is_arg(S::op(r)) ? (u32)ai[r] : __float_as_uint(a[r]);
+    }
+    __syncthreads();
+}
+
+// the element-wise pass over this block's slice
+template <template <int> class SV, class P, int V, int THREADS, int UNROLL>
+DEV void rr_ew(const P& q, i64 k, const RowCtx& cx) {
+    typedef SV<V> S;
+    typename S::H h;
+    S::load_h(q, k, h);
+    for (i64 v = cx.v0 + threadIdx.x; v < cx.v1; v += (i64)THREADS * UNROLL) {
+        typename S::L l[UNROLL];
+#pragma unroll
+        for (int u = 0; u < UNROLL; ++u) if (v + (i64)u * THREADS < cx.v1) S::load_l(q, k, (v + (i64)u * THREADS) * V, l[u]);
+#pragma unroll
+        for (int u = 0; u < UNROLL; ++u) {
+            if (v + (i64)u * THREADS < cx.v1) {
+                const i64 n = (v + (i64)u * THREADS) * V;
+                float out[1][V];
+                S::eval(q, h, l[u], k, n, out);
+                S::store(q, k, n, out[0]);
+            }
+        }
+    }
+}
+
 }  // namespace b200

@@ -478,11 +478,14 @@ class _Fields(object):
 class Pass(object):
     """One kernel launch of a statement."""
     __slots__ = ("source", "name", "grid", "block", "fields", "kernel", "uses_rng", "desc",
-                 "results", "kind")
+                 "results", "kind", "smem", "cluster", "setup")
 
     def __init__(self):
         self.kernel = None
         self.uses_rng = False
+        self.smem = 0          # dynamic shared memory per block
+        self.cluster = 1       # thread blocks per cluster
+        self.setup = None      # callable(runtime, kernel, pass) run once after compilation
         self.results = []      # (reduction op, fp32 result address, int32 index address or 0, count)
 
 
@@ -507,6 +510,11 @@ class Planner(object):
         self.binary = BINARY_C if precise_math else BINARY_FAST
         # launch tuning (measured on B200, see profiles/): vectors per thread and
         # minimum resident blocks per SM of the element-wise skeleton
+        self.red_resident = 5              # blocks of a reduction kernel resident per SM (48 registers)
+        self.rowres = True                 # keep rows in cluster shared memory across passes when they fit
+        self.smem_cap = 200 * 1024         # dynamic shared memory a row-resident block may ask for
+        self.rowres_slice_cap = 100 * 1024 # preferred largest slice of a row per block (two blocks per SM)
+        self.status_ptr = 0                # device int the kernels set when a bounded wait gives up
         self.ew_unroll = 4
         self.ew_min_blocks = None          # None: 5 for instruction-heavy statements, else 4
 
@@ -527,6 +535,10 @@ class Planner(object):
         full_shape = self._full_shape(st)
         root_is_k = st.root.shape[ra] == 1
         out_is_k = st.out_shape[ra] == 1
+        if fuse_final and levels and self.rowres:
+            pz = self._rowres_pass(st, reds, levels, ka, ra, full_shape, rounding, root_is_k and out_is_k)
+            if pz is not None:
+                return [pz]
         for li, lv in enumerate(levels):
             rs = [n for n in reds if n.level == lv]
             final = fuse_final and (lv == levels[-1]) and root_is_k and out_is_k and st.root.level == lv
@@ -543,6 +555,238 @@ class Planner(object):
                 return passes
         passes.append(self._ew_pass(st, res_buf, ka, ra, rounding))
         return passes
+
+    # ---- row-resident statement: all passes in one cluster kernel -------------------
+    def _rowres_pass(self, st, reds, levels, ka, ra, full_shape, rounding, red_out):
+        """One kernel for a statement whose passes all walk the same rows along the
+        contiguous axis, when a row of its full-size inputs fits in the shared memory
+        of a cluster of at most 8 blocks.  Returns None when that does not apply."""
+        K, N = full_shape[ka], full_shape[ra]
+        if rounding or any(n.kind == "z" for n in st.nodes):
+            return None
+        n_passes = len(levels) + (0 if red_out else 1)
+        if n_passes < 2:
+            return None
+        self._frame(st, ka, ra)
+        tables = (self.unary, self.binary)
+        f = _Fields()
+        ems, lane_ops, staged = [], [], {}
+        res_buf = {}
+        for r in reds:
+            res_buf[r.nid] = (0, 0)
+        for lv in levels:
+            em = self._Emit(st, f, ka, ra, False, res_buf, lv - 1, tables)
+            em.no_nc = True
+            rs = [n for n in reds if n.level == lv]
+            outs = [em.elem(r.args[0]) for r in rs]
+            ems.append((em, rs, outs))
+            lane_ops += em.lane_ops
+            staged.update(em.full_inputs)
+        fin = self._Emit(st, f, ka, ra, False, res_buf, 1 << 30, tables)
+        fin.no_nc = True
+        if red_out:
+            last_rs = ems[-1][1]
+            for i, r in enumerate(last_rs):
+                fin.names[("h", r.nid)] = "(float)ri[%d]" % i if r.op.startswith("arg") else "r[%d]" % i
+            if st.root.kind == "r" and st.root.op.startswith("arg"):
+                store = "st_index<%s>(p.o, k * p.o_sk, ri[%d]);" % (DT_NAMES[st.out.dt], last_rs.index(st.root))
+            else:
+                store = "{ const int i = 0; (void)i; st_one<%s>(p.o, k * p.o_sk, %s); }" % (
+                    DT_NAMES[st.out.dt], fin.hoist(st.root))
+            extra_ops = []
+        else:
+            val = fin.elem(st.root)
+            lane_ops += fin.lane_ops
+            staged.update(fin.full_inputs)
+            extra_ops = [(st.out, "n")]
+        if not staged:
+            return None
+        for o in staged.values():
+            if o._frame_strides[1] != 1:
+                return None
+        V = self._pick_v(lane_ops, N, True, extra=extra_ops)
+        if V == 1 or N % V:
+            return None
+        nvec = N // V
+        row_bytes = sum(DT_SIZE[o.dt] for o in staged.values())          # per element
+        C = None
+        for c in (1, 2, 4, 8):
+            per = (nvec + c - 1) // c * V
+            need = sum(((per * DT_SIZE[o.dt] + 127) & ~127) for o in staged.values())
+            if need <= self.rowres_slice_cap:
+                C = c
+                break
+        if C is None:                         # does not fit in small slices: one big block per SM
+            for c in (1, 2, 4, 8):
+                per = (nvec + c - 1) // c * V
+                need = sum(((per * DT_SIZE[o.dt] + 127) & ~127) for o in staged.values())
+                if need <= self.smem_cap:
+                    C = c
+                    break
+        if C is None:
+            return None
+        while C < 8 and K * C < self.sm_count and (nvec + 2 * C - 1) // (2 * C) >= 512:
+            C *= 2                            # few rows: more blocks per row to fill the machine
+        per = (nvec + C - 1) // C * V
+        need = sum(((per * DT_SIZE[o.dt] + 127) & ~127) for o in staged.values())
+        seg_vecs = per // V
+        if seg_vecs < 256 or K * C * 2 < self.sm_count:
+            return None                       # rows too short or too few: the multi-pass kernels do better
+        # 64 registers per thread: at most 1024 threads resident per SM, shared by the
+        # blocks that fit next to each other in shared memory
+        fit = (self.smem_cap + 24 * 1024) // max(need, 1)
+        blocks_per_sm = 4 if fit >= 4 else (2 if fit >= 2 else 1)
+        threads = 1024 // blocks_per_sm
+        while threads > 256 and seg_vecs < 2 * threads:
+            threads //= 2
+        unroll = 2
+        nrmax = max(len(rs) for _, rs, _ in ems)
+        nres = len(reds)
+        slot_of = {}
+        for _, rs, _ in ems:                      # results of one pass sit next to each other
+            for r in rs:
+                slot_of[r.nid] = len(slot_of)
+
+        f.u64("o", st.out.ptr)
+        f.i64("o_sk", st.out._frame_strides[0])
+        f.i64("o_sn", st.out._frame_strides[1])
+        f.i64("K", K)
+        f.i64("N", N)
+        f.i64("nvec", nvec)
+        f.u64("status", self.status_ptr)
+        offs, off = {}, 0
+        for pre, o in sorted(staged.items()):
+            offs[pre] = off
+            f.u32("off_" + pre, off)
+            off += (per * DT_SIZE[o.dt] + 127) & ~127
+        dyn_bytes = off
+
+        parts = ['#include "optree_templates.cuh"', "using namespace b200;", f.decl()]
+        for i, (em, rs, outs) in enumerate(ems):
+            ops = " : ".join("r == %d ? %s" % (j, RED_CODE[r.op]) for j, r in enumerate(rs[:-1]))
+            ops = (ops + " : " if ops else "") + RED_CODE[rs[-1].op]
+            tail = ["out[%d][i] = %s;" % (j, e) for j, e in enumerate(outs)]
+            parts.append(self._struct("S%d" % i, em, tail, len(rs), ops, None, None))
+        if red_out:
+            parts.append(self._struct("SF", fin, [], 0, "OP_SUM", fin.h_lines + [store], None, epilogue_only=True))
+        else:
+            st_lines = ["SrCtx c; c.shift = 0; c.mask = 0;",
+                        "st_f<%s, V, false>(p.o, k * p.o_sk + n, v, c, nullptr);" % DT_NAMES[st.out.dt]]
+            parts.append(self._struct("SE", fin, ["out[0][i] = %s;" % val], 0, "OP_SUM", None, st_lines))
+
+        body = []
+        body.append("extern __shared__ __align__(128) unsigned char dyn[];")
+        body.append("__shared__ u64 bar;")
+        body.append("__shared__ float sv[%d][%d]; __shared__ int si[%d][%d];" % (nrmax, threads // 32, nrmax, threads // 32))
+        body.append("__shared__ u32 slots[%d][2][%d][2]; __shared__ u32 s_res[%d];" % (len(ems), nrmax, nres))
+        body.append("RowCtx cx; rr_begin<%d>(cx, p.nvec, &bar);" % C)
+        body.append("const i64 n0 = cx.v0 * %d; const u32 seg = (u32)(cx.v1 - cx.v0) * %d;" % (V, V))
+        body.append("const i64 kfirst = %s, kstep = %s;" % (("cluster_index()", "cluster_count()") if C > 1
+                                                            else ("blockIdx.x", "gridDim.x")))
+        body.append("for (i64 k = kfirst; k < p.K; k += kstep) {")
+        body.append("    rr_stage_begin(&bar, seg * %du);" % row_bytes)
+        for pre, o in sorted(staged.items()):
+            isz = DT_SIZE[o.dt]
+            body.append("    rr_stage_copy(dyn + p.off_%s, p.%s + (u64)((k * p.%s_sk + n0) * %d), seg * %du, &bar);"
+                        % (pre, pre, pre, isz, isz))
+        body.append("    rr_stage_wait(cx, &bar, p.status);")
+        body.append("    P q = p;")
+        for pre, o in sorted(staged.items()):
+            body.append("    q.%s = (u64)(dyn + p.off_%s) - (u64)(n0 * %d); q.%s_sk = 0;" % (pre, pre, DT_SIZE[o.dt], pre))
+        for r in reds:
+            if ("r%d" % r.nid) in f.values:
+                body.append("    q.r%d = (u64)&s_res[%d]; q.r%d_sk = 0; q.r%d_sn = 0;" % (r.nid, slot_of[r.nid], r.nid, r.nid))
+        body.append("    float a[%d]; int ai[%d];" % (nrmax, nrmax))
+        for i, (em, rs, outs) in enumerate(ems):
+            body.append("    rr_reduce<S%d, P, %d, %d, %d>(q, k, cx, a, ai, sv, si);" % (i, V, threads, unroll))
+            body.append("    rr_combine<S%d, %d, %d>(cx, a, ai, &slots[%d][0][0][0], &s_res[%d]);"
+                        % (i, V, C, i, slot_of[rs[0].nid]))
+        if red_out:
+            body.append("    if (threadIdx.x == 0 && cx.rank == 0) SF<%d>::epilogue(q, k, a, ai);" % V)
+        else:
+            body.append("    rr_ew<SE, P, %d, %d, %d>(q, k, cx);" % (V, threads, unroll))
+        body.append("    cx.row_parity ^= 1;")
+        body.append("}")
+        if C > 1:
+            body.append("cluster_barrier();      // nobody leaves while a peer may still read its exchange slots")
+        text = "\n".join(parts) + "\n"
+        import zlib
+        name = "ot_rowres_kernel_%08x" % (zlib.crc32((text + "\n".join(body)).encode()) & 0xFFFFFFFF)
+        text += ('extern "C" __global__ void __launch_bounds__(%d, %d) %s(const __grid_constant__ P p) {\n    %s\n}\n'
+                 % (threads, blocks_per_sm, name, "\n    ".join(body)))
+        pz = Pass()
+        pz.kind = "rowres"
+        pz.name, pz.source, pz.fields = name, text, f
+        pz.block = (threads, 1, 1)
+        pz.smem, pz.cluster = dyn_bytes, C
+        clusters = max(1, min(K, (self.sm_count * blocks_per_sm) // C))
+        pz.grid = (clusters * C, 1, 1)
+        pz.desc = "rowres V=%d K=%d N=%d cluster=%d threads=%d smem=%d passes=%d grid=%s" % (
+            V, K, N, C, threads, dyn_bytes, n_passes, pz.grid)
+
+        def setup(rt, kernel, pz, K=K, C=C, threads=threads, dyn=dyn_bytes):
+            """Opt in to the dynamic shared memory and size the grid to the clusters the
+            device can hold at once (they loop over the rows)."""
+            rt.kernel_max_smem(kernel, dyn)
+            fit = rt.kernel_max_clusters(kernel, threads, dyn, C, pz.grid[0]) if C > 1 else \
+                rt.kernel_occupancy(kernel, threads, dyn) * self.sm_count
+            fit = max(1, min(K, fit))
+            pz.grid = (fit * C, 1, 1)
+        pz.setup = setup
+        return pz
+
+    @staticmethod
+    def _struct(name, em, eval_tail, nred, ops, ep_lines, st_lines, epilogue_only=False):
+        ind = "\n        "
+        nout = max(nred, 1)
+        parts = ["template <int V> struct %s {" % name]
+        parts.append("    enum { NRED = %d };" % nred)
+        parts.append("    static DEV constexpr int op(int r) { return %s; }" % ops)
+        if not epilogue_only:
+            parts.append("    struct H { %s int unused_; };" % " ".join(em.h_decl))
+            parts.append("    struct L { %s int unused_; };" % " ".join(em.l_decl))
+            parts.append("    static DEV void load_h(const P& p, i64 k, H& h) {" + ind + ind.join(em.h_lines) + "\n    }")
+            parts.append("    static DEV void load_l(const P& p, i64 k, i64 n, L& l) {" + ind + ind.join(em.l_lines) + "\n    }")
+            body = list(em.e_pre)
+            body.append("_Pragma(\"unroll\") for (int i = 0; i < V; ++i) {")
+            body.extend("    " + x for x in em.e_lines)
+            body.extend("    " + x for x in eval_tail)
+            body.append("}")
+            parts.append("    static DEV void eval(const P& p, const H& h, const L& l, i64 k, i64 n, float (&out)[%d][V]) {" % nout
+                         + ind + ind.join(body) + "\n    }")
+        if st_lines is not None:
+            parts.append("    static DEV void store(const P& p, i64 k, i64 n, const float* v) {" + ind + ind.join(st_lines) + "\n    }")
+        if ep_lines is not None:
+            parts.append("    static DEV void epilogue(const P& p, i64 k, const float* r, const int* ri) {"
+                         + ind + ind.join(ep_lines) + "\n    }")
+        parts.append("};")
+        return "\n".join(parts)
+
+    def _pick_split(self, units, max_split):
+        """How many blocks share one reduction unit (a row, or a tile of columns).
+        Blocks run in rounds of sm_count * resident; a round that is nearly empty
+        costs as much as a full one, and past ~60% occupancy the memory system is
+        saturated.  So: as few rounds as possible with the last one at least 60%
+        full, and within that the split that leaves about 80% of the slots used
+        (measured best for the whole-tensor and the 256-row cases)."""
+        slots = self.sm_count * self.red_resident
+        max_split = max(1, int(max_split))
+        best = None
+        for sp in range(1, min(max_split, 4 * slots) + 1):
+            ctas = units * sp
+            rounds = (ctas + slots - 1) // slots
+            last = ctas - (rounds - 1) * slots
+            if last < 0.6 * slots and not (rounds == 1 and sp == max_split):
+                continue
+            score = (rounds, abs(last / float(slots) - 0.8))
+            if best is None or score < best[0]:
+                best = (score, sp)
+            if ctas > 2 * slots:
+                break
+        if best is None:
+            # no split fills a round: take the largest one that stays within one round
+            return max(1, min(max_split, slots // max(units, 1)))
+        return best[1]
 
     # rough instruction counts per element of the fast-math expansions
     _OP_COST = {"tanh": 15, "tanh2": 16, "exp": 8, "exp2": 3, "log": 10, "log2": 8, "safelog": 12, "sig": 12,
@@ -610,6 +854,8 @@ class Planner(object):
             self.uses_rng = False
             self.lane_ops = []                 # (operand, lane axis) of every vector access
             self.pseudo = {}
+            self.no_nc = False                 # True: operands may point at shared memory, plain loads only
+            self.full_inputs = {}              # prefix -> operand, tensors that vary along both axes
 
         def var_k(self, n):
             return n.shape[self.ka] > 1
@@ -659,7 +905,7 @@ class Planner(object):
             name = "k%d" % n.nid
             if n.kind in ("t", "r"):
                 o, pre = self._leaf(n)
-                nc = "false" if o.alias_out else "true"
+                nc = "false" if (o.alias_out or self.no_nc) else "true"
                 if self.lk and self.var_k(n):
                     self.lane_ops.append((o, "k"))
                     self.h_lines.append("float %s[V]; ld_f<%s, V, %s>(p.%s, k * p.%s_sk, %s);"
@@ -714,8 +960,10 @@ class Planner(object):
                 return self.names[key]
             if n.kind in ("t", "r"):
                 o, pre = self._leaf(n)
-                nc = "false" if o.alias_out else "true"
+                nc = "false" if (o.alias_out or self.no_nc) else "true"
                 lane_var = self.var_k(n) if self.lk else True     # var_n holds here
+                if n.kind == "t" and self.var_k(n):
+                    self.full_inputs[pre] = o
                 aname = "a_" + pre
                 if lane_var:
                     self.lane_ops.append((o, "k" if self.lk else "n"))
@@ -870,8 +1118,7 @@ class Planner(object):
             CW = min(8, _pow2ceil((K + V - 1) // V))
             RH = BLOCK // CW
             tiles = (K + CW * V - 1) // (CW * V)
-            want = self.sm_count * 4
-            split = max(1, min((want + tiles - 1) // tiles, (N + RH * 4 - 1) // (RH * 4)))
+            split = self._pick_split(tiles, (N + RH * 4 - 1) // (RH * 4))
             seg = (N + split - 1) // split
             split = (N + seg - 1) // seg
             grid = (tiles, split, 1)
@@ -884,7 +1131,7 @@ class Planner(object):
             nvec = N // V
             if nvec >= 2 * BLOCK or (K * 8 <= self.target and nvec > 32):
                 TPR = BLOCK
-                split = max(1, min((self.target + K - 1) // K, nvec // (BLOCK * 4)))
+                split = self._pick_split(K, nvec // (BLOCK * 4))
                 seg = (nvec + split - 1) // split
                 split = max(1, (nvec + seg - 1) // seg)
                 grid = (K * split, 1, 1)

@@ -258,6 +258,22 @@ def kernel_get(source, name="optree_kernel", options=None):
     return k.value
 
 
+def kernel_max_smem(kernel, nbytes):
+    check(lib().b200_kernel_max_smem(kernel, nbytes))
+
+
+def kernel_occupancy(kernel, threads, smem):
+    n = i32(0)
+    check(lib().b200_kernel_occupancy(kernel, threads, smem, C.byref(n)))
+    return n.value
+
+
+def kernel_max_clusters(kernel, threads, smem, cluster, grid_blocks):
+    n = i32(0)
+    check(lib().b200_kernel_max_clusters(kernel, threads, smem, cluster, grid_blocks, C.byref(n)))
+    return n.value
+
+
 def launch(kernel, grid, block, params, smem=0, stream=0, cluster=1, cooperative=False):
     check(lib().b200_launch(kernel, grid[0], grid[1], grid[2], block[0], block[1], block[2],
                             smem, stream, params, len(params), cluster, 1 if cooperative else 0))

@@ -42,9 +42,25 @@ def test_softmax_is_three_passes_with_deduplicated_max(dry):
 def test_axis1_statistics_use_row_kernels_and_vector_width_8_for_fp16():
     be = DryRunBackend()
     be.compile = False
+    be._planner.rowres = False
     _run_dry(be, cfg4(256, 401408))
     assert [p.kind for p in be.passes] == ["red_rows", "red_rows", "ew_2d"]
     assert all("V=8" in p.desc for p in be.passes)
+
+
+def test_rows_that_fit_cluster_shared_memory_become_one_row_resident_kernel():
+    be = DryRunBackend()
+    be.compile = False
+    _run_dry(be, cfg4(256, 401408))          # 802,816-byte rows: eight blocks of 100,352 bytes, two per SM
+    assert [p.kind for p in be.passes] == ["rowres"]
+    pz = be.passes[0]
+    assert pz.cluster == 8 and pz.smem == 100352 and pz.block == (512, 1, 1)
+    be.passes = []
+    _run_dry(be, cfg4(32, 4096))             # short rows: the multi-pass kernels
+    assert [p.kind for p in be.passes] == ["red_rows", "red_rows", "ew_2d"]
+    be.passes = []
+    _run_dry(be, cfg4(8, 4000000))           # a row larger than eight blocks can hold
+    assert "rowres" not in [p.kind for p in be.passes]
 
 
 def test_whole_tensor_reduction_is_one_flat_pass():

@@ -59,6 +59,44 @@ def test_large_configs_match_checker(case, b200):
     _compare(case, got, _oracle64(case))
 
 
+def _rowres_cases():
+    def in1(shape, dtype=np.float32, scale=1.0):
+        return lambda rng: {"x": (scale * rng.uniform(-1, 1, shape)).astype(dtype)}
+
+    out = [cases.cfg4(256, 56 * 56 * 128), cases.cfg4(64, 100352), cases.cfg4(300, 8192)]
+
+    def softmax1(be, t):
+        x = t["x"]
+        t["out"][:] = be.exp(x - be.max(x, axis=1)) / be.sum(be.exp(x - be.max(x, axis=1)), axis=1)
+    out.append(cases.Case("softmax_axis1_200x16384", in1((200, 16384), scale=3.0),
+                          {"out": ((200, 16384), np.float32)}, softmax1))
+
+    def var_rows(be, t):
+        t["out"][:] = be.var(t["x"], axis=1)
+    out.append(cases.Case("var_axis1_red_out_150x40000", in1((150, 40000)),
+                          {"out": ((150, 1), np.float32)}, var_rows))
+
+    def argmax_center(be, t):
+        x = t["x"]
+        t["out"][:] = (x - be.mean(x, axis=1)) * be.argmax(x, axis=1)
+    out.append(cases.Case("center_times_argmax_128x65536_f16", in1((128, 65536), np.float16),
+                          {"out": ((128, 65536), np.float32)}, argmax_center))
+    return out
+
+
+@pytest.mark.parametrize("case", _rowres_cases(), ids=lambda c: c.name)
+def test_row_resident_cluster_kernel_matches_checker(case, b200):
+    """Statements whose rows fit in cluster shared memory run as one kernel (TMA-staged
+    rows, reductions exchanged through distributed shared memory)."""
+    b200.launch_log = []
+    got = cases.run_case(b200, case)
+    kinds = [k for k, _ in b200.launch_log]
+    b200.launch_log = None
+    assert kinds == ["rowres"], kinds
+    b200.check_status()
+    _compare(case, got, _oracle64(case))
+
+
 def test_full_size_properties_cfg5(b200):
     """2^28 elements of the fp16 chain with stochastic rounding: size-independent checks.
     total must equal the float64 sum of the device-produced z (relative to sum|z|),
