@@ -38,9 +38,10 @@ ROWS = COLS = 32768
 BYTES_PER_ELEMENT = 6 + 2 + 2          # z statement, total, peak (algorithmic)
 Z_BYTES_PER_ELEMENT = 6                # dominant kernel: read x, y (fp16), write z (fp16)
 METRIC = "compound-optree effective HBM GB/s"
-# dram__bytes_read.sum + dram__bytes_write.sum of the z kernel divided by its elements,
-# from the ncu capture summarised in profiles/ (None until one has been taken)
-Z_DRAM_BYTES_PER_ELEMENT = None
+# dram__bytes_read.sum + dram__bytes_write.sum of the z kernel divided by its elements, from the
+# ncu capture of a 2^26-element launch (profiles/ew_kernel_cfg5_fp16_chain.md: 269.2 MB + 105.5 MB);
+# traffic grows in proportion to the elements, so a full launch is this times its element count
+Z_DRAM_BYTES_PER_ELEMENT = (269.218304e6 + 105.476864e6) / (1 << 26)
 
 
 def measured_peak():
@@ -66,7 +67,7 @@ class ClockSampler(object):
     def start(self):
         try:
             self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.device), "--query-gpu=" + self.Q,
-                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                          "--format=csv,noheader,nounits", "-lms", "20"],
                                          stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             self.thread = threading.Thread(target=self._read, daemon=True)
             self.thread.start()
@@ -352,7 +353,6 @@ def main():
     barrier()
     ms_total = max_over_ranks(be.get_time(ev0, ev1))
     launches = be.launches - launches0
-    clocks = sampler.stop() if rank == 0 else None
     z_ms = float(np.mean([be.get_time(a, b) for a, b in kz]))
     res_total, res_peak = float(total.get()[0, 0]), float(peak.get()[0, 0])
 
@@ -372,6 +372,7 @@ def main():
     be.synchronize()
     barrier()
     e2e_ms = max_over_ranks(be.get_time(ev0, ev1))
+    clocks = sampler.stop() if rank == 0 else None      # sampled over both timed regions
 
     if rank != 0:
         return

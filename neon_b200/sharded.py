@@ -29,7 +29,7 @@ import numpy as np
 
 from . import runtime as rt
 from .backend import B200Backend
-from .lowering import Statement
+from .lowering import BoundPlan, Statement, program_key
 from .optree import OpTreeNode, Tensor
 
 _none_slice = slice(None, None, None)
@@ -168,12 +168,19 @@ class ShardedBackend(B200Backend):
             lin = out.flat_of if out.flat_of else (out.shape[1], out.c0)
         local_stack = [s.local if isinstance(s, ShardedTensor) else s for s in stack]
         rounding = self._rounding_bits(local_stack[0])
-        uses_rng = bool(rounding) or any(type(s) is dict and s["op"] == "rand" for s in stack)
-        st = Statement(local_stack, allow_flat=not uses_rng)
-        crosses = st.has_red and st.axis == 1
-        self._scratch.reset()
-        passes = self._planner.plan(st, self._scratch, rounding=rounding, fuse_final=not crosses, lin=lin)
-        for pz in passes:
+        key = (program_key(local_stack), rounding, lin)
+        cached = self._plans.get(key)
+        if cached is None:
+            uses_rng = bool(rounding) or any(type(s) is dict and s["op"] == "rand" for s in stack)
+            st = Statement(local_stack, allow_flat=not uses_rng)
+            crosses = st.has_red and st.axis == 1
+            self._scratch.reset()
+            passes = self._planner.plan(st, self._scratch, rounding=rounding, fuse_final=not crosses, lin=lin)
+            cached = self._plans[key] = (BoundPlan(st, passes), crosses)
+        else:
+            cached[0].rebind(local_stack)
+        plan, crosses = cached
+        for pz in plan.passes:
             self._launch(pz)
             if crosses:
                 for op, addr_v, addr_i, count in pz.results:

@@ -41,6 +41,7 @@ class DryRunBackend(B200Backend):
         self._min_dims = 2
         self._planner = Planner(sm_count)
         self._temps, self._temps_used = {}, {}
+        self._plans = {}
         self._next = 0x7F0000000000
         self.launches = 0
         self.passes = []            # every Pass planned so far
