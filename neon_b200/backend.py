@@ -376,23 +376,6 @@ class B200Backend(OpTreeBackend):
     def fill_normal(self, ary, mean=0, stdv=1):
         ary[:] = (self.rng.standard_normal(ary.shape) * stdv + mean).astype(ary.dtype)
 
-    # ------------------------------------------------------------------ thin op-tree wrappers (nervanagpu.py:3179-3231)
-    def fprop_relu(self, layer, x, slope):
-        return self.maximum(x, 0) + slope * self.minimum(0, x)
-
-    def bprop_relu(self, layer, x, error, deltas, slope):
-        return self.greater(x, 0) + slope * self.less(x, 0)
-
-    def fprop_softmax(self, x, axis):
-        return (self.reciprocal(self.sum(self.exp(x - self.max(x, axis=axis)), axis=axis)) *
-                self.exp(x - self.max(x, axis=axis)))
-
-    def fprop_skipnode(self, x, y, beta):
-        y[:] = y * beta + x
-
-    def bprop_skipnode(self, error, deltas, alpha, beta):
-        deltas[:] = deltas * beta + alpha * error
-
     # ------------------------------------------------------------------ timing marks (nervanagpu.py:3138-3177)
     def init_mark(self):
         ev = rt.event_create()

@@ -468,11 +468,17 @@ class _Fields(object):
         return f
 
     def pack(self, values=None):
+        """The kernel's parameter block.  The layout is frozen at the first call."""
+        packer = getattr(self, "_packer", None)
+        if packer is None:
+            self._names = self.names()
+            self._pad = len(self.f4) % 2
+            packer = self._packer = struct.Struct(self.fmt())
         values = self.values if values is None else values
-        vals = [values[n] for n in self.names()]
-        if len(self.f4) % 2:
+        vals = [values[n] for n in self._names]
+        if self._pad:
             vals.append(0)
-        return struct.pack(self.fmt(), *vals)
+        return packer.pack(*vals)
 
 
 class Pass(object):

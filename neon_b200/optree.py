@@ -438,6 +438,140 @@ class OpTreeBackend(object):
         t[:] = 0
         return t
 
+    # ---- plumbing the layer classes call on every backend (backend.py:533-700);
+    #      single-device backends answer with the neutral values
+    def set_caffe_compat(self):
+        self.compat_mode = "caffe"
+
+    def check_caffe_compat(self):
+        return self.compat_mode == "caffe"
+
+    def shared_iobuf_size(self, shape, parallelism):
+        num_dev = 1 if parallelism in ("Data", "Model") else getattr(self, "num_dev", 1)
+        return num_dev * int(np.prod(shape))
+
+    def distribute_data(self, tensor, layer_parallelism):
+        return None
+
+    def convert_data(self, tensor, layer_mkl):
+        return None
+
+    def clean_data(self, tensor, layer_mkl):
+        return None
+
+    def allocate_new_deltas(self, delta, in_shape, parallelism):
+        return delta
+
+    def allocate_new_outputs(self, layer, share_output):
+        layer.allocate(shared_outputs=share_output)
+
+    def is_mkl(self):
+        return False
+
+    def revert_tensor(self, tensor):
+        pass
+
+    def begin(self, block, identifier):
+        pass
+
+    def end(self, block, identifier):
+        pass
+
+    # ---- layer entry points that are op-trees on the GPU backend
+    #      (nervanagpu.py:3179-3231)
+    def relu_layer(self):
+        return None
+
+    def batchnorm_layer(self, in_shape):
+        return None
+
+    def mergesum_layer(self, layer_num):
+        return None
+
+    def mergebroadcast_layer(self, layer_num):
+        return None
+
+    def fprop_relu(self, layer, x, slope):
+        return self.maximum(x, 0) + slope * self.minimum(0, x)
+
+    def bprop_relu(self, layer, x, error, deltas, slope):
+        return self.greater(x, 0) + slope * self.less(x, 0)
+
+    def fprop_softmax(self, x, axis):
+        return (self.reciprocal(self.sum(self.exp(x - self.max(x, axis=axis)), axis=axis)) *
+                self.exp(x - self.max(x, axis=axis)))
+
+    def fprop_transform(self, ngLayer, transform, inputs, outputs, relu=False):
+        outputs[:] = transform(inputs)
+
+    def bprop_transform(self, ngLayer, transform, outputs, error, deltas, relu):
+        deltas[:] = transform.bprop(outputs) * error
+
+    def fprop_skipnode(self, x, y, beta):
+        y[:] = y * beta + x
+
+    def bprop_skipnode(self, error, deltas, alpha, beta):
+        deltas[:] = deltas * beta + alpha * error
+
+    def fprop_mergesum(self, ngLayer, inputs, inference, layers, outputs, out_shape):
+        for l in layers:
+            l.fprop(inputs, inference, beta=0 if l is layers[0] else 1)
+
+    def bprop_mergesum(self, ngLayer, alpha, beta, layers, error, deltas):
+        for l in reversed(layers):
+            l.bprop(error, alpha=alpha, beta=beta if l is layers[-1] else 1)
+
+    def fprop_mergebroadcast(self, ngLayer, inputs, inference, outputs, layers, out_shape):
+        for l in layers:
+            l.fprop(inputs, inference)
+
+    def bprop_mergebroadcast(self, ngLayer, layers, error_views, error, delta, out_shape,
+                             alpha, beta, alphas, betas):
+        betas[-1] = beta
+        for l, e, a, b in reversed(list(zip(layers, error_views, alphas, betas))):
+            l.bprop(e, alpha=a * alpha, beta=b)
+
+    # ---- batch normalisation as the BatchNorm layer calls it (layers/layer.py:2483-2520).
+    #      Semantics of the fused GPU kernels (cuda_batchnorm.py:27-219 and 222-431,
+    #      nervanagpu.py:2463-2547), expressed as op-tree statements: xsum stays the
+    #      batch *sum*, the variance is the centred second moment, xhat multiplies by
+    #      the reciprocal root.
+    def compound_fprop_bn(self, x, xsum, xvar, gmean, gvar, gamma, beta, y, eps, rho,
+                          compute_batch_sum, accumbeta=0.0, relu=False, threads=None, repeat=1,
+                          binary=False, inference=False, outputs=None, layer=None):
+        if binary:
+            raise NotImplementedError("binary (shift based) batch normalisation")
+        if inference:
+            xhat = (x - gmean) / self.sqrt(gvar + eps)
+            y[:] = y * accumbeta + xhat * gamma + beta
+            return
+        if compute_batch_sum:
+            xsum[:] = self.sum(x, axis=1)
+        rcp_n = 1.0 / x.shape[1]
+        xmean = xsum * rcp_n
+        xvar[:] = self.sum(self.square(x - xmean), axis=1) * rcp_n
+        gmean[:] = gmean * rho + (1.0 - rho) * xmean
+        gvar[:] = gvar * rho + (1.0 - rho) * xvar
+        val = (x - xmean) * self.reciprocal(self.sqrt(xvar + eps)) * gamma + beta
+        if relu:
+            val = self.maximum(val, 0)
+        out = y.reshape(x.shape)
+        if accumbeta != 0.0:
+            val = out * accumbeta + val
+        out[:] = val
+
+    def compound_bprop_bn(self, delta_out, grad_gamma, grad_beta, delta_in, x, xsum, xvar,
+                          gamma, eps, threads=None, repeat=1, binary=False, layer=None):
+        if binary:
+            raise NotImplementedError("binary (shift based) batch normalisation")
+        rcp_n = 1.0 / x.shape[1]
+        rstd = self.reciprocal(self.sqrt(xvar + eps))
+        xhat = (x - xsum * rcp_n) * rstd
+        grad_gamma[:] = self.sum(xhat * delta_in, axis=1)
+        grad_beta[:] = self.sum(delta_in, axis=1)
+        xtmp = (xhat * grad_gamma + grad_beta) * rcp_n
+        delta_out.reshape(delta_in.shape)[:] = (delta_in - xtmp) * gamma * rstd
+
     def update_fc_bias(self, err, out):
         """out = sum(err, axis=1) (backend.py:1539-1547)."""
         self.sum(err, axis=1, out=out)

@@ -42,6 +42,7 @@ class DryRunBackend(B200Backend):
         self._planner = Planner(sm_count)
         self._temps, self._temps_used = {}, {}
         self._plans = {}
+        self.compat_mode = None
         self._next = 0x7F0000000000
         self.launches = 0
         self.passes = []            # every Pass planned so far
@@ -76,6 +77,11 @@ class DryRunBackend(B200Backend):
         return self.empty(shape, dtype=dtype)
 
     ones = zeros
+
+    def empty_like(self, other, name=None, persist_values=True):
+        return self.empty(other.shape, dtype=other.dtype)
+
+    zeros_like = empty_like
 
     def _run(self, out, expr):
         stack = OpTreeNode({"op": "assign"}, out, expr).traverse([])
