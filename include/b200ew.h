@@ -161,6 +161,16 @@ uint64_t    b200_reduce_scratch_bytes(void);
 b200_status b200_reduce_full(uint64_t in, int32_t dtype, uint64_t count, int32_t op, int32_t absolute,
                              uint64_t out, uint64_t scratch, uint64_t stream);
 
+/* ---- matrix product for `dot` nodes inside op-trees
+ * stands in for compound_dot on the op-tree path only (neon/backends/nervanagpu.py:1123-1146,
+ * 1275-1281, 1441-1622): C = alpha * A.B + beta * C with element strides (so transposed views
+ * work), f32/f16 operands, fp32 accumulation.  A plain shared-memory tiled kernel: it is there
+ * so that trees containing dot evaluate, not to compete with the SASS GEMMs of the reference. */
+b200_status b200_gemm(uint64_t a, int32_t a_dtype, int64_t a_stride0, int64_t a_stride1,
+                      uint64_t b, int32_t b_dtype, int64_t b_stride0, int64_t b_stride1,
+                      uint64_t c, int32_t c_dtype, int64_t c_stride0, int64_t c_stride1,
+                      int32_t m, int32_t n, int32_t k, float alpha, float beta, uint64_t stream);
+
 /* ---- the same reduction for callers that cannot allocate device memory
  * No counterpart in the reference.  Meant for hosts where cudaMalloc is off
  * limits when the call is made (a framework pool owns the device, a latency-

@@ -163,9 +163,16 @@ class B200Backend(OpTreeBackend):
         expr, tag = self._split(rhs, stmts)
         if tag == "flat" and tuple(out.shape) != (1, 1):
             expr = self._materialise(expr, (1, 1), stmts)
-        for dst, tree in stmts:
-            self._run(dst, tree)
-        self._run(out, expr)
+        if type(expr) is tuple:                 # the whole right-hand side is a dot
+            stmts.append((out,) + expr[1:])
+            expr = None
+        for stmt in stmts:
+            if len(stmt) == 3:
+                self.compound_dot(stmt[1], stmt[2], stmt[0])
+            else:
+                self._run(stmt[0], stmt[1])
+        if expr is not None:
+            self._run(out, expr)
         return out
 
     # -- splitting ----------------------------------------------------------------
@@ -181,8 +188,15 @@ class B200Backend(OpTreeBackend):
         return pool[used]
 
     def _materialise(self, expr, shape, stmts):
+        if type(expr) is tuple:
+            return self._finish_dot(expr, stmts)
         buf = self._temp(shape)
         stmts.append((buf, expr))
+        return buf
+
+    def _finish_dot(self, dot, stmts):
+        buf = self._temp((dot[1].shape[0], dot[2].shape[1]))
+        stmts.append((buf, dot[1], dot[2]))
         return buf
 
     @staticmethod
@@ -240,22 +254,42 @@ class B200Backend(OpTreeBackend):
                 operand = self._materialise(OpTreeNode(child[0], inner, None), child[0]["shape"], stmts)
                 return OpTreeNode(info, operand, None), axis
             operand, prev = self._split(child, stmts)
+            if type(operand) is tuple:
+                operand = self._finish_dot(operand, stmts)
             if prev is not None and prev != axis:
                 shape = (1, 1) if prev == "flat" else operand.shape
                 operand = self._materialise(operand, shape, stmts)
             return OpTreeNode(info, operand, None), axis
         if op == "transpose":
             operand, _ = self._split(node[1], stmts)
+            if type(operand) is tuple:
+                operand = self._finish_dot(operand, stmts)
             if isinstance(operand, Tensor):
                 return operand.T, None
             return self._materialise(operand, operand.shape, stmts).T, None
         if op == "dot":
-            raise NotImplementedError("dot inside an op-tree is outside this backend's op-tree path")
+            # operands and result live in tensors; the product is its own launch
+            # (nervanagpu.py:1123-1146)
+            sides = []
+            for child in (node[1], node[2]):
+                operand, tag = self._split(child, stmts)
+                if type(operand) is tuple:
+                    operand = self._finish_dot(operand, stmts)
+                if not isinstance(operand, Tensor):
+                    operand = self._materialise(operand, (1, 1) if tag == "flat" else operand.shape, stmts)
+                sides.append(operand)
+            return ("dot", sides[0], sides[1]), None
         if op in OpCollection.unary_ops or node[2] is None:
             operand, tag = self._split(node[1], stmts)
+            if type(operand) is tuple:
+                operand = self._finish_dot(operand, stmts)
             return OpTreeNode(info, operand, None), tag
         left, lt = self._split(node[1], stmts)
         right, rt_ = self._split(node[2], stmts)
+        if type(left) is tuple:
+            left = self._finish_dot(left, stmts)
+        if type(right) is tuple:
+            right = self._finish_dot(right, stmts)
         if lt is not None and rt_ is not None and lt != rt_:
             # two sides reduce differently: evaluate one of them first.  A flat side
             # is a (1,1) value; otherwise the side reducing along axis 0 goes first
@@ -407,7 +441,20 @@ class B200Backend(OpTreeBackend):
     def _off_path(self, *a, **k):
         raise NotImplementedError("outside the compound op-tree path of the b200 backend")
 
-    compound_dot = batched_dot = conv_layer = deconv_layer = fprop_conv = bprop_conv = _off_path
+    def compound_dot(self, A, B, C, alpha=1.0, beta=0.0, relu=False, bsum=None):
+        """C = alpha * A.B + beta * C for `dot` nodes of op-trees (plain tiled kernel;
+        the reference's SASS GEMM path, nervanagpu.py:1441-1622, is not rebuilt)."""
+        if relu or bsum is not None:
+            raise NotImplementedError("fused relu / batch-sum epilogues of the GEMM path")
+        assert A.shape[1] == B.shape[0] and C.shape == (A.shape[0], B.shape[1])
+        from .lowering import dtype_code
+        rt.gemm(A.ptr, dtype_code(A.dtype), A.strides, B.ptr, dtype_code(B.dtype), B.strides,
+                C.ptr, dtype_code(C.dtype), C.strides, A.shape[0], B.shape[1], A.shape[1],
+                float(alpha), float(beta), self.stream)
+        self.launches += 1
+        return C
+
+    batched_dot = conv_layer = deconv_layer = fprop_conv = bprop_conv = _off_path
     update_conv = pool_layer = fprop_pool = bprop_pool = compound_bprop_lut = _off_path
 
 

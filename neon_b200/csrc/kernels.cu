@@ -66,7 +66,66 @@ cudaError_t launch_full_dt(const RP& p, int op, bool absolute, bool vec, unsigne
     return absolute ? launch_full<DT, b200::OP_MIN, true>(p, vec, grid, s) : launch_full<DT, b200::OP_MIN, false>(p, vec, grid, s);
 }
 
+// ---- plain tiled GEMM for `dot` nodes inside op-trees (conformance, not a performance path):
+// C[m,n] = alpha * sum_k A[m,k] * B[k,n] + beta * C[m,n], any element strides, fp32 accumulation
+struct GemmP {
+    u64 a, b, c;
+    i64 a_s0, a_s1, b_s0, b_s1, c_s0, c_s1;
+    int m, n, k, pad_;
+    float alpha, beta;
+};
+
+template <int DA, int DB, int DC>
+__global__ void __launch_bounds__(256) gemm_kernel(const __grid_constant__ GemmP p) {
+    __shared__ float sa[16][17], sb[16][17];
+    const int tx = threadIdx.x % 16, ty = threadIdx.x / 16;
+    const int row = blockIdx.y * 16 + ty, col = blockIdx.x * 16 + tx;
+    float acc = 0.f;
+    for (int k0 = 0; k0 < p.k; k0 += 16) {
+        float va = 0.f, vb = 0.f;
+        if (row < p.m && k0 + tx < p.k) b200::ld_f<DA, 1, false>(p.a, (i64)row * p.a_s0 + (i64)(k0 + tx) * p.a_s1, &va);
+        if (k0 + ty < p.k && col < p.n) b200::ld_f<DB, 1, false>(p.b, (i64)(k0 + ty) * p.b_s0 + (i64)col * p.b_s1, &vb);
+        sa[ty][tx] = va; sb[ty][tx] = vb;
+        __syncthreads();
+#pragma unroll
+        for (int kk = 0; kk < 16; ++kk) acc = fmaf(sa[ty][kk], sb[kk][tx], acc);
+        __syncthreads();
+    }
+    if (row < p.m && col < p.n) {
+        const i64 o = (i64)row * p.c_s0 + (i64)col * p.c_s1;
+        float prev = 0.f;
+        if (p.beta != 0.f) b200::ld_f<DC, 1, false>(p.c, o, &prev);
+        b200::st_one<DC>(p.c, o, p.alpha * acc + p.beta * prev);
+    }
+}
+
+template <int DA, int DB>
+cudaError_t launch_gemm_c(const GemmP& p, int dc, dim3 grid, cudaStream_t s) {
+    if (dc == B200_F32) gemm_kernel<DA, DB, b200::F32><<<grid, 256, 0, s>>>(p);
+    else gemm_kernel<DA, DB, b200::F16><<<grid, 256, 0, s>>>(p);
+    return cudaGetLastError();
+}
+
 }  // namespace
+
+extern "C" int b200_detail_gemm(uint64_t a, int da, int64_t a_s0, int64_t a_s1,
+                                uint64_t b, int db, int64_t b_s0, int64_t b_s1,
+                                uint64_t c, int dc, int64_t c_s0, int64_t c_s1,
+                                int m, int n, int k, float alpha, float beta, void* stream) {
+    GemmP p;
+    p.a = a; p.b = b; p.c = c;
+    p.a_s0 = a_s0; p.a_s1 = a_s1; p.b_s0 = b_s0; p.b_s1 = b_s1; p.c_s0 = c_s0; p.c_s1 = c_s1;
+    p.m = m; p.n = n; p.k = k; p.pad_ = 0; p.alpha = alpha; p.beta = beta;
+    dim3 grid((n + 15) / 16, (m + 15) / 16, 1);
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    const bool af = da == B200_F32, bf = db == B200_F32;
+    cudaError_t e;
+    if (af && bf) e = launch_gemm_c<b200::F32, b200::F32>(p, dc, grid, s);
+    else if (af) e = launch_gemm_c<b200::F32, b200::F16>(p, dc, grid, s);
+    else if (bf) e = launch_gemm_c<b200::F16, b200::F32>(p, dc, grid, s);
+    else e = launch_gemm_c<b200::F16, b200::F16>(p, dc, grid, s);
+    return (int)e;
+}
 
 enum { kMaxSplit = 4096, kCounterBytes = 256 };
 

@@ -148,6 +148,10 @@ extern "C" int b200_detail_fill(void *dst, uint32_t value, int width, uint64_t c
 extern "C" int b200_detail_reduce_full(uint64_t in, int32_t dtype, uint64_t count, int32_t op, int32_t absolute,
                                        uint64_t out, uint64_t scratch, int sm_count, void *stream);
 
+extern "C" int b200_detail_gemm(uint64_t a, int da, int64_t a_s0, int64_t a_s1, uint64_t b, int db, int64_t b_s0,
+                                int64_t b_s1, uint64_t c, int dc, int64_t c_s0, int64_t c_s1, int m, int n, int k,
+                                float alpha, float beta, void *stream);
+
 // helpers for the other translation units of the library
 extern "C" void *b200_detail_stream(uint64_t stream) { return stream ? reinterpret_cast<void *>(stream) : g.stream; }
 extern "C" int32_t b200_detail_fail(int32_t code, const char *message) { return fail(code, "%s", message); }
@@ -617,6 +621,23 @@ b200_status b200_reduce_full(uint64_t in, int32_t dtype, uint64_t count, int32_t
     if (!sms) CU(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, g.device));
     int e = b200_detail_reduce_full(in, dtype, count, op, absolute, out, scratch, sms, as_stream(stream));
     if (e) return fail(B200_ERR_CUDA, "reduce kernel: %s", cudaGetErrorString((cudaError_t)e));
+    return B200_OK;
+}
+
+// ---------------------------------------------------------------- small GEMM
+b200_status b200_gemm(uint64_t a, int32_t a_dtype, int64_t a_stride0, int64_t a_stride1,
+                      uint64_t b, int32_t b_dtype, int64_t b_stride0, int64_t b_stride1,
+                      uint64_t c, int32_t c_dtype, int64_t c_stride0, int64_t c_stride1,
+                      int32_t m, int32_t n, int32_t k, float alpha, float beta, uint64_t stream) {
+    if (g.device < 0) return fail(B200_ERR_INVALID, "b200_init has not been called");
+    if (!a || !b || !c) return fail(B200_ERR_INVALID, "null device pointer");
+    if (m <= 0 || n <= 0 || k <= 0) return fail(B200_ERR_INVALID, "empty matrix");
+    for (int dt : {a_dtype, b_dtype, c_dtype})
+        if (dt != B200_F32 && dt != B200_F16) return fail(B200_ERR_UNSUPPORTED, "gemm operands must be f32 or f16");
+    if ((m + 15) / 16 > 65535) return fail(B200_ERR_UNSUPPORTED, "more than 1048560 rows");
+    int e = b200_detail_gemm(a, a_dtype, a_stride0, a_stride1, b, b_dtype, b_stride0, b_stride1,
+                             c, c_dtype, c_stride0, c_stride1, m, n, k, alpha, beta, as_stream(stream));
+    if (e) return fail(B200_ERR_CUDA, "gemm kernel: %s", cudaGetErrorString((cudaError_t)e));
     return B200_OK;
 }
 

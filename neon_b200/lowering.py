@@ -119,10 +119,12 @@ class Node(object):
 
 class Operand(object):
     """A distinct tensor of the statement: pointer, dtype, 2-d shape, element strides."""
-    __slots__ = ("tensor", "ptr", "dt", "shape", "strides", "alias_out", "span", "_frame_strides")
+    __slots__ = ("tensor", "ptr", "dt", "shape", "strides", "alias_out", "span", "_frame_strides", "take")
 
     def __init__(self, tensor, shape, strides):
         self.tensor = tensor
+        # fancy-indexed view: (address of the int32 index vector, tensor axis it replaces)
+        self.take = (int(tensor.take_array[0].ptr), tensor.take_array[1]) if tensor.take_array else None
         self.ptr = int(tensor.ptr)
         self.dt = dtype_code(tensor.dtype)
         self.shape = tuple(shape)
@@ -141,10 +143,11 @@ class Operand(object):
 
 class _Pseudo(object):
     """Operand-like view of a reduction result held in scratch."""
-    __slots__ = ("ptr", "dt", "shape", "strides", "alias_out", "_frame_strides")
+    __slots__ = ("ptr", "dt", "shape", "strides", "alias_out", "_frame_strides", "take")
 
     def __init__(self, ptr, dt, shape):
         self.ptr, self.dt, self.shape = ptr, dt, tuple(shape)
+        self.take = None
         self.strides = (1, 1)           # a vector: the extent-1 axis is zeroed by the frame
         self.alias_out = True           # written by an earlier launch: plain loads
 
@@ -183,7 +186,8 @@ def program_key(stack):
     for s in stack:
         if isinstance(s, Tensor):
             ix = seen.setdefault(id(s), len(seen))
-            key.append((ix, s.dtype.char, s.shape, s.strides, s.ptr & 15, bool(s.take_array),
+            key.append((ix, s.dtype.char, s.shape, s.strides, s.ptr & 15,
+                        s.take_array[1] if s.take_array else None,
                         s is not out and shares_memory(s, out)))
         elif type(s) is dict:
             idx = s.get("idx")
@@ -201,19 +205,25 @@ class BoundPlan(object):
         self.passes = passes
         self.binds = []
         for pz in passes:
-            ptrs, consts = [], []
+            ptrs, consts, takes = [], [], []
             for name in pz.fields.names():
                 if name == "o":
                     ptrs.append((name, 0))
+                elif name == "o_take":
+                    takes.append((name, 0))
+                elif name[0] == "t" and name.endswith("_take"):
+                    takes.append((name, st.tensor_pos[int(name[1:-5])]))
                 elif name[0] == "t" and name[1:].isdigit():
                     ptrs.append((name, st.tensor_pos[int(name[1:])]))
                 elif name[0] == "c" and name[1:].isdigit():
                     consts.append((name, st.nodes[int(name[1:])].extra))
-            self.binds.append((ptrs, consts))
+            self.binds.append((ptrs, consts, takes))
 
     def rebind(self, stack):
-        for pz, (ptrs, consts) in zip(self.passes, self.binds):
+        for pz, (ptrs, consts, takes) in zip(self.passes, self.binds):
             vals = pz.fields.values
+            for name, pos in takes:
+                vals[name] = stack[pos].take_array[0].ptr
             for name, pos in ptrs:
                 obj = stack[pos]
                 vals[name] = (obj["idx"] if type(obj) is dict else obj).ptr
@@ -236,8 +246,6 @@ class Statement(object):
         out = stack[0]
         if not isinstance(out, Tensor):
             raise TypeError("first element of the program must be the output tensor")
-        if out.take_array:
-            raise NotImplementedError("assignment into a fancy-indexed view")
         self.out_tensor = out
 
         # ---- pass 1 (float_ew.py:672-707): reduction axis and simple-elementwise test
@@ -256,8 +264,6 @@ class Statement(object):
                 elif op in ("onehot", "rand"):
                     flat_ok = False
             elif isinstance(s, Tensor):
-                if s.take_array:
-                    raise NotImplementedError("fancy-indexed operands")
                 if not _fast_flat_ok(s, out.shape):
                     if not (tuple(s.shape) == (1, 1) and s is not out):
                         flat_ok = False
@@ -569,6 +575,8 @@ class Planner(object):
         of a cluster of at most 8 blocks.  Returns None when that does not apply."""
         K, N = full_shape[ka], full_shape[ra]
         if rounding or any(n.kind == "z" for n in st.nodes):
+            return None
+        if st.out.take is not None or any(o.take is not None for o in st.operands):
             return None
         n_passes = len(levels) + (0 if red_out else 1)
         if n_passes < 2:
@@ -893,7 +901,29 @@ class Planner(object):
             self.f.u64(pre, o.ptr)
             self.f.i64(pre + "_sk", sk)
             self.f.i64(pre + "_sn", sn)
+            if o.take is not None:
+                self.f.u64(pre + "_take", o.take[0])
+                if o.take[1] == (self.ka if self.lk else self.ra):
+                    # gather along the lanes: no vector access for this operand
+                    o._frame_strides = (sk, sn) if False else ((0x7fffffff, sn) if self.lk else (sk, 0x7fffffff))
             return o, pre
+
+        def _off(self, o, pre, vec):
+            """Element offset of (k, n) in operand ``pre``; ``vec``: a V-wide access
+            (unit stride along the lanes when V > 1)."""
+            kk, nn = "k * p.%s_sk" % pre, "n * p.%s_sn" % pre
+            if vec and self.lk:
+                kk = "(V > 1 ? k : k * p.%s_sk)" % pre
+            elif vec:
+                nn = "(V > 1 ? n : n * p.%s_sn)" % pre
+            if o.take is not None:
+                if o.take[1] == self.ka:
+                    kk = "(i64)ld_idx(p.%s_take, k) * p.%s_sk" % (pre, pre)
+                else:
+                    nn = "(i64)ld_idx(p.%s_take, n) * p.%s_sn" % (pre, pre)
+            if self.st.flat:
+                return "n"
+            return "%s + %s" % (kk, nn)
 
         # value of node for use in hoisted (per-k) code; scope 'h'
         def hoist(self, n):
@@ -914,12 +944,16 @@ class Planner(object):
                 nc = "false" if (o.alias_out or self.no_nc) else "true"
                 if self.lk and self.var_k(n):
                     self.lane_ops.append((o, "k"))
-                    self.h_lines.append("float %s[V]; ld_f<%s, V, %s>(p.%s, k * p.%s_sk, %s);"
-                                        % (name, DT_NAMES[o.dt], nc, pre, pre, name))
+                    koff = "(i64)ld_idx(p.%s_take, k) * p.%s_sk" % (pre, pre) \
+                        if (o.take is not None and o.take[1] == self.ka) else "k * p.%s_sk" % pre
+                    self.h_lines.append("float %s[V]; ld_f<%s, V, %s>(p.%s, %s, %s);"
+                                        % (name, DT_NAMES[o.dt], nc, pre, koff, name))
                     ref = name + "[i]"
                 else:
-                    self.h_lines.append("float %s[1]; ld_f<%s, 1, %s>(p.%s, k * p.%s_sk, %s);"
-                                        % (name, DT_NAMES[o.dt], nc, pre, pre, name))
+                    koff = "(i64)ld_idx(p.%s_take, k) * p.%s_sk" % (pre, pre) \
+                        if (o.take is not None and o.take[1] == self.ka) else "k * p.%s_sk" % pre
+                    self.h_lines.append("float %s[1]; ld_f<%s, 1, %s>(p.%s, %s, %s);"
+                                        % (name, DT_NAMES[o.dt], nc, pre, koff, name))
                     ref = name + "[0]"
                 self.names[key] = ref
                 return ref
@@ -974,20 +1008,14 @@ class Planner(object):
                 if lane_var:
                     self.lane_ops.append((o, "k" if self.lk else "n"))
                     self.l_decl.append("u32 %s[(%d * V + 3) / 4];" % (aname, DT_SIZE[o.dt]))
-                    # with V > 1 the host guarantees unit stride along the lanes
-                    if self.lk:
-                        off = "(V > 1 ? k : k * p.%s_sk) + n * p.%s_sn" % (pre, pre)
-                    elif self.st.flat:
-                        off = "n"
-                    else:
-                        off = "k * p.%s_sk + (V > 1 ? n : n * p.%s_sn)" % (pre, pre)
+                    off = self._off(o, pre, True)
                     self.l_lines.append("ld_w<%s, V, %s>(p.%s, %s, l.%s);" % (DT_NAMES[o.dt], nc, pre, off, aname))
                     self.e_pre.append("float %s[V]; cvt_in<%s, V>(l.%s, %s);" % (aname, DT_NAMES[o.dt], aname, aname))
                     ref = aname + "[i]"
                 else:
                     self.l_decl.append("u32 %s[1];" % aname)
-                    self.l_lines.append("ld_w<%s, 1, %s>(p.%s, k * p.%s_sk + n * p.%s_sn, l.%s);"
-                                        % (DT_NAMES[o.dt], nc, pre, pre, pre, aname))
+                    self.l_lines.append("ld_w<%s, 1, %s>(p.%s, %s, l.%s);"
+                                        % (DT_NAMES[o.dt], nc, pre, self._off(o, pre, False), aname))
                     self.e_pre.append("float %s[1]; cvt_in<%s, 1>(l.%s, %s);" % (aname, DT_NAMES[o.dt], aname, aname))
                     ref = aname + "[0]"
                 self.names[key] = ref
@@ -1063,6 +1091,8 @@ class Planner(object):
                 sk = 0
             if o.shape[ra] == 1:
                 sn = 0
+            if o.take is not None and o.take[1] == ra:
+                sn = 0x7fffffff                 # gathered along the loop axis: never a vector access
             o._frame_strides = (sk, sn)
 
     # ---- passes -----------------------------------------------------------------
@@ -1096,12 +1126,16 @@ class Planner(object):
             odt = st.out.dt
             f.u64("o", st.out.ptr)
             f.i64("o_sk", st.out._frame_strides[0])
+            ko = "k * p.o_sk"
+            if st.out.take is not None and st.out.take[1] == ka:
+                f.u64("o_take", st.out.take[0])
+                ko = "(i64)ld_idx(p.o_take, k) * p.o_sk"
             if st.root.kind == "r" and st.root.op.startswith("arg"):
                 val = None
-                store = "st_index<%s>(p.o, k * p.o_sk, ri[%d]);" % (DT_NAMES[odt], fresh[st.root.nid])
+                store = "st_index<%s>(p.o, %s, ri[%d]);" % (DT_NAMES[odt], ko, fresh[st.root.nid])
             else:
                 val = ep.hoist(st.root)
-                store = "{ const int i = 0; (void)i; st_one<%s>(p.o, k * p.o_sk, %s); }" % (DT_NAMES[odt], val)
+                store = "{ const int i = 0; (void)i; st_one<%s>(p.o, %s, %s); }" % (DT_NAMES[odt], ko, val)
             ep_lines = ep.h_lines + [store]
         else:
             for r in reds:
@@ -1193,7 +1227,7 @@ class Planner(object):
         odt = st.out.dt
         f.u64("o", st.out.ptr)
         f.i64("o_sk", st.out._frame_strides[0])
-        f.i64("o_sn", st.out._frame_strides[1])
+        f.i64("o_sn", st.out.strides[ra] if st.out.shape[ra] > 1 else 0)
         f.i64("K", K)
         f.i64("N", N)
         nvec = N // V
@@ -1201,6 +1235,12 @@ class Planner(object):
         sr = bool(rounding)
         st_lines = []
         o_off = "n" if st.flat else "k * p.o_sk + (V > 1 ? n : n * p.o_sn)"
+        if st.out.take is not None:
+            f.u64("o_take", st.out.take[0])
+            if st.out.take[1] == ka:
+                o_off = "(i64)ld_idx(p.o_take, k) * p.o_sk + (V > 1 ? n : n * p.o_sn)"
+            else:
+                o_off = "k * p.o_sk + (i64)ld_idx(p.o_take, n) * p.o_sn"
         if sr:
             em.uses_rng = True
             f.u32("rk0", 0)

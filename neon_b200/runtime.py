@@ -71,6 +71,8 @@ SIGNATURES = {
     "b200_rng_set_state": (i32, [P(u64)]),
     "b200_reduce_scratch_bytes": (u64, []),
     "b200_reduce_full": (i32, [u64, i32, u64, i32, i32, u64, u64, u64]),
+    "b200_gemm": (i32, [u64, i32, C.c_int64, C.c_int64, u64, i32, C.c_int64, C.c_int64,
+                        u64, i32, C.c_int64, C.c_int64, i32, i32, i32, C.c_float, C.c_float, u64]),
     "b200_reduce_full_noalloc_max_count": (u64, []),
     "b200_reduce_full_noalloc": (i32, [u64, i32, u64, i32, i32, u64, u64]),
     "b200_comm_unique_id": (i32, [P(C.c_uint8)]),
@@ -312,6 +314,11 @@ def reduce_scratch_bytes():
 
 def reduce_full(src, dtype, count, op, absolute, out, scratch, stream=0):
     check(lib().b200_reduce_full(src, dtype, count, op, 1 if absolute else 0, out, scratch, stream))
+
+
+def gemm(a, a_dt, a_strides, b, b_dt, b_strides, c, c_dt, c_strides, m, n, k, alpha=1.0, beta=0.0, stream=0):
+    check(lib().b200_gemm(a, a_dt, a_strides[0], a_strides[1], b, b_dt, b_strides[0], b_strides[1],
+                          c, c_dt, c_strides[0], c_strides[1], m, n, k, alpha, beta, stream))
 
 
 def reduce_full_noalloc(src, dtype, count, op, absolute, out, stream=0):

@@ -83,6 +83,12 @@ class DryRunBackend(B200Backend):
 
     zeros_like = empty_like
 
+    def compound_dot(self, A, B, C, alpha=1.0, beta=0.0, relu=False, bsum=None):
+        assert A.shape[1] == B.shape[0] and C.shape == (A.shape[0], B.shape[1])
+        self.launches += 1
+        self.dots = getattr(self, "dots", 0) + 1
+        return C
+
     def _run(self, out, expr):
         stack = OpTreeNode({"op": "assign"}, out, expr).traverse([])
         st = Statement(stack)

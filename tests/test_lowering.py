@@ -94,3 +94,18 @@ def test_unaligned_views_fall_back_to_narrower_vectors():
     out = be.empty((64, 99))
     out[:] = x[:, 1:] * 2.0                              # 4-byte aligned only, odd row length
     assert "V=1" in be.passes[-1].desc
+
+
+def test_dot_inside_an_op_tree_is_split_into_its_own_launch():
+    """tests/test_backend_compound_optree.py:39-58 builds trees around be.dot."""
+    be = DryRunBackend()
+    be.compile = False
+    a, b, c = be.empty((20, 30)), be.empty((30, 40)), be.empty((20, 40))
+    out = be.empty((20, 40))
+    out[:] = be.dot(a, b)
+    assert be.dots == 1 and not be.passes
+    out[:] = be.dot(a * 2.0, b) + c
+    assert be.dots == 2 and [p.kind for p in be.passes] == ["ew_flat", "ew_flat"]
+    col = be.empty((20, 1))
+    col[:] = be.sum(be.dot(a, b.T.T if False else b), axis=1) * 0.5
+    assert be.dots == 3

@@ -268,6 +268,97 @@ def test_rng_reproducible_after_reset_and_state_restore(b200):
     assert set(np.unique(m).tolist()) <= {0.0, 1.0} and abs(m.mean() - 0.3) < 0.02
 
 
+def test_take_addressing(b200):
+    """Fancy-indexed operands and outputs (neon in1/in2/out1/out2 modes,
+    cuda_templates.py:448-478); LookupTable.fprop is ``out[:] = W.take(idx, axis=0)``."""
+    be = b200
+    rng = np.random.RandomState(4)
+    Wh = rng.randn(1000, 64).astype(np.float32)
+    ih = rng.randint(0, 1000, (1, 200)).astype(np.int32)
+    W, idx = be.array(Wh), be.array(ih, dtype=np.int32)
+    out = be.empty((200, 64))
+    out[:] = W.take(idx, axis=0)
+    assert np.array_equal(out.get(), Wh[ih[0]])
+    Wt = be.array(np.ascontiguousarray(Wh.T))
+    o2 = be.empty((64, 200))
+    o2[:] = Wt.take(idx, axis=1) * 2.0 + 1.0
+    assert np.allclose(o2.get(), Wh.T[:, ih[0]] * 2.0 + 1.0, rtol=1e-6)
+    s = be.empty((1, 64))
+    s[:] = be.sum(W.take(idx, axis=0), axis=0)
+    np.testing.assert_allclose(s.get(), Wh[ih[0]].sum(0, keepdims=True), rtol=1e-5, atol=1e-5)
+    m = be.empty((200, 1))
+    m[:] = be.max(W.take(idx, axis=0), axis=1)
+    assert np.array_equal(m.get(), Wh[ih[0]].max(1, keepdims=True))
+    perm = rng.permutation(1000)[:200].astype(np.int32).reshape(1, -1)
+    dW = be.zeros((1000, 64))
+    dW[be.array(perm, dtype=np.int32), :] = out * 0.5
+    want = np.zeros((1000, 64), np.float32)
+    want[perm[0]] = Wh[ih[0]] * 0.5
+    assert np.array_equal(dW.get(), want)
+    # the plan cache re-aims at a new index vector
+    ih2 = rng.randint(0, 1000, (1, 200)).astype(np.int32)
+    out[:] = W.take(be.array(ih2, dtype=np.int32), axis=0)
+    assert np.array_equal(out.get(), Wh[ih2[0]])
+
+
+def _bn_case(rows, cols, dtype, relu, accumbeta):
+    def inputs(rng):
+        return {"x": (1.0 + 2.0 * rng.randn(rows, cols)).astype(dtype),
+                "delta": rng.randn(rows, cols).astype(dtype),
+                "gamma": rng.uniform(0.5, 1.5, (rows, 1)).astype(np.float32),
+                "beta": rng.uniform(-0.5, 0.5, (rows, 1)).astype(np.float32),
+                "gmean": rng.randn(rows, 1).astype(np.float32),
+                "gvar": rng.uniform(0.5, 1.5, (rows, 1)).astype(np.float32),
+                "y": rng.randn(rows, cols).astype(np.float32)}
+
+    def run(be, t):
+        be.compound_fprop_bn(t["x"], t["xsum"], t["xvar"], t["gmean"], t["gvar"], t["gamma"], t["beta"],
+                             t["y"], 1e-3, 0.9, True, accumbeta=accumbeta, relu=relu)
+        be.compound_bprop_bn(t["dx"], t["ggamma"], t["gbeta"], t["delta"], t["x"], t["xsum"], t["xvar"],
+                             t["gamma"], 1e-3)
+        t["yinf"][:] = 0
+        be.compound_fprop_bn(t["x"], t["xsum"], t["xvar"], t["gmean"], t["gvar"], t["gamma"], t["beta"],
+                             t["yinf"], 1e-3, 0.9, True, inference=True)
+
+    col = ((rows, 1), np.float32)
+    return cases.Case("compound_bn_%dx%d_%s_relu%d_acc%g" % (rows, cols, np.dtype(dtype).name, relu, accumbeta),
+                      inputs, {"xsum": col, "xvar": col, "ggamma": col, "gbeta": col,
+                               "dx": ((rows, cols), np.float32), "yinf": ((rows, cols), np.float32)}, run)
+
+
+@pytest.mark.parametrize("case", [_bn_case(32, 1024, np.float32, False, 0.0),
+                                  _bn_case(64, 50176, np.float16, True, 0.0),
+                                  _bn_case(16, 333, np.float32, False, 0.5)], ids=lambda c: c.name)
+def test_compound_batchnorm_entry_points(case, b200):
+    """The calls the BatchNorm layer makes (layers/layer.py:2483-2520) against the same
+    calls on the checker."""
+    got = cases.run_case(b200, case)
+    _compare(case, got, _oracle64(case))
+
+
+def test_dot_inside_op_trees(b200):
+    """Trees that contain a matrix product (tests/test_backend_compound_optree.py:39-58):
+    the product runs as its own launch between the fused element-wise statements."""
+    be = b200
+    rng = np.random.RandomState(9)
+    ah, bh, ch = rng.randn(37, 53).astype(np.float32), rng.randn(53, 29).astype(np.float32), rng.randn(37, 29).astype(np.float32)
+    a, b, c = be.array(ah), be.array(bh), be.array(ch)
+    out = be.empty((37, 29))
+    out[:] = be.dot(a, b)
+    np.testing.assert_allclose(out.get(), ah.dot(bh), rtol=1e-5, atol=1e-5)
+    out[:] = be.dot(a * 2.0, b) + c
+    np.testing.assert_allclose(out.get(), (ah * 2).dot(bh) + ch, rtol=1e-5, atol=1e-5)
+    col = be.empty((37, 1))
+    col[:] = be.sum(be.dot(a, b), axis=1) * 0.5
+    np.testing.assert_allclose(col.get(), ah.dot(bh).sum(1, keepdims=True) * 0.5, rtol=1e-5, atol=1e-4)
+    sq = be.empty((53, 53))
+    sq[:] = be.dot(a.T, a)
+    np.testing.assert_allclose(sq.get(), ah.T.dot(ah), rtol=1e-5, atol=1e-4)
+    h = be.array(ah.astype(np.float16), dtype=np.float16)
+    out[:] = be.dot(h, b)
+    np.testing.assert_allclose(out.get(), ah.astype(np.float16).astype(np.float32).dot(bh), rtol=1e-5, atol=1e-4)
+
+
 def test_onehot_and_views(b200):
     be = b200
     idx = np.random.RandomState(3).randint(0, 10, (1, 64)).astype(np.int32)
