@@ -761,30 +761,39 @@ template <int C> DEV void rr_begin(RowCtx& cx, i64 nvec, u64* bar) {
     __syncthreads();
 }
 // before the async copies overwrite the slice: all reads of the previous row are done
-DEV void rr_stage_begin(u64* bar, u32 total_bytes) {
+DEV void rr_stage_begin(const RowCtx& cx, u64* bar, u32 total_bytes) {
     __syncthreads();
-    if (threadIdx.x == 0) {
+    if (threadIdx.x == 0 && !cx.failed) {       // after a failed wait the barrier is left alone
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
         mbar_expect_tx(bar, total_bytes);
     }
 }
-DEV void rr_stage_copy(unsigned char* dst, u64 src, u32 bytes, u64* bar) {
-    if (threadIdx.x == 0) {
+DEV void rr_stage_copy(const RowCtx& cx, unsigned char* dst, u64 src, u32 bytes, u64* bar) {
+    if (threadIdx.x == 0 && !cx.failed) {
         for (u32 off = 0; off < bytes; off += 32768u) {
             const u32 n = bytes - off < 32768u ? bytes - off : 32768u;
             bulk_g2s(dst + off, reinterpret_cast<const char*>(src) + off, n, bar);
         }
     }
 }
-DEV void rr_stage_wait(RowCtx& cx, u64* bar, u64 status) {
-    bool done = false;
-    for (int spin = 0; spin < (1 << 22); ++spin) {
-        if (mbar_try_wait(bar, cx.phase)) { done = true; break; }
+DEV u64 global_ns() { u64 t; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t)); return t; }
+// Wait for the staged slice, for at most limit_ns.  When the time runs out the
+// block records it in *status, stops waiting for later rows as well (its results
+// are then meaningless, the host raises on the status) and keeps taking part in
+// every barrier so that its cluster peers are never left waiting.
+DEV void rr_stage_wait(RowCtx& cx, u64* bar, u64 status, u64 limit_ns) {
+    if (!cx.failed) {
+        const u64 t0 = global_ns();
+        bool done = false;
+        while (!(done = mbar_try_wait(bar, cx.phase))) {
+            if (global_ns() - t0 > limit_ns) break;
+        }
+        if (!done) {
+            cx.failed = true;
+            if (status) atomicExch(reinterpret_cast<int*>(status), 1);
+        }
     }
-    if (!done) {
-        cx.failed = true;
-        if (threadIdx.x == 0 && status) atomicExch(reinterpret_cast<int*>(status), 1);
-    }
+    cx.failed = __syncthreads_or(cx.failed) != 0;     // one verdict for the whole block
     cx.phase ^= 1;
 }
 

@@ -527,6 +527,8 @@ class Planner(object):
         self.smem_cap = 200 * 1024         # dynamic shared memory a row-resident block may ask for
         self.rowres_slice_cap = 100 * 1024 # preferred largest slice of a row per block (two blocks per SM)
         self.status_ptr = 0                # device int the kernels set when a bounded wait gives up
+        self.wait_limit_ns = 2000000000    # how long a block waits for its staged row slice
+        self.debug_starve_bytes = 0        # tests only: announce this many bytes that never arrive
         self.ew_unroll = 4
         self.ew_min_blocks = None          # None: 5 for instruction-heavy statements, else 4
 
@@ -668,6 +670,8 @@ class Planner(object):
         f.i64("N", N)
         f.i64("nvec", nvec)
         f.u64("status", self.status_ptr)
+        f.u64("wait_ns", int(self.wait_limit_ns))
+        f.u32("starve", int(self.debug_starve_bytes))
         offs, off = {}, 0
         for pre, o in sorted(staged.items()):
             offs[pre] = off
@@ -698,12 +702,12 @@ class Planner(object):
         body.append("const i64 kfirst = %s, kstep = %s;" % (("cluster_index()", "cluster_count()") if C > 1
                                                             else ("blockIdx.x", "gridDim.x")))
         body.append("for (i64 k = kfirst; k < p.K; k += kstep) {")
-        body.append("    rr_stage_begin(&bar, seg * %du);" % row_bytes)
+        body.append("    rr_stage_begin(cx, &bar, seg * %du + p.starve);" % row_bytes)
         for pre, o in sorted(staged.items()):
             isz = DT_SIZE[o.dt]
-            body.append("    rr_stage_copy(dyn + p.off_%s, p.%s + (u64)((k * p.%s_sk + n0) * %d), seg * %du, &bar);"
+            body.append("    rr_stage_copy(cx, dyn + p.off_%s, p.%s + (u64)((k * p.%s_sk + n0) * %d), seg * %du, &bar);"
                         % (pre, pre, pre, isz, isz))
-        body.append("    rr_stage_wait(cx, &bar, p.status);")
+        body.append("    rr_stage_wait(cx, &bar, p.status, p.wait_ns);")
         body.append("    P q = p;")
         for pre, o in sorted(staged.items()):
             body.append("    q.%s = (u64)(dyn + p.off_%s) - (u64)(n0 * %d); q.%s_sk = 0;" % (pre, pre, DT_SIZE[o.dt], pre))

@@ -97,6 +97,38 @@ def test_row_resident_cluster_kernel_matches_checker(case, b200):
     _compare(case, got, _oracle64(case))
 
 
+def test_bounded_wait_reports_instead_of_hanging():
+    """The one software wait in the kernels (a block waiting for its TMA-staged row slice)
+    has a time limit.  Announce 16 bytes that never arrive, give it 20 ms: the kernel must
+    end by itself, the host must see the status, and the backend must keep working."""
+    from neon_b200 import runtime as rt
+    from neon_b200.backend import B200Backend
+    be = B200Backend(rng_seed=0)
+    x = be.array(np.random.RandomState(0).randn(64, 16384).astype(np.float32))
+    y = be.empty((64, 16384))
+
+    def stmt():
+        y[:] = (x - be.mean(x, axis=1)) / (be.std(x, axis=1) + 1e-3)
+
+    be._planner.wait_limit_ns = 20 * 1000 * 1000
+    be._planner.debug_starve_bytes = 16
+    be.launch_log = []
+    stmt()
+    assert [k for k, _ in be.launch_log] == ["rowres"]
+    with pytest.raises(rt.B200Error) as e:
+        be.synchronize()
+    assert e.value.status == -6
+    # same context, same backend: a clean statement afterwards gives the right answer
+    be._planner.debug_starve_bytes = 0
+    be._planner.wait_limit_ns = 2000000000
+    be._plans.clear()
+    stmt()
+    be.synchronize()
+    xh = x.get().astype(np.float64)
+    want = (xh - xh.mean(1, keepdims=True)) / (xh.std(1, keepdims=True) + 1e-3)
+    np.testing.assert_allclose(y.get(), want, rtol=1e-4, atol=1e-5)
+
+
 def test_full_size_properties_cfg5(b200):
     """2^28 elements of the fp16 chain with stochastic rounding: size-independent checks.
     total must equal the float64 sum of the device-produced z (relative to sum|z|),
