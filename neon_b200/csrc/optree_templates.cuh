@@ -191,9 +191,18 @@ DEV u32 rng_hash(const Rng& g, u32 lo, u32 hi) {
 DEV u32 rng_bits(const Rng& g, u64 idx) { return rng_hash(g, (u32)idx, (u32)(idx >> 32)); }
 // 16-bit float stores share one hash between elements 2q and 2q+1: the even one
 // reads it as is, the odd one with its halves swapped
+// 16-bit float stores need 13 random bits per element, so eight neighbouring
+// elements share ONE hash: group = idx >> 3 is hashed, the four element pairs of
+// the group take successive steps of a linear congruential chain from it, and
+// the odd element of a pair reads its word with the halves swapped.
+DEV u32 rng_chain(u32 h) { return h * 0x2C9277B5u + 0xAC564B05u; }
+DEV u32 rng_chain_word(u32 h) { return h ^ (h >> 16); }
 DEV u32 rng_bits_pair(const Rng& g, u64 idx) {
-    const u32 h = rng_bits(g, idx >> 1);
-    return (idx & 1) ? __funnelshift_l(h, h, 16) : h;
+    u32 h = rng_bits(g, idx >> 3);
+    const int s = (int)(idx >> 1) & 3;
+    for (int j = 0; j < s; ++j) h = rng_chain(h);
+    const u32 w = s ? rng_chain_word(h) : h;
+    return (idx & 1) ? __funnelshift_l(w, w, 16) : w;
 }
 DEV float frand(const Rng& g, u64 idx) { return __uint2float_rn(rng_bits(g, idx)) * 2.3283064365386963e-10f; }
 
@@ -285,19 +294,23 @@ template <int DT, int V, bool SR> DEV void cvt_out(const float* v, u32* w, const
 }
 
 // Random words for the V lanes of a store whose lane i has element index idx0 + i*step.
-// PAIR: 16-bit float stores (two elements per hash).  ALIGNED: idx0 % V == 0 and
-// step == 1, so a vector never straddles a pair or a 2^32 boundary and the
+// PAIR: 16-bit float stores (eight elements per hash).  ALIGNED: idx0 % V == 0 and
+// step == 1, so a vector never straddles a group or a 2^32 boundary and the
 // 64-bit arithmetic is done once per vector instead of once per lane.
 template <int V, bool PAIR, bool ALIGNED> DEV void rng_lanes(const Rng& g, u64 idx0, i64 step, u32* ur) {
     if constexpr (ALIGNED && V > 1) {
         if constexpr (PAIR) {
-            const u64 q0 = idx0 >> 1;
-            const u32 lo = (u32)q0, hi = (u32)(q0 >> 32);
+            // V divides 8 and idx0 % V == 0: the vector lies inside one group of eight
+            const u64 grp = idx0 >> 3;
+            u32 h = rng_hash(g, (u32)grp, (u32)(grp >> 32));
+            const int s0 = (int)(idx0 >> 1) & 3;          // 0 when V == 8
+            for (int j = 0; j < s0; ++j) h = rng_chain(h);
 #pragma unroll
             for (int j = 0; j < V / 2; ++j) {
-                const u32 h = rng_hash(g, lo + j, hi);
-                ur[2 * j] = h;
-                ur[2 * j + 1] = __funnelshift_l(h, h, 16);
+                const u32 w = (V == 8) ? (j ? rng_chain_word(h) : h) : ((s0 + j) ? rng_chain_word(h) : h);
+                ur[2 * j] = w;
+                ur[2 * j + 1] = __funnelshift_l(w, w, 16);
+                h = rng_chain(h);
             }
         } else {
             const u32 lo = (u32)idx0, hi = (u32)(idx0 >> 32);
