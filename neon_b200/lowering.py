@@ -1148,6 +1148,9 @@ class Planner(object):
                 if r.op.startswith("arg"):
                     f.u64("r%dv" % r.nid, ai)
                     ep_lines.append("reinterpret_cast<int*>(p.r%dv)[k] = ri[%d];" % (r.nid, i))
+                    # the extreme value itself, for callers that merge results of several devices
+                    f.u64("r%dx" % r.nid, av)
+                    ep_lines.append("reinterpret_cast<float*>(p.r%dx)[k] = r[%d];" % (r.nid, i))
                 else:
                     f.u64("r%dv" % r.nid, av)
                     ep_lines.append("reinterpret_cast<float*>(p.r%dv)[k] = r[%d];" % (r.nid, i))
@@ -1260,8 +1263,13 @@ class Planner(object):
             pair = "true" if odt in (DT_CODES["f2"], DT_CODES["bf2"]) else "false"
             aligned = "true" if (ra == 1 and (st.flat or ncols % V == 0)) else "false"
             st_lines.append("const SrCtx c = sr_ctx(p.sr_mb); const Rng g{p.rk0, p.rk1}; u32 ur[V];")
-            st_lines.append("rng_lanes<V, %s, %s>(g, (u64)(p.lin_0 + %s * p.lin_r + %s * p.lin_c), %s, ur);"
-                            % (pair, aligned, row, col, step))
+            if st.flat and self._lin is None:
+                lin_expr = "(u64)n"                       # one row: the element index is n itself
+            elif ra == 1:
+                lin_expr = "(u64)(p.lin_0 + %s * p.lin_r + %s)" % (row, col)     # lin_c is 1
+            else:
+                lin_expr = "(u64)(p.lin_0 + %s * p.lin_r + %s * p.lin_c)" % (row, col)
+            st_lines.append("rng_lanes<V, %s, %s>(g, %s, %s, ur);" % (pair, aligned, lin_expr, step))
             st_lines.append("st_f<%s, V, true>(p.o, %s, v, c, ur);" % (DT_NAMES[odt], o_off))
         else:
             st_lines.append("SrCtx c; c.shift = 0; c.mask = 0;")

@@ -184,9 +184,30 @@ class ShardedBackend(B200Backend):
             self._launch(pz)
             if crosses:
                 for op, addr_v, addr_i, count in pz.results:
-                    if op not in _NCCL_OP:
-                        raise NotImplementedError("%s across the sharded axis" % op)
-                    self._allreduce(addr_v, count, _NCCL_OP[op])
+                    if op in _NCCL_OP:
+                        self._allreduce(addr_v, count, _NCCL_OP[op])
+                    else:
+                        self._merge_arg(op, addr_v, addr_i, count, sharded[0])
+
+    def _merge_arg(self, op, addr_v, addr_i, count, like):
+        """argmax / argmin across the shards: every rank contributes (extreme value,
+        global column index) per row, all ranks gather the pairs and keep, per row,
+        the index of the first rank that holds the extreme value -- columns grow with
+        the rank, so that is the first occurrence, as numpy.argmax gives it."""
+        from .tensor import B200Tensor
+        W = self.world_size
+        val = B200Tensor(self, (1, count), np.float32, gpudata=addr_v)
+        idx = B200Tensor(self, (1, count), np.int32, gpudata=addr_i)
+        c0 = like.c0 if like.flat_of is None else 0
+        idx[:] = idx + float(c0)                                   # local -> global column
+        vals = self.empty((W, count), dtype=np.float32)
+        idxs = self.empty((W, count), dtype=np.int32)
+        rt.allgather(self.comm, addr_v, vals.ptr, 4 * count, self.stream)
+        rt.allgather(self.comm, addr_i, idxs.ptr, 4 * count, self.stream)
+        self.collectives += 2
+        winner = self.empty((1, count), dtype=np.int32)
+        winner[:] = self.argmax(vals, axis=0) if op == "argmax" else self.argmin(vals, axis=0)
+        idx[:] = self.sum(self.onehot(winner, axis=0) * idxs, axis=0)
 
     def _allreduce(self, addr, count, op):
         rt.allreduce(self.comm, addr, addr, count, rt.F32, op, self.stream)

@@ -41,6 +41,15 @@ def main():
     mx[:] = be.max(x, axis=1) - be.min(x, axis=1)
     x64 = xh.astype(np.float64)
     check_output("sharded max-min", mx.get(), x64.max(1, keepdims=True) - x64.min(1, keepdims=True), np.float32)
+    am = be.empty((rows, 1), dtype=np.int32)
+    am[:] = be.argmax(x, axis=1)
+    assert np.array_equal(am.get(), x64.argmax(1).reshape(-1, 1)), "sharded argmax"
+    am[:] = be.argmin(x, axis=1)
+    assert np.array_equal(am.get(), x64.argmin(1).reshape(-1, 1)), "sharded argmin"
+    tie = np.round(xh.astype(np.float32)).astype(np.float16)       # many equal maxima: first one wins
+    xt = be.array(tie, dtype=np.float16, parallel=True)
+    am[:] = be.argmax(xt, axis=1)
+    assert np.array_equal(am.get(), tie.astype(np.float64).argmax(1).reshape(-1, 1)), "sharded argmax with ties"
     s0 = be.empty((1, cols), parallel=True)
     s0[:] = be.sum(x, axis=0)
     check_output("sharded axis-0 sum", s0.get(), x64.sum(0, keepdims=True), np.float32)
