@@ -67,7 +67,7 @@ class B200Backend(OpTreeBackend):
                  scratch_size=0, hist_bins=64, hist_offset=-48, compat_mode=None,
                  enable_winograd=True, cache_dir=None, num_devices=None, max_devices=None,
                  precise_math=False):
-        if default_dtype not in (np.float16, np.float32):
+        if default_dtype not in (np.float16, np.float32) and np.dtype(default_dtype).name != "bfloat16":
             raise ValueError("Default data type for the b200 backend must be float16 or 32")
         if rt.device_count() <= int(device_id):
             raise RuntimeError("b200 backend needs CUDA device %d; none is visible" % int(device_id))
@@ -354,10 +354,12 @@ class B200Backend(OpTreeBackend):
             return 0
         if rounding is True:
             rounding = 10
-        elif out.dtype.type is np.float32:
+        if out.dtype.type is np.float32:
             rounding = min(int(rounding), 15)
         elif out.dtype.type is np.float16:
             rounding = min(int(rounding), 10)
+        elif out.dtype.name == "bfloat16":
+            rounding = min(int(rounding), 7)
         elif out.dtype.kind != "f":
             rounding = 1                       # integer stores: on/off only
         return max(int(rounding), 1)

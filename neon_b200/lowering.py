@@ -94,7 +94,7 @@ BINARY_HOST = {
 
 def dtype_code(dtype):
     dtype = np.dtype(dtype)
-    key = dtype.str[1:]
+    key = "bf2" if dtype.name == "bfloat16" else dtype.str[1:]
     if key not in DT_CODES:
         raise TypeError("unsupported tensor dtype %s" % dtype)
     return DT_CODES[key]
@@ -186,7 +186,7 @@ def program_key(stack):
     for s in stack:
         if isinstance(s, Tensor):
             ix = seen.setdefault(id(s), len(seen))
-            key.append((ix, s.dtype.char, s.shape, s.strides, s.ptr & 15,
+            key.append((ix, s.dtype.str, s.shape, s.strides, s.ptr & 15,
                         s.take_array[1] if s.take_array else None,
                         s is not out and shares_memory(s, out)))
         elif type(s) is dict:

@@ -18,6 +18,12 @@ from .optree import OpTreeNode, Tensor
 _none_slice = slice(None, None, None)
 
 SUPPORTED = (np.float16, np.float32, np.uint8, np.int8, np.uint16, np.int16, np.uint32, np.int32)
+try:                                    # bfloat16 storage when the numpy extension type is installed
+    import ml_dtypes
+    bfloat16 = ml_dtypes.bfloat16
+    SUPPORTED = SUPPORTED + (bfloat16,)
+except ImportError:                     # pragma: no cover
+    bfloat16 = None
 
 
 def _contiguous_strides(shape):

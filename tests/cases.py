@@ -33,7 +33,8 @@ class Case(object):
 
 
 def _is_float(dt):
-    return np.dtype(dt).kind == "f"
+    dt = np.dtype(dt)
+    return dt.kind == "f" or dt.name == "bfloat16"
 
 
 def run_case(be, case, compute_dtype=None, seed=0, rounding=None):

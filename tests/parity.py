@@ -14,6 +14,12 @@ def ulp16(x):
     return np.maximum(np.spacing(h).astype(np.float64), 2.0 ** -24)
 
 
+def ulp_bf16(x):
+    """Spacing of bfloat16 (8 significant bits) at |x|."""
+    a = np.maximum(np.abs(np.asarray(x, np.float64)), 2.0 ** -126)
+    return 2.0 ** (np.floor(np.log2(a)) - 7)
+
+
 def check_output(name, got, want64, dtype, scale=None):
     """Assert ``got`` (device result, storage dtype) matches ``want64`` (checker run in float64)."""
     dtype = np.dtype(dtype)
@@ -25,6 +31,11 @@ def check_output(name, got, want64, dtype, scale=None):
         return
     g = got.astype(np.float64)
     w = want64.astype(np.float64)
+    if dtype.name == "bfloat16":
+        noise = 1e-6 * (float(np.max(np.abs(w))) if w.size else 0.0)
+        err = (np.abs(g - w) - noise) / ulp_bf16(w)
+        assert np.all(err <= 1.0 + 1e-3), "%s: bf16 error %.3f ulp" % (name, err.max())
+        return
     if dtype == np.float16:
         # one fp16 ulp of the exact value, plus the fp32 rounding noise of the terms that
         # were combined (matters only where the result cancels to almost nothing and an

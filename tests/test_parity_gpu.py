@@ -391,6 +391,49 @@ def test_dot_inside_op_trees(b200):
     np.testing.assert_allclose(out.get(), ah.astype(np.float16).astype(np.float32).dot(bh), rtol=1e-5, atol=1e-4)
 
 
+def _bf16_cases():
+    import ml_dtypes
+    bf = ml_dtypes.bfloat16
+    out = [cases.unary_case("tanh", (64, 328), bf), cases.unary_case("exp", (33, 77), bf),
+           cases.binary_case("mul", (64, 328), (64, 1), bf), cases.binary_case("add", (4, 3), (4, 3), bf),
+           cases.reduce_case("sum", (64, 4096), 1, bf), cases.reduce_case("max", (4096, 64), 0, bf),
+           cases.reduce_case("argmax", (300, 40), 0, bf, ties=True)]
+
+    def chain(be, t):
+        x, y = t["x"], t["y"]
+        t["z"][:] = be.tanh(x) * be.sqrt(be.absolute(y)) + 0.5 * x * y
+    out.append(cases.Case("bf16_chain_256x512",
+                          lambda rng: {"x": rng.uniform(-4, 4, (256, 512)).astype(bf),
+                                       "y": rng.uniform(-4, 4, (256, 512)).astype(bf)},
+                          {"z": ((256, 512), bf)}, chain))
+    return out
+
+
+@pytest.mark.parametrize("case", _bf16_cases(), ids=lambda c: c.name)
+def test_bfloat16_storage(case, b200):
+    """bf16 storage with fp32 arithmetic (no counterpart in neon, which predates the format)."""
+    got = cases.run_case(b200, case)
+    _compare(case, got, _oracle64(case))
+
+
+def test_bfloat16_stochastic_rounding_bit_exact(b200):
+    import ml_dtypes
+    bf = ml_dtypes.bfloat16
+    be = b200
+    rng = np.random.RandomState(21)
+    shape = (200, 512)
+    xh = rng.uniform(-4, 4, shape).astype(np.float16)
+    x = be.array(xh, dtype=np.float16)
+    z = be.empty(shape, dtype=bf)
+    z.rounding = True                       # capped at the 7 mantissa bits bf16 has
+    seed, launch = be.rng_get_state()[1]
+    z[:] = x * 1.0
+    key = sround.launch_key(int(seed), int(launch))
+    ur = sround.rng_bits_pair(key[0], key[1], np.arange(xh.size, dtype=np.uint64)).reshape(shape)
+    want32 = sround.sr_f32(xh.astype(np.float32), ur, 7)          # exactly representable in bf16
+    assert np.array_equal(z.get().astype(np.float32).view(np.uint32), want32.view(np.uint32))
+
+
 def test_onehot_and_views(b200):
     be = b200
     idx = np.random.RandomState(3).randint(0, 10, (1, 64)).astype(np.int32)
