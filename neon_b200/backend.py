@@ -412,6 +412,13 @@ class B200Backend(OpTreeBackend):
     def fill_normal(self, ary, mean=0, stdv=1):
         ary[:] = (self.rng.standard_normal(ary.shape) * stdv + mean).astype(ary.dtype)
 
+    def copy_transpose(self, a, out, axes=None, repeat=1):
+        """out = a transposed (neon/backends/nervanagpu.py:3077-3118); two-dimensional
+        tensors only, as one strided element-wise statement."""
+        if len(a.shape) != 2 or (axes is not None and tuple(axes) != (1, 0)):
+            raise NotImplementedError("copy_transpose of more than two dimensions")
+        out[:] = a.T
+
     # ------------------------------------------------------------------ timing marks (nervanagpu.py:3138-3177)
     def init_mark(self):
         ev = rt.event_create()

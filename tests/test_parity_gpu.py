@@ -129,6 +129,32 @@ def test_bounded_wait_reports_instead_of_hanging():
     np.testing.assert_allclose(y.get(), want, rtol=1e-4, atol=1e-5)
 
 
+def test_full_size_adam_against_checker_on_a_sample(b200):
+    """Config 3 at its quoted size (1e8 elements, param/m/v fp32, grad fp16), three steps.
+    The update is element-wise, so the checker run on every 977th element must agree
+    with the same elements of the full-size device result."""
+    be = b200
+    n_rows, n_cols = 100000, 1000
+    rng = np.random.RandomState(3)
+    ph = (0.02 * rng.standard_normal((n_rows, n_cols))).astype(np.float32)
+    param = be.array(ph)
+    m, v = be.zeros((n_rows, n_cols)), be.zeros((n_rows, n_cols))
+    grad = be.empty((n_rows, n_cols), dtype=np.float16)
+    ob = OracleBackend(default_dtype=np.float64)
+    pick = slice(0, None, 977)
+    op = ob.array(ph.reshape(-1)[pick].reshape(-1, 1), dtype=np.float64)
+    om, ov = ob.zeros(op.shape, dtype=np.float64), ob.zeros(op.shape, dtype=np.float64)
+    be.bsz = ob.bsz = 1
+    for step in range(1, 4):
+        gh = (1e-3 * np.random.RandomState(1000 + step).standard_normal((n_rows, n_cols))).astype(np.float16)
+        grad.set(gh)
+        cases.adam_step(be, param, grad, m, v, step)
+        og = ob.array(gh.reshape(-1)[pick].reshape(-1, 1), dtype=np.float64)
+        cases.adam_step(ob, op, og, om, ov, step)
+    for name, dev, ref in (("param", param, op), ("m", m, om), ("v", v, ov)):
+        check_output("adam 1e8/" + name, dev.get().reshape(-1)[pick].reshape(-1, 1), ref.get(), np.float32)
+
+
 def test_full_size_properties_cfg5(b200):
     """2^28 elements of the fp16 chain with stochastic rounding: size-independent checks.
     total must equal the float64 sum of the device-produced z (relative to sum|z|),
