@@ -370,14 +370,24 @@ DEV void red_merge(int op, float& a, int& ai, float b, int bi) {
 // MODE 0: 2-d, vector index -> (k, n) by division; grid.x * BLOCK * UNROLL >= K * nvec.
 // MODE 1: flat (K == 1, all operands contiguous), scalar tail of N % V elements.
 // MODE 2: 2-d with long rows: blockIdx.y/z select the row, blockIdx.x tiles it.
-template <template <int> class SV, class P, int V, int BLOCK, int UNROLL, int MODE>
+// MODE 3: flat over a contiguous 2-d tensor whose row length is p.flat_bpr times the elements
+//         one block handles: like MODE 1, but k carries the row of the block (one 32-bit
+//         division per thread) for statements that need element coordinates.
+// IDX32: the host guarantees that element counts and byte offsets fit 32 bits, so vector
+//        indices are computed in 32-bit arithmetic (widening multiply-adds for addresses).
+template <template <int> class SV, class P, int V, int BLOCK, int UNROLL, int MODE, bool IDX32 = false>
 DEV void ew_kernel(const P& p) {
     typedef SV<V> S;
-    constexpr bool FLAT = MODE == 1;
+    constexpr bool FLAT = MODE == 1 || MODE == 3;
     const i64 nvec = p.nvec;                     // vectors per row (FLAT: all vectors)
     const i64 total = MODE == 0 ? p.K * nvec : nvec;
-    const i64 base = (i64)blockIdx.x * (BLOCK * UNROLL) + threadIdx.x;
-    const i64 krow = MODE == 2 ? (i64)blockIdx.y + (i64)blockIdx.z * gridDim.y : 0;
+    const i64 base = IDX32 ? (i64)(blockIdx.x * (u32)(BLOCK * UNROLL) + threadIdx.x)
+                           : (i64)blockIdx.x * (BLOCK * UNROLL) + threadIdx.x;
+    i64 krow = 0;
+    if constexpr (MODE == 2) krow = (i64)blockIdx.y + (i64)blockIdx.z * gridDim.y;
+    // MODE 3: k carries, instead of the row r itself, the amount to add to a flat index of row r to
+    // get the element index in the enclosing tensor: lin_0 + r * lin_r
+    if constexpr (MODE == 3) krow = p.lin_0 + (i64)(blockIdx.x / (u32)p.flat_bpr) * p.lin_r;
     if (MODE == 2 && krow >= p.K) return;
     typename S::L l[UNROLL];
     typename S::H h[UNROLL];
@@ -386,7 +396,8 @@ DEV void ew_kernel(const P& p) {
     for (int u = 0; u < UNROLL; ++u) {
         i64 g = base + (i64)u * BLOCK;
         if (g < total) {
-            if constexpr (MODE != 0) { kk[u] = krow; nn[u] = g * V; }
+            if constexpr (MODE != 0 && IDX32) { kk[u] = krow; nn[u] = (i64)((u32)g * (u32)V); }
+            else if constexpr (MODE != 0) { kk[u] = krow; nn[u] = g * V; }
             else if (nvec <= 0x7fffffffLL && g <= 0x7fffffffLL) {
                 u32 q = (u32)g / (u32)nvec; kk[u] = q; nn[u] = (i64)((u32)g - q * (u32)nvec) * V;
             } else { kk[u] = g / nvec; nn[u] = (g - kk[u] * nvec) * V; }

@@ -536,9 +536,9 @@ class Planner(object):
     def plan(self, st, scratch, rounding=0, fuse_final=True, lin=None):
         """Return the list of Pass objects for Statement ``st``.  ``fuse_final=False``
         keeps every reduction result in scratch (for a caller that combines results
-        of several devices between passes); ``lin=(ncols, col0)`` makes element
-        indices for random numbers those of a wider tensor this one is a column
-        slice of."""
+        of several devices between passes); ``lin=(ncols, col0, local cols)`` makes
+        element indices for random numbers those of a wider tensor this one is a
+        column slice of."""
         self._lin = lin
         ra = st.axis                # reduced / loop axis in tensor coordinates
         ka = 1 - ra
@@ -1258,13 +1258,19 @@ class Planner(object):
             ncols = 0 if st.flat else st.out_shape[1]
             if self._lin is not None:
                 ncols = self._lin[0] if self._lin[1] % V == 0 else 1      # 1: never aligned
+                if st.flat:
+                    aligned_flat = ncols % V == 0 and self._lin[2] % V == 0
             step = "p.lin_c" if ra == 1 else "p.lin_r"
             row, col = ("k", "n") if ka == 0 else ("n", "k")
             pair = "true" if odt in (DT_CODES["f2"], DT_CODES["bf2"]) else "false"
             aligned = "true" if (ra == 1 and (st.flat or ncols % V == 0)) else "false"
+            if st.flat and self._lin is not None:
+                aligned = "true" if aligned_flat else "false"
             st_lines.append("const SrCtx c = sr_ctx(p.sr_mb); const Rng g{p.rk0, p.rk1}; u32 ur[V];")
             if st.flat and self._lin is None:
                 lin_expr = "(u64)n"                       # one row: the element index is n itself
+            elif st.flat:
+                lin_expr = "(u64)(n + k)"                 # the skeleton passes the row's index shift as k
             elif ra == 1:
                 lin_expr = "(u64)(p.lin_0 + %s * p.lin_r + %s)" % (row, col)     # lin_c is 1
             else:
@@ -1284,8 +1290,18 @@ class Planner(object):
             grid = ((nvec + BLOCK * unroll - 1) // (BLOCK * unroll), min(K, 65535), (K + 65534) // 65535)
         else:
             mode = 1 if st.flat else 0
+            if st.flat and self._lin is not None:
+                # flat view of a column shard: blocks must not straddle rows
+                cl = self._lin[2]
+                while unroll > 1 and cl % (BLOCK * unroll * V):
+                    unroll //= 2
+                assert cl % (BLOCK * unroll * V) == 0 and N % V == 0
+                mode = 3
+                f.u32("flat_bpr", cl // (BLOCK * unroll * V))
             grid = (max(1, (total + BLOCK * unroll - 1) // (BLOCK * unroll)), 1, 1)
-        call = "ew_kernel<S, P, %d, %d, %d, %d>(p);" % (V, BLOCK, unroll, mode)
+        widest = max([DT_SIZE[odt]] + [DT_SIZE[o.dt] for o, _ in em.lane_ops])
+        idx32 = mode != 0 and (N + BLOCK * unroll * V) * widest < (1 << 32)
+        call = "ew_kernel<S, P, %d, %d, %d, %d, %s>(p);" % (V, BLOCK, unroll, mode, "true" if idx32 else "false")
         min_blocks = self.ew_min_blocks
         if min_blocks is None:
             moved = DT_SIZE[odt] + sum(DT_SIZE[o.dt] for o, _ in em.lane_ops)
@@ -1303,7 +1319,9 @@ class Planner(object):
             f.values["lin_r"] = st.out_shape[1] if not st.flat else 0
             f.values["lin_c"] = 1
             if self._lin is not None:
-                f.values["lin_r"], f.values["lin_0"] = self._lin
+                f.values["lin_r"], f.values["lin_0"] = self._lin[0], self._lin[1]
+                if st.flat:            # flat index n -> n + c0 + row * (global - local row length)
+                    f.values["lin_r"] = self._lin[0] - self._lin[2]
         return pz
 
     @staticmethod

@@ -113,7 +113,7 @@ class ShardedTensor(Tensor):
         if tuple(shape) != (1, self.size):
             raise NotImplementedError("sharded tensors reshape only to (1, size)")
         return ShardedTensor(self.backend, shape, self.local.reshape(1, self.local.size), self.c0,
-                             self.name, flat_of=(self.shape[1], self.c0))
+                             self.name, flat_of=(self.shape[1], self.c0, self.local.shape[1]))
 
 
 class ShardedBackend(B200Backend):
@@ -165,14 +165,17 @@ class ShardedBackend(B200Backend):
             return super(ShardedBackend, self)._run(out, expr)
         lin = None
         if isinstance(out, ShardedTensor):
-            lin = out.flat_of if out.flat_of else (out.shape[1], out.c0)
+            lin = out.flat_of if out.flat_of else (out.shape[1], out.c0, out.local.shape[1])
         local_stack = [s.local if isinstance(s, ShardedTensor) else s for s in stack]
         rounding = self._rounding_bits(local_stack[0])
         key = (program_key(local_stack), rounding, lin)
         cached = self._plans.get(key)
         if cached is None:
             uses_rng = bool(rounding) or any(type(s) is dict and s["op"] == "rand" for s in stack)
-            st = Statement(local_stack, allow_flat=not uses_rng)
+            # random words need element coordinates: a flat pass can supply them only when
+            # no block straddles a row of the shard (8192 elements per block at most)
+            row_ok = lin is not None and out.flat_of is None and lin[2] % 8192 == 0
+            st = Statement(local_stack, allow_flat=(not uses_rng) or row_ok)
             crosses = st.has_red and st.axis == 1
             self._scratch.reset()
             passes = self._planner.plan(st, self._scratch, rounding=rounding, fuse_final=not crosses, lin=lin)
