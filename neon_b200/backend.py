@@ -95,6 +95,8 @@ class B200Backend(OpTreeBackend):
         self._marks = []
         self.launches = 0                  # kernels launched so far (statements may take several)
         self.launch_log = None             # set to a list to record (kind, desc) per launch
+        self.trace = []                    # with bench=True: one record per launch (name, geometry, ms)
+        self._trace_events = None
         super(B200Backend, self).__init__(rng_seed, default_dtype, compat_mode=compat_mode,
                                           deterministic=deterministic)
 
@@ -341,8 +343,21 @@ class B200Backend(OpTreeBackend):
             k0, k1 = rt.rng_next_key()
             pz.fields.values["rk0"] = k0
             pz.fields.values["rk1"] = k1
+        if self.bench:
+            if self._trace_events is None:
+                self._trace_events = (rt.event_create(), rt.event_create())
+            rt.event_record(self._trace_events[0], self.stream)
         rt.launch(kernel, pz.grid, pz.block, pz.fields.pack(), smem=pz.smem, stream=self.stream,
                   cluster=pz.cluster)
+        if self.bench:
+            # per-launch timing, as be.bench does in the reference (float_ew.py:917-938); the
+            # records stay in self.trace (newest last, bounded) and dump_trace() writes them out
+            rt.event_record(self._trace_events[1], self.stream)
+            rt.event_sync(self._trace_events[1])
+            self.trace.append({"kernel": pz.name, "kind": pz.kind, "desc": pz.desc,
+                               "ms": rt.event_elapsed_ms(*self._trace_events)})
+            if len(self.trace) > 4096:
+                del self.trace[:1024]
         self.launches += 1
         if self.launch_log is not None:
             self.launch_log.append((pz.kind, pz.desc))
@@ -433,6 +448,12 @@ class B200Backend(OpTreeBackend):
 
     def get_time(self, start, end):
         return rt.event_elapsed_ms(start, end)
+
+    def dump_trace(self, path):
+        """Write the per-launch records collected with ``bench=True`` as JSON."""
+        import json
+        with open(path, "w") as f:
+            json.dump(self.trace, f, indent=1)
 
     def synchronize(self):
         rt.stream_sync(self.stream)

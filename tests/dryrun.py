@@ -43,6 +43,8 @@ class DryRunBackend(B200Backend):
         self._temps, self._temps_used = {}, {}
         self._plans = {}
         self.compat_mode = None
+        self.bench = False
+        self.trace = []
         self._next = 0x7F0000000000
         self.launches = 0
         self.passes = []            # every Pass planned so far

@@ -460,6 +460,21 @@ def test_bfloat16_stochastic_rounding_bit_exact(b200):
     assert np.array_equal(z.get().astype(np.float32).view(np.uint32), want32.view(np.uint32))
 
 
+def test_bench_flag_records_every_launch(tmp_path):
+    """be.bench turns on per-launch timing (the reference prints msecs per compound kernel,
+    float_ew.py:917-938); here the records are kept and can be dumped as JSON."""
+    import json
+    from neon_b200.backend import B200Backend
+    be = B200Backend(rng_seed=0, bench=True)
+    x = be.array(np.random.RandomState(0).randn(1000, 64).astype(np.float32))
+    y = be.empty((1000, 64))
+    y[:] = be.exp(x - be.max(x, axis=0)) / be.sum(be.exp(x - be.max(x, axis=0)), axis=0)
+    assert [r["kind"] for r in be.trace] == ["red_cols", "red_cols", "ew_2d"]
+    assert all(r["ms"] > 0 and r["kernel"].startswith("ot_") for r in be.trace)
+    be.dump_trace(str(tmp_path / "trace.json"))
+    assert len(json.load(open(str(tmp_path / "trace.json")))) == 3
+
+
 def test_onehot_and_views(b200):
     be = b200
     idx = np.random.RandomState(3).randint(0, 10, (1, 64)).astype(np.int32)
