@@ -728,11 +728,13 @@ DEV void red_cols_kernel(const P& p) {
 // shared memory between two hardware cluster barriers, and the last pass
 // streams the result to HBM.  Clusters walk over rows persistently.
 //
-// The generated driver calls the pieces in this order per row:
-//   rr_stage_begin / rr_stage_copy... / rr_stage_wait, then per reduction pass
-//   rr_reduce + rr_combine, finally rr_ew.
-// Waits are bounded: a bulk copy that never completes sets *status and the
-// kernel carries on to its end instead of spinning.
+// The slice is staged in chunks, each with its own mbarrier: the first pass of a
+// row consumes chunk by chunk as the copies land, and the last pass hands each
+// chunk it has finished with to the copies of the next row, so HBM reads run
+// underneath the passes.  The generated driver calls rr_begin, rr_issue_row for
+// the first row, then per row rr_pass (+ rr_combine after reductions) and
+// rr_row_end.  Waits are bounded in time: a copy that never completes sets
+// *status and the kernel carries on to its end instead of spinning.
 
 DEV u32 smem_u32(const void* p) { return (u32)__cvta_generic_to_shared(p); }
 DEV u32 cluster_rank() { u32 r; asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r)); return r; }
@@ -766,114 +768,142 @@ DEV void bulk_g2s(void* dst, const void* src, u32 bytes, u64* bar) {
                  ::"r"(smem_u32(dst)), "l"(src), "r"(bytes), "r"(smem_u32(bar)) : "memory");
 }
 
+enum { RR_MAX_CHUNKS = 32 };
+
 struct RowCtx {
     u32 rank;            // block's rank in its cluster
-    i64 v0, v1;          // this block's slice of the row, in V-wide vectors
-    u32 phase;           // mbarrier parity of the next staging
+    u32 v0, v1;          // this block's slice of the row, in V-wide vectors
+    u32 cv, nc;          // vectors per chunk, chunks in the slice (each chunk has its own mbarrier)
+    u32 phase;           // mbarrier parity of the row being consumed
     u32 row_parity;      // which set of exchange slots this row uses
     bool failed;
 };
 
-template <int C> DEV void rr_begin(RowCtx& cx, i64 nvec, u64* bar) {
+// THREADS * UNROLL vectors per chunk: one trip of the pass loops
+template <int C, int THREADS, int UNROLL> DEV void rr_begin(RowCtx& cx, i64 nvec, u64* bars) {
     cx.rank = C > 1 ? cluster_rank() : 0;
-    const i64 per = (nvec + C - 1) / C;
-    cx.v0 = (i64)cx.rank * per;
-    cx.v1 = cx.v0 + per < nvec ? cx.v0 + per : nvec;
+    const u32 per = (u32)((nvec + C - 1) / C);
+    cx.v0 = cx.rank * per;
+    cx.v1 = cx.v0 + per < (u32)nvec ? cx.v0 + per : (u32)nvec;
     if (cx.v0 > cx.v1) cx.v0 = cx.v1;
+    cx.cv = THREADS * UNROLL;
+    cx.nc = (cx.v1 - cx.v0 + cx.cv - 1) / cx.cv;
     cx.phase = 0; cx.row_parity = 0; cx.failed = false;
-    if (threadIdx.x == 0) mbar_init(bar, 1);
+    if (threadIdx.x == 0) {
+        for (u32 c = 0; c < cx.nc; ++c)
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bars + c)), "r"(1) : "memory");
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
     __syncthreads();
 }
-// before the async copies overwrite the slice: all reads of the previous row are done
-DEV void rr_stage_begin(const RowCtx& cx, u64* bar, u32 total_bytes) {
-    __syncthreads();
-    if (threadIdx.x == 0 && !cx.failed) {       // after a failed wait the barrier is left alone
-        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-        mbar_expect_tx(bar, total_bytes);
+// one operand's part of chunk c: global -> shared, at most 32 KB per bulk copy
+DEV void rr_copy(unsigned char* dst, u64 src, u32 bytes, u64* bar) {
+    for (u32 off = 0; off < bytes; off += 32768u) {
+        const u32 n = bytes - off < 32768u ? bytes - off : 32768u;
+        bulk_g2s(dst + off, reinterpret_cast<const char*>(src) + off, n, bar);
     }
 }
-DEV void rr_stage_copy(const RowCtx& cx, unsigned char* dst, u64 src, u32 bytes, u64* bar) {
-    if (threadIdx.x == 0 && !cx.failed) {
-        for (u32 off = 0; off < bytes; off += 32768u) {
-            const u32 n = bytes - off < 32768u ? bytes - off : 32768u;
-            bulk_g2s(dst + off, reinterpret_cast<const char*>(src) + off, n, bar);
-        }
-    }
+// ST::issue(p, cx, k, c, dyn, bars) (generated) announces and starts the copies of chunk c of row k
+template <class ST, class P>
+DEV void rr_issue_row(const P& p, const RowCtx& cx, i64 k, unsigned char* dyn, u64* bars) {
+    if (threadIdx.x == 0 && !cx.failed)
+        for (u32 c = 0; c < cx.nc; ++c) ST::issue(p, cx, k, c, dyn, bars);
 }
 DEV u64 global_ns() { u64 t; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t)); return t; }
-// Wait for the staged slice, for at most limit_ns.  When the time runs out the
-// block records it in *status, stops waiting for later rows as well (its results
-// are then meaningless, the host raises on the status) and keeps taking part in
-// every barrier so that its cluster peers are never left waiting.
-DEV void rr_stage_wait(RowCtx& cx, u64* bar, u64 status, u64 limit_ns) {
-    if (!cx.failed) {
-        const u64 t0 = global_ns();
-        bool done = false;
-        while (!(done = mbar_try_wait(bar, cx.phase))) {
-            if (global_ns() - t0 > limit_ns) break;
-        }
-        if (!done) {
+// Wait for one chunk, for at most limit_ns.  When the time runs out the thread
+// records it in *status and stops waiting; rr_row_end makes that the verdict of
+// the whole block, which then stops staging (its results are meaningless, the
+// host raises on the status) but keeps taking part in every barrier so that its
+// cluster peers are never left waiting.
+DEV void rr_wait_chunk(RowCtx& cx, u64* bar, u64 status, u64 limit_ns) {
+    if (cx.failed || mbar_try_wait(bar, cx.phase)) return;
+    const u64 t0 = global_ns();
+    while (!mbar_try_wait(bar, cx.phase)) {
+        if (global_ns() - t0 > limit_ns) {
             cx.failed = true;
             if (status) atomicExch(reinterpret_cast<int*>(status), 1);
+            return;
         }
     }
-    cx.failed = __syncthreads_or(cx.failed) != 0;     // one verdict for the whole block
+}
+DEV void rr_row_end(RowCtx& cx) {
+    cx.failed = __syncthreads_or(cx.failed) != 0;
     cx.phase ^= 1;
+    cx.row_parity ^= 1;
 }
 
-// one reduction pass over this block's slice (operands already point at shared memory)
-template <template <int> class SV, class P, int V, int THREADS, int UNROLL>
-DEV void rr_reduce(const P& q, i64 k, const RowCtx& cx, float* a, int* ai, float (*sv)[THREADS / 32], int (*si)[THREADS / 32]) {
+// One pass over this block's slice, chunk by chunk (operands already point at shared memory).
+//   WAIT     first pass of a row: wait for each chunk's copies before touching it
+//   RELEASE  last pass of a row: once all threads are done with a chunk, start the copies of
+//            the same chunk of the next row (knext), so loads overlap the rest of this pass
+//   NR == 0  element-wise pass (stores through S::store), else reductions into a / ai
+template <template <int> class SV, class ST, class P, int V, int THREADS, int UNROLL, bool WAIT, bool RELEASE>
+DEV void rr_pass(const P& q, const P& p, i64 k, i64 knext, RowCtx& cx, unsigned char* dyn, u64* bars,
+                 float* a, int* ai, float (*sv)[THREADS / 32], int (*si)[THREADS / 32]) {
     typedef SV<V> S;
     constexpr int NR = S::NRED;
+    constexpr int NA = NR > 0 ? NR : 1;
     const int tid = threadIdx.x;
-    float acc[NR][V]; int acci[NR][V];
+    float acc[NA][V]; int acci[NA][V];
 #pragma unroll
     for (int r = 0; r < NR; ++r)
 #pragma unroll
         for (int i = 0; i < V; ++i) { acc[r][i] = red_init(S::op(r)); acci[r][i] = -1; }
     typename S::H h;
     S::load_h(q, k, h);
-    for (i64 v = cx.v0 + tid; v < cx.v1; v += (i64)THREADS * UNROLL) {
+    for (u32 c = 0; c < cx.nc; ++c) {
+        if constexpr (WAIT) rr_wait_chunk(cx, bars + c, p.status, p.wait_ns);
+        const u32 vb = cx.v0 + c * cx.cv;
         typename S::L l[UNROLL];
 #pragma unroll
-        for (int u = 0; u < UNROLL; ++u) if (v + (i64)u * THREADS < cx.v1) S::load_l(q, k, (v + (i64)u * THREADS) * V, l[u]);
+        for (int u = 0; u < UNROLL; ++u)
+            if (vb + tid + u * THREADS < cx.v1) S::load_l(q, k, (i64)((vb + tid + u * THREADS) * (u32)V), l[u]);
 #pragma unroll
         for (int u = 0; u < UNROLL; ++u) {
-            if (v + (i64)u * THREADS < cx.v1) {
-                const i64 n = (v + (i64)u * THREADS) * V;
-                float out[NR][V];
+            if (vb + tid + u * THREADS < cx.v1) {
+                const i64 n = (i64)((vb + tid + u * THREADS) * (u32)V);
+                float out[NA][V];
                 S::eval(q, h, l[u], k, n, out);
+                if constexpr (NR == 0) {
+                    S::store(q, k, n, out[0]);
+                } else {
 #pragma unroll
-                for (int r = 0; r < NR; ++r)
+                    for (int r = 0; r < NR; ++r)
 #pragma unroll
-                    for (int i = 0; i < V; ++i) red_acc(S::op(r), acc[r][i], acci[r][i], out[r][i], (int)(n + i));
+                        for (int i = 0; i < V; ++i) red_acc(S::op(r), acc[r][i], acci[r][i], out[r][i], (int)(n + i));
+                }
             }
         }
-    }
-#pragma unroll
-    for (int r = 0; r < NR; ++r) {
-        a[r] = acc[r][0]; ai[r] = acci[r][0];
-#pragma unroll
-        for (int i = 1; i < V; ++i) red_merge(S::op(r), a[r], ai[r], acc[r][i], acci[r][i]);
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) {
-            float b = __shfl_xor_sync(0xffffffffu, a[r], o);
-            int bi = __shfl_xor_sync(0xffffffffu, ai[r], o);
-            red_merge(S::op(r), a[r], ai[r], b, bi);
+        if constexpr (RELEASE) {
+            __syncthreads();                      // every thread has read its part of chunk c
+            if (tid == 0 && knext < p.K && !cx.failed) ST::issue(p, cx, knext, c, dyn, bars);
         }
     }
-    const int warp = tid >> 5, lane = tid & 31;
-    __syncthreads();                       // sv/si may still be read from the previous pass
-    if (lane == 0) {
+    if constexpr (NR > 0) {
 #pragma unroll
-        for (int r = 0; r < NR; ++r) { sv[r][warp] = a[r]; si[r][warp] = ai[r]; }
-    }
-    __syncthreads();
+        for (int r = 0; r < NR; ++r) {
+            a[r] = acc[r][0]; ai[r] = acci[r][0];
 #pragma unroll
-    for (int r = 0; r < NR; ++r) {          // every thread folds the warp results, in warp order
-        a[r] = sv[r][0]; ai[r] = si[r][0];
-        for (int w = 1; w < THREADS / 32; ++w) red_merge(S::op(r), a[r], ai[r], sv[r][w], si[r][w]);
+            for (int i = 1; i < V; ++i) red_merge(S::op(r), a[r], ai[r], acc[r][i], acci[r][i]);
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) {
+                float b = __shfl_xor_sync(0xffffffffu, a[r], o);
+                int bi = __shfl_xor_sync(0xffffffffu, ai[r], o);
+                red_merge(S::op(r), a[r], ai[r], b, bi);
+            }
+        }
+        const int warp = tid >> 5, lane = tid & 31;
+        __syncthreads();                          // sv/si may still be read from the previous pass
+        if (lane == 0) {
+#pragma unroll
+            for (int r = 0; r < NR; ++r) { sv[r][warp] = a[r]; si[r][warp] = ai[r]; }
+        }
+        __syncthreads();
+#pragma unroll
+        for (int r = 0; r < NR; ++r) {            // every thread folds the warp results, in warp order
+            a[r] = sv[r][0]; ai[r] = si[r][0];
+            for (int w = 1; w < THREADS / 32; ++w) red_merge(S::op(r), a[r], ai[r], sv[r][w], si[r][w]);
+        }
     }
 }
 
@@ -902,28 +932,6 @@ DEV void rr_combine(const RowCtx& cx, float* a, int* ai, u32* slots /* [2 pariti
         for (int r = 0; r < NR; ++r) res[r] = red_is_arg(S::op(r)) ? (u32)ai[r] : __float_as_uint(a[r]);
     }
     __syncthreads();
-}
-
-// the element-wise pass over this block's slice
-template <template <int> class SV, class P, int V, int THREADS, int UNROLL>
-DEV void rr_ew(const P& q, i64 k, const RowCtx& cx) {
-    typedef SV<V> S;
-    typename S::H h;
-    S::load_h(q, k, h);
-    for (i64 v = cx.v0 + threadIdx.x; v < cx.v1; v += (i64)THREADS * UNROLL) {
-        typename S::L l[UNROLL];
-#pragma unroll
-        for (int u = 0; u < UNROLL; ++u) if (v + (i64)u * THREADS < cx.v1) S::load_l(q, k, (v + (i64)u * THREADS) * V, l[u]);
-#pragma unroll
-        for (int u = 0; u < UNROLL; ++u) {
-            if (v + (i64)u * THREADS < cx.v1) {
-                const i64 n = (v + (i64)u * THREADS) * V;
-                float out[1][V];
-                S::eval(q, h, l[u], k, n, out);
-                S::store(q, k, n, out[0]);
-            }
-        }
-    }
 }
 
 }  // namespace b200

@@ -656,6 +656,8 @@ class Planner(object):
         while threads > 256 and seg_vecs < 2 * threads:
             threads //= 2
         unroll = 2
+        if (seg_vecs + threads * unroll - 1) // (threads * unroll) > 32:      # RR_MAX_CHUNKS mbarriers
+            return None
         nrmax = max(len(rs) for _, rs, _ in ems)
         nres = len(reds)
         slot_of = {}
@@ -692,38 +694,52 @@ class Planner(object):
                         "st_f<%s, V, false>(p.o, k * p.o_sk + n, v, c, nullptr);" % DT_NAMES[st.out.dt]]
             parts.append(self._struct("SE", fin, ["out[0][i] = %s;" % val], 0, "OP_SUM", None, st_lines))
 
-        body = []
-        body.append("extern __shared__ __align__(128) unsigned char dyn[];")
-        body.append("__shared__ u64 bar;")
-        body.append("__shared__ float sv[%d][%d]; __shared__ int si[%d][%d];" % (nrmax, threads // 32, nrmax, threads // 32))
-        body.append("__shared__ u32 slots[%d][2][%d][2]; __shared__ u32 s_res[%d];" % (len(ems), nrmax, nres))
-        body.append("RowCtx cx; rr_begin<%d>(cx, p.nvec, &bar);" % C)
-        body.append("const i64 n0 = cx.v0 * %d; const u32 seg = (u32)(cx.v1 - cx.v0) * %d;" % (V, V))
-        body.append("const i64 kfirst = %s, kstep = %s;" % (("cluster_index()", "cluster_count()") if C > 1
-                                                            else ("blockIdx.x", "gridDim.x")))
-        body.append("for (i64 k = kfirst; k < p.K; k += kstep) {")
-        body.append("    rr_stage_begin(cx, &bar, seg * %du + p.starve);" % row_bytes)
+        # the generated staging struct: announce and start the copies of chunk c of row k
+        issue = ["const u32 e0 = c * cx.cv * %du;" % V,
+                 "const u32 seg = (cx.v1 - cx.v0) * %du;" % V,
+                 "const u32 ne = seg - e0 < cx.cv * %du ? seg - e0 : cx.cv * %du;" % (V, V),
+                 "const i64 n0 = (i64)cx.v0 * %d + e0;" % V,
+                 "asm volatile(\"fence.proxy.async.shared::cta;\" ::: \"memory\");",
+                 "mbar_expect_tx(bars + c, ne * %du + (c == 0 ? p.starve : 0u));" % row_bytes]
         for pre, o in sorted(staged.items()):
             isz = DT_SIZE[o.dt]
-            body.append("    rr_stage_copy(cx, dyn + p.off_%s, p.%s + (u64)((k * p.%s_sk + n0) * %d), seg * %du, &bar);"
-                        % (pre, pre, pre, isz, isz))
-        body.append("    rr_stage_wait(cx, &bar, p.status, p.wait_ns);")
-        body.append("    P q = p;")
+            issue.append("rr_copy(dyn + p.off_%s + e0 * %du, p.%s + (u64)((k * p.%s_sk + n0) * %d), ne * %du, bars + c);"
+                         % (pre, isz, pre, pre, isz, isz))
+        parts.append("struct ST {\n    static DEV void issue(const P& p, const RowCtx& cx, i64 k, u32 c, "
+                     "unsigned char* dyn, u64* bars) {\n        " + "\n        ".join(issue) + "\n    }\n};")
+
+        body = []
+        body.append("extern __shared__ __align__(128) unsigned char dyn[];")
+        body.append("__shared__ u64 bars[RR_MAX_CHUNKS];")
+        body.append("__shared__ float sv[%d][%d]; __shared__ int si[%d][%d];" % (nrmax, threads // 32, nrmax, threads // 32))
+        body.append("__shared__ u32 slots[%d][2][%d][2]; __shared__ u32 s_res[%d];" % (len(ems), nrmax, nres))
+        body.append("RowCtx cx; rr_begin<%d, %d, %d>(cx, p.nvec, bars);" % (C, threads, unroll))
+        body.append("const i64 n0 = (i64)cx.v0 * %d;" % V)
+        body.append("const i64 kfirst = %s, kstep = %s;" % (("cluster_index()", "cluster_count()") if C > 1
+                                                            else ("blockIdx.x", "gridDim.x")))
+        body.append("if (kfirst < p.K) rr_issue_row<ST>(p, cx, kfirst, dyn, bars);")
+        body.append("P q = p;")
         for pre, o in sorted(staged.items()):
-            body.append("    q.%s = (u64)(dyn + p.off_%s) - (u64)(n0 * %d); q.%s_sk = 0;" % (pre, pre, DT_SIZE[o.dt], pre))
+            body.append("q.%s = (u64)(dyn + p.off_%s) - (u64)(n0 * %d); q.%s_sk = 0;" % (pre, pre, DT_SIZE[o.dt], pre))
         for r in reds:
             if ("r%d" % r.nid) in f.values:
-                body.append("    q.r%d = (u64)&s_res[%d]; q.r%d_sk = 0; q.r%d_sn = 0;" % (r.nid, slot_of[r.nid], r.nid, r.nid))
+                body.append("q.r%d = (u64)&s_res[%d]; q.r%d_sk = 0; q.r%d_sn = 0;" % (r.nid, slot_of[r.nid], r.nid, r.nid))
+        body.append("for (i64 k = kfirst; k < p.K; k += kstep) {")
+        body.append("    const i64 knext = k + kstep;")
         body.append("    float a[%d]; int ai[%d];" % (nrmax, nrmax))
+        n_launch = len(ems) + (0 if red_out else 1)
         for i, (em, rs, outs) in enumerate(ems):
-            body.append("    rr_reduce<S%d, P, %d, %d, %d>(q, k, cx, a, ai, sv, si);" % (i, V, threads, unroll))
+            last = red_out and i == len(ems) - 1
+            body.append("    rr_pass<S%d, ST, P, %d, %d, %d, %s, %s>(q, p, k, knext, cx, dyn, bars, a, ai, sv, si);"
+                        % (i, V, threads, unroll, "true" if i == 0 else "false", "true" if last else "false"))
             body.append("    rr_combine<S%d, %d, %d>(cx, a, ai, &slots[%d][0][0][0], &s_res[%d]);"
                         % (i, V, C, i, slot_of[rs[0].nid]))
         if red_out:
             body.append("    if (threadIdx.x == 0 && cx.rank == 0) SF<%d>::epilogue(q, k, a, ai);" % V)
         else:
-            body.append("    rr_ew<SE, P, %d, %d, %d>(q, k, cx);" % (V, threads, unroll))
-        body.append("    cx.row_parity ^= 1;")
+            body.append("    rr_pass<SE, ST, P, %d, %d, %d, false, true>(q, p, k, knext, cx, dyn, bars, a, ai, sv, si);"
+                        % (V, threads, unroll))
+        body.append("    rr_row_end(cx);")
         body.append("}")
         if C > 1:
             body.append("cluster_barrier();      // nobody leaves while a peer may still read its exchange slots")
@@ -857,6 +873,7 @@ class Planner(object):
 
         def __init__(self, st, fields, ka, ra, lanes_on_k, res_buf, avail_level, tables):
             self.unary, self.binary = tables
+            self.fast = self.binary is BINARY_FAST
             self.st = st
             self.f = fields
             self.ka, self.ra = ka, ra
@@ -1024,8 +1041,26 @@ class Planner(object):
                     ref = aname + "[0]"
                 self.names[key] = ref
                 return ref
-            args = [self.elem(a) for a in n.args]
-            expr = (self.unary[n.op] if n.kind == "u" else self.binary[n.op]).format(*args)
+            if (n.kind == "b" and n.op == "div" and self.fast and not self.var_n(n.args[1])
+                    and n.args[1].kind != "c"):
+                # dividing every element by a per-row value: multiply by its reciprocal, taken
+                # once per thread in the hoisted code (fast-math mode; within 2 ulp of the quotient)
+                den = n.args[1]
+                ref = self.hoist(den)
+                hname = "q%d" % den.nid
+                if hname not in self.hoisted:
+                    self.hoisted[hname] = hname
+                    if self.lk:
+                        self.h_decl.append("float %s[V];" % hname)
+                        self.h_lines.append("_Pragma(\"unroll\") for (int i = 0; i < V; ++i) h.%s[i] = 1.0f / %s;" % (hname, ref))
+                    else:
+                        self.h_decl.append("float %s;" % hname)
+                        self.h_lines.append("{ const int i = 0; (void)i; h.%s = 1.0f / %s; }" % (hname, ref))
+                rcp = ("h.%s[i]" % hname) if self.lk else ("h.%s" % hname)
+                expr = "(%s * %s)" % (self.elem(n.args[0]), rcp)
+            else:
+                args = [self.elem(a) for a in n.args]
+                expr = (self.unary[n.op] if n.kind == "u" else self.binary[n.op]).format(*args)
             name = "x%d" % n.nid
             self.e_lines.append("const float %s = %s;" % (name, expr))
             self.names[key] = name

@@ -6,6 +6,8 @@ without one, which is why the outputs are committed):
 
     python tests/golden/make_golden.py [/path/to/neon/checkout]
 
+(default: $NEON_REFERENCE, else a directory named "reference" beside this repository)
+
 neon is imported unmodified from the checkout.  Three modules it wants are not
 installed and have nothing to do with the numpy backend, so stand-ins are put in
 ``sys.modules`` before the import: ``future`` (py2/3 helpers), ``appdirs``
@@ -55,7 +57,8 @@ def import_reference_cpu(path):
 
 
 def main():
-    path = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    default = os.path.join(os.path.dirname(os.path.dirname(os.path.dirname(HERE))), "reference")
+    path = sys.argv[1] if len(sys.argv) > 1 else os.environ.get("NEON_REFERENCE", default)
     NervanaCPU = import_reference_cpu(path)
     from tests.cases import run_case, standard_cases, summarize
 

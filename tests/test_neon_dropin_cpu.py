@@ -11,7 +11,9 @@ import os
 import numpy as np
 import pytest
 
-REFERENCE = os.environ.get("NEON_REFERENCE", "/root/reference")
+# a neon checkout: $NEON_REFERENCE, else a directory named "reference" beside this repository
+REFERENCE = os.environ.get("NEON_REFERENCE") or os.path.join(
+    os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__)))), "reference")
 pytestmark = pytest.mark.skipif(not os.path.isdir(os.path.join(REFERENCE, "neon", "backends")),
                                 reason="no neon checkout on this machine")
 

@@ -8,7 +8,9 @@ from oracle.numpy_backend import OracleBackend
 from tests.cases import run_case, standard_cases, summarize
 
 CASES = standard_cases()
-REFERENCE = os.environ.get("NEON_REFERENCE", "/root/reference")
+# a neon checkout: $NEON_REFERENCE, else a directory named "reference" beside this repository
+REFERENCE = os.environ.get("NEON_REFERENCE") or os.path.join(
+    os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__)))), "reference")
 
 
 def _check(fingerprint, golden, prefix):
