@@ -328,6 +328,8 @@ def main():
 
     from neon_b200 import runtime as rt
     if world > 1:
+        # stdout carries the JSON line only: NCCL's version/debug banner goes to stderr
+        os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")
         from neon_b200.sharded import gen_sharded_backend
         be = gen_sharded_backend(rank=rank, world_size=world, device_id=local_rank, rng_seed=0)
         barrier, max_over_ranks = be.host_barrier, be.host_max
