@@ -142,6 +142,18 @@ b200_status b200_launch(uint64_t kernel, uint32_t grid_x, uint32_t grid_y, uint3
                         const void *params, uint32_t params_size,
                         uint32_t cluster_x, int32_t cooperative);
 
+/* ---- CUDA graphs: record the launches of a statement sequence once, replay them with one call
+ * no counterpart in the reference (it predates CUDA graphs); answers the same problem its
+ * memoised stacks do (neon/backends/nervanagpu.py:662-691): per-statement host work that is
+ * larger than the kernels for small tensors.  Between begin and end every launch / fill / device
+ * copy on `stream` is recorded instead of run; allocation, compilation and host transfers are not
+ * allowed there (run the sequence once eagerly first).  Pointers and numbers are frozen as
+ * recorded. */
+b200_status b200_graph_begin(uint64_t stream);
+b200_status b200_graph_end(uint64_t stream, uint64_t *graph_exec);
+b200_status b200_graph_launch(uint64_t graph_exec, uint64_t stream);
+b200_status b200_graph_destroy(uint64_t graph_exec);
+
 /* ---- random state: counter-based generator keyed by (seed, launch number)
  * replaces the 3x65536-word LFSR pool and gen_rng / rng_reset / rng_get_state /
  * rng_set_state (neon/backends/nervanagpu.py:901-1049, cuda_templates.py:138-186) */

@@ -58,6 +58,25 @@ class _Scratch(object):
                 pass
 
 
+class CapturedGraph(object):
+    """A recorded statement sequence (see ``B200Backend.capture``)."""
+
+    def __init__(self, backend, handle, launches):
+        self.backend, self.handle, self.launches = backend, handle, launches
+
+    def replay(self):
+        rt.graph_launch(self.handle, self.backend.stream)
+        self.backend.launches += self.launches
+
+    def __del__(self):
+        try:
+            if self.handle:
+                rt.graph_destroy(self.handle)
+                self.handle = 0
+        except Exception:
+            pass
+
+
 class B200Backend(OpTreeBackend):
     backend_name = "b200"
     tensor_cls = B200Tensor
@@ -160,6 +179,24 @@ class B200Backend(OpTreeBackend):
         """
         assert optree[0]["op"] == "assign"
         out, rhs = optree[1], optree[2]
+        # common case first (nervanagpu.py:1239-1270): no dot / transpose node and all
+        # reductions along one axis -> the program is one statement as it stands
+        stack = optree.traverse([])
+        axis, simple = None, True
+        for s in stack:
+            if type(s) is dict:
+                op = s["op"]
+                if op in OpCollection.reduction_ops:
+                    if axis is not None and s.get("axis") != axis:
+                        simple = False
+                        break
+                    axis = s.get("axis")
+                elif op == "dot" or op == "transpose":
+                    simple = False
+                    break
+        if simple:
+            self._run_stack(out, stack)
+            return out
         stmts = []
         self._temps_used = {}
         expr, tag = self._split(rhs, stmts)
@@ -317,7 +354,9 @@ class B200Backend(OpTreeBackend):
 
     # -- one statement ------------------------------------------------------------
     def _run(self, out, expr):
-        stack = OpTreeNode({"op": "assign"}, out, expr).traverse([])
+        self._run_stack(out, OpTreeNode({"op": "assign"}, out, expr).traverse([]))
+
+    def _run_stack(self, out, stack):
         rounding = self._rounding_bits(out)
         key = (program_key(stack), rounding)
         plan = self._plans.get(key)
@@ -426,6 +465,27 @@ class B200Backend(OpTreeBackend):
 
     def fill_normal(self, ary, mean=0, stdv=1):
         ary[:] = (self.rng.standard_normal(ary.shape) * stdv + mean).astype(ary.dtype)
+
+    def capture(self, fn):
+        """
+        Record the device work of ``fn()`` -- a sequence of assignments -- as a CUDA
+        graph and return it; ``graph.replay()`` then issues the whole sequence with one
+        call, which is what makes small, launch-bound statements (a few MB per tensor)
+        run at the speed of their kernels instead of the speed of the host.  ``fn`` runs
+        twice here: once eagerly (compiles, allocates temporaries), once recorded.
+        Tensor addresses and python numbers are frozen as recorded, and statements that
+        draw random numbers replay the same random words; ``fn`` must not read tensors
+        back or create them.
+        """
+        fn()
+        self.synchronize()
+        before = self.launches
+        rt.graph_begin(self.stream)
+        try:
+            fn()
+        finally:
+            handle = rt.graph_end(self.stream)
+        return CapturedGraph(self, handle, self.launches - before)
 
     def copy_transpose(self, a, out, axes=None, repeat=1):
         """out = a transposed (neon/backends/nervanagpu.py:3077-3118); two-dimensional

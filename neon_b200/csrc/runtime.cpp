@@ -579,6 +579,40 @@ b200_status b200_launch(uint64_t kernel, uint32_t gx, uint32_t gy, uint32_t gz,
     return B200_OK;
 }
 
+// ---------------------------------------------------------------- graphs
+b200_status b200_graph_begin(uint64_t stream) {
+    if (g.device < 0) return fail(B200_ERR_INVALID, "b200_init has not been called");
+    CU(cudaStreamBeginCapture(as_stream(stream), cudaStreamCaptureModeRelaxed));
+    return B200_OK;
+}
+
+b200_status b200_graph_end(uint64_t stream, uint64_t *graph_exec) {
+    if (!graph_exec) return fail(B200_ERR_INVALID, "graph_exec is null");
+    cudaGraph_t graph = nullptr;
+    cudaError_t e = cudaStreamEndCapture(as_stream(stream), &graph);
+    if (e != cudaSuccess || !graph) {
+        cudaGetLastError();
+        return fail(B200_ERR_CUDA, "cudaStreamEndCapture: %s", cudaGetErrorString(e));
+    }
+    cudaGraphExec_t exec = nullptr;
+    e = cudaGraphInstantiate(&exec, graph, 0);
+    cudaGraphDestroy(graph);
+    if (e != cudaSuccess) { cudaGetLastError(); return fail(B200_ERR_CUDA, "cudaGraphInstantiate: %s", cudaGetErrorString(e)); }
+    *graph_exec = reinterpret_cast<uint64_t>(exec);
+    return B200_OK;
+}
+
+b200_status b200_graph_launch(uint64_t graph_exec, uint64_t stream) {
+    if (!graph_exec) return fail(B200_ERR_INVALID, "null graph");
+    CU(cudaGraphLaunch(reinterpret_cast<cudaGraphExec_t>(graph_exec), as_stream(stream)));
+    return B200_OK;
+}
+
+b200_status b200_graph_destroy(uint64_t graph_exec) {
+    if (graph_exec) CU(cudaGraphExecDestroy(reinterpret_cast<cudaGraphExec_t>(graph_exec)));
+    return B200_OK;
+}
+
 // ---------------------------------------------------------------- rng
 b200_status b200_rng_seed(uint64_t seed) { g.seed = seed; g.launches = 0; return B200_OK; }
 

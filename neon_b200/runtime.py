@@ -65,6 +65,10 @@ SIGNATURES = {
     "b200_kernel_max_clusters": (i32, [u64, i32, i32, i32, i32, P(i32)]),
     "b200_cache_stats": (i32, [P(u64), P(u64), P(u64)]),
     "b200_launch": (i32, [u64, u32, u32, u32, u32, u32, u32, u32, u64, C.c_void_p, u32, u32, i32]),
+    "b200_graph_begin": (i32, [u64]),
+    "b200_graph_end": (i32, [u64, P(u64)]),
+    "b200_graph_launch": (i32, [u64, u64]),
+    "b200_graph_destroy": (i32, [u64]),
     "b200_rng_seed": (i32, [u64]),
     "b200_rng_next_key": (i32, [P(u32)]),
     "b200_rng_get_state": (i32, [P(u64)]),
@@ -279,6 +283,24 @@ def kernel_max_clusters(kernel, threads, smem, cluster, grid_blocks):
 def launch(kernel, grid, block, params, smem=0, stream=0, cluster=1, cooperative=False):
     check(lib().b200_launch(kernel, grid[0], grid[1], grid[2], block[0], block[1], block[2],
                             smem, stream, params, len(params), cluster, 1 if cooperative else 0))
+
+
+def graph_begin(stream=0):
+    check(lib().b200_graph_begin(stream))
+
+
+def graph_end(stream=0):
+    g = u64(0)
+    check(lib().b200_graph_end(stream, C.byref(g)))
+    return g.value
+
+
+def graph_launch(graph, stream=0):
+    check(lib().b200_graph_launch(graph, stream))
+
+
+def graph_destroy(graph):
+    check(lib().b200_graph_destroy(graph))
 
 
 def cache_stats():

@@ -158,11 +158,10 @@ class ShardedBackend(B200Backend):
         return t.set(ary.astype(t.dtype))
 
     # ---- one statement
-    def _run(self, out, expr):
-        stack = OpTreeNode({"op": "assign"}, out, expr).traverse([])
+    def _run_stack(self, out, stack):
         sharded = [s for s in stack if isinstance(s, ShardedTensor)]
         if not sharded:
-            return super(ShardedBackend, self)._run(out, expr)
+            return super(ShardedBackend, self)._run_stack(out, stack)
         lin = None
         if isinstance(out, ShardedTensor):
             lin = out.flat_of if out.flat_of else (out.shape[1], out.c0, out.local.shape[1])

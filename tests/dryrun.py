@@ -91,8 +91,7 @@ class DryRunBackend(B200Backend):
         self.dots = getattr(self, "dots", 0) + 1
         return C
 
-    def _run(self, out, expr):
-        stack = OpTreeNode({"op": "assign"}, out, expr).traverse([])
+    def _run_stack(self, out, stack):
         st = Statement(stack)
         passes = self._planner.plan(st, self._scratch_alloc, rounding=self._rounding_bits(out))
         for pz in passes:

@@ -460,6 +460,36 @@ def test_bfloat16_stochastic_rounding_bit_exact(b200):
     assert np.array_equal(z.get().astype(np.float32).view(np.uint32), want32.view(np.uint32))
 
 
+def test_graph_replay_of_a_statement_sequence(b200):
+    """A captured sequence replays with one call and computes the same values; inputs
+    changed in place between replays are seen (addresses are frozen, contents are not)."""
+    be = b200
+    rng = np.random.RandomState(1)
+    ah, bh = rng.randn(512, 128).astype(np.float32), rng.randn(512, 128).astype(np.float32)
+    ch = rng.uniform(-.5, .5, (512, 1)).astype(np.float32)
+    a, b, c = be.array(ah), be.array(bh), be.array(ch)
+    out, s, m = be.empty((512, 128)), be.empty((1, 128)), be.empty((1, 128), dtype=np.int32)
+
+    def step():
+        out[:] = be.maximum(a * b + c, 0)
+        s[:] = be.sum(out, axis=0)
+        m[:] = be.argmax(out, axis=0)
+
+    graph = be.capture(step)
+    assert graph.launches == 3
+    for trial in range(3):
+        ah = rng.randn(512, 128).astype(np.float32)
+        a.set(ah)
+        graph.replay()
+        want = np.maximum(ah.astype(np.float64) * bh + ch, 0)
+        np.testing.assert_allclose(out.get(), want, rtol=1e-5, atol=1e-6)
+        np.testing.assert_allclose(s.get(), want.sum(0, keepdims=True), rtol=1e-5, atol=1e-4)
+        assert np.array_equal(m.get(), out.get().argmax(0).reshape(1, -1))
+    # eager execution still works afterwards
+    step()
+    be.synchronize()
+
+
 def test_bench_flag_records_every_launch(tmp_path):
     """be.bench turns on per-launch timing (the reference prints msecs per compound kernel,
     float_ew.py:917-938); here the records are kept and can be dumped as JSON."""
