@@ -41,9 +41,9 @@ METRIC = "compound-optree effective HBM GB/s"
 WORKLOAD = ("cfg5: z=tanh(x)*sqrt(|y|)+0.5*x*y (fp16, stochastic rounding), "
             "total=sum(z), peak=max|z|")
 # dram__bytes_read.sum + dram__bytes_write.sum of the z kernel divided by its elements, from the
-# ncu capture of a 2^26-element launch (profiles/ew_kernel_cfg5_fp16_chain.md: 269.2 MB + 105.5 MB);
+# ncu capture of a 2^26-element launch (profiles/ew_kernel_cfg5_fp16_chain.md: 268.5 MB + 103.2 MB);
 # traffic grows in proportion to the elements, so a full launch is this times its element count
-Z_DRAM_BYTES_PER_ELEMENT = (269.218304e6 + 105.476864e6) / (1 << 26)
+Z_DRAM_BYTES_PER_ELEMENT = (268.460288e6 + 103.152128e6) / (1 << 26)
 
 
 def measured_peak():
