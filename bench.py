@@ -350,10 +350,22 @@ def main():
 
     from neon_b200 import runtime as rt
     if world > 1:
-        # stdout carries the JSON line only: NCCL's version/debug banner goes to stderr
-        os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")
         from neon_b200.sharded import gen_sharded_backend
-        be = gen_sharded_backend(rank=rank, world_size=world, device_id=local_rank, rng_seed=0)
+        # stdout carries the JSON line only: whatever NCCL prints while the communicator
+        # comes up (its version banner, debug lines) is sent to stderr
+        sys.stdout.flush()
+        saved = os.dup(1)
+        os.dup2(2, 1)
+        try:
+            be = gen_sharded_backend(rank=rank, world_size=world, device_id=local_rank, rng_seed=0)
+            warm = be.empty((1, 1))
+            warm[:] = 0
+            be.allreduce_tensor(warm)
+            be.synchronize()
+        finally:
+            sys.stdout.flush()
+            os.dup2(saved, 1)
+            os.close(saved)
         barrier, max_over_ranks = be.host_barrier, be.host_max
     else:
         from neon_b200 import gen_backend
