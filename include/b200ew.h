@@ -183,6 +183,30 @@ b200_status b200_gemm(uint64_t a, int32_t a_dtype, int64_t a_stride0, int64_t a_
                       uint64_t c, int32_t c_dtype, int64_t c_stride0, int64_t c_stride1,
                       int32_t m, int32_t n, int32_t k, float alpha, float beta, uint64_t stream);
 
+/* ---- dimension shuffle (copy with permuted axes)
+ * replaces copy_transpose (neon/backends/nervanagpu.py:3077-3118; kernel generator
+ * _get_copy_transpose_kernel in neon/backends/convolution.py), which the data iterator
+ * calls once per minibatch to turn (examples, features) rows into neon's (features, batch)
+ * layout (neon/data/dataiterator.py:144-202).  The copy is described in OUTPUT dimension
+ * order: shape[i] is the extent of output dimension i, dst_strides[i] the output's element
+ * stride there and src_strides[i] the element stride of the input axis that lands there
+ * (a.strides[axes[i]]).  Views are fine (any non-negative strides); the two tensors must
+ * not overlap.  elem_bytes in {1,2,4,8}; at most B200_SHUFFLE_MAX_DIMS dimensions. */
+#define B200_SHUFFLE_MAX_DIMS 8
+b200_status b200_dimshuffle(uint64_t dst, uint64_t src, int32_t elem_bytes, int32_t ndim,
+                            const int64_t *shape, const int64_t *dst_strides,
+                            const int64_t *src_strides, uint64_t stream);
+
+/* ---- Kahan-compensated accumulation
+ * replaces NervanaGPU.compensated_sum (neon/backends/nervanagpu.py:1896-1917; kernel text
+ * neon/backends/float_ew.py:944-1037): sum += add*add_scale - cmp*cmp_scale with the
+ * rounding error of the stored sum kept in cmp.  sum, cmp and add are contiguous arrays of
+ * `count` elements of one dtype (f32, f16, bf16).  rounding_bits > 0 rounds the new sum
+ * stochastically to that many mantissa bits (capped at 15 / 10 / 7) with the library's
+ * seeded generator, and advances its launch counter; 0 rounds to nearest. */
+b200_status b200_compensated_sum(uint64_t sum, uint64_t cmp, uint64_t add, int32_t dtype, uint64_t count,
+                                 float cmp_scale, float add_scale, int32_t rounding_bits, uint64_t stream);
+
 /* ---- the same reduction for callers that cannot allocate device memory
  * No counterpart in the reference.  Meant for hosts where cudaMalloc is off
  * limits when the call is made (a framework pool owns the device, a latency-

@@ -12,7 +12,7 @@ lookup tables) raise ``NotImplementedError``.
 import numpy as np
 
 from . import runtime as rt
-from .lowering import BoundPlan, Planner, Statement, program_key
+from .lowering import BoundPlan, Planner, Statement, dtype_code, program_key
 from .optree import OpCollection, OpTreeBackend, OpTreeNode, Tensor
 from .tensor import B200Tensor
 
@@ -488,11 +488,44 @@ class B200Backend(OpTreeBackend):
         return CapturedGraph(self, handle, self.launches - before)
 
     def copy_transpose(self, a, out, axes=None, repeat=1):
-        """out = a transposed (neon/backends/nervanagpu.py:3077-3118); two-dimensional
-        tensors only, as one strided element-wise statement."""
-        if len(a.shape) != 2 or (axes is not None and tuple(axes) != (1, 0)):
-            raise NotImplementedError("copy_transpose of more than two dimensions")
-        out[:] = a.T
+        """out = numpy.transpose(a, axes) for tensors of any rank, views included
+        (neon/backends/nervanagpu.py:3077-3118): one shared-memory tiled shuffle kernel."""
+        assert a.dtype == out.dtype
+        assert a.size == out.size
+        assert a.gpudata != out.gpudata
+        if axes is None:
+            axes = tuple(range(len(a.shape) - 1, -1, -1))
+        elif type(axes) is not tuple:
+            axes = tuple(axes)
+        assert all(out.shape[i] == a.shape[x] for i, x in enumerate(axes))
+        if a.take_array is not None or out.take_array is not None:
+            raise NotImplementedError("copy_transpose of a tensor indexed with an array")
+        for _ in range(max(int(repeat), 1)):
+            rt.dimshuffle(out.gpudata, a.gpudata, a.dtype.itemsize, out.shape, out.strides,
+                          [a.strides[x] for x in axes], self.stream)
+        self.launches += max(int(repeat), 1)
+        return out
+
+    def compensated_sum(self, sum_tensor, cmp_tensor, add_tensor, cmp_scale=1.0, add_scale=1.0):
+        """Kahan-compensated ``sum_tensor += add_tensor*add_scale`` with the lost low-order
+        bits kept in ``cmp_tensor`` (neon/backends/nervanagpu.py:1896-1917); the new sum is
+        rounded stochastically when ``sum_tensor.rounding`` is set.  Contiguous tensors of
+        one floating-point dtype."""
+        if cmp_tensor.kahan_reset and cmp_tensor.kahan_count > cmp_tensor.kahan_reset:
+            cmp_scale = 0
+            cmp_tensor.kahan_count = 0
+        assert sum_tensor.dtype.type == cmp_tensor.dtype.type == add_tensor.dtype.type
+        assert sum_tensor.size == cmp_tensor.size == add_tensor.size
+        for t in (sum_tensor, cmp_tensor, add_tensor):
+            if not t.is_contiguous or t.take_array is not None:
+                raise ValueError("compensated_sum needs contiguous tensors")
+        cmp_tensor.kahan_count += 1
+        rounding = sum_tensor.rounding
+        bits = 10 if rounding is True else int(rounding or 0)
+        rt.compensated_sum(sum_tensor.gpudata, cmp_tensor.gpudata, add_tensor.gpudata,
+                           dtype_code(sum_tensor.dtype), sum_tensor.size, float(cmp_scale), float(add_scale),
+                           bits, self.stream)
+        self.launches += 1
 
     # ------------------------------------------------------------------ timing marks (nervanagpu.py:3138-3177)
     def init_mark(self):

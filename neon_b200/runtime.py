@@ -77,6 +77,8 @@ SIGNATURES = {
     "b200_reduce_full": (i32, [u64, i32, u64, i32, i32, u64, u64, u64]),
     "b200_gemm": (i32, [u64, i32, C.c_int64, C.c_int64, u64, i32, C.c_int64, C.c_int64,
                         u64, i32, C.c_int64, C.c_int64, i32, i32, i32, C.c_float, C.c_float, u64]),
+    "b200_dimshuffle": (i32, [u64, u64, i32, i32, P(C.c_int64), P(C.c_int64), P(C.c_int64), u64]),
+    "b200_compensated_sum": (i32, [u64, u64, u64, i32, u64, C.c_float, C.c_float, i32, u64]),
     "b200_reduce_full_noalloc_max_count": (u64, []),
     "b200_reduce_full_noalloc": (i32, [u64, i32, u64, i32, i32, u64, u64]),
     "b200_comm_unique_id": (i32, [P(C.c_uint8)]),
@@ -341,6 +343,18 @@ def reduce_full(src, dtype, count, op, absolute, out, scratch, stream=0):
 def gemm(a, a_dt, a_strides, b, b_dt, b_strides, c, c_dt, c_strides, m, n, k, alpha=1.0, beta=0.0, stream=0):
     check(lib().b200_gemm(a, a_dt, a_strides[0], a_strides[1], b, b_dt, b_strides[0], b_strides[1],
                           c, c_dt, c_strides[0], c_strides[1], m, n, k, alpha, beta, stream))
+
+
+def dimshuffle(dst, src, elem_bytes, shape, dst_strides, src_strides, stream=0):
+    """Permuted copy; all three lists are in output dimension order, strides in elements."""
+    n = len(shape)
+    arr = C.c_int64 * n
+    check(lib().b200_dimshuffle(dst, src, elem_bytes, n, arr(*shape), arr(*dst_strides), arr(*src_strides), stream))
+
+
+def compensated_sum(sum_ptr, cmp_ptr, add_ptr, dtype, count, cmp_scale, add_scale, rounding_bits, stream=0):
+    check(lib().b200_compensated_sum(sum_ptr, cmp_ptr, add_ptr, dtype, count, cmp_scale, add_scale,
+                                     rounding_bits, stream))
 
 
 def reduce_full_noalloc(src, dtype, count, op, absolute, out, stream=0):

@@ -281,6 +281,10 @@ class OracleBackend(OpTreeBackend):
     def zeros_like(self, other, name=None, persist_values=True):
         return self.zeros(other.shape, dtype=self.default_dtype, name=name)
 
+    def copy_transpose(self, a, out, axes=None, repeat=1):
+        """numpy.transpose into ``out`` (nervanacpu.py:1046-1051)."""
+        out._tensor[:] = np.transpose(a._tensor, axes).copy()
+
     def rng_reset(self):
         self.rng.set_state(self.init_rng_state)
 

@@ -30,6 +30,9 @@ pattern (integer add of the top random bits, mask) rather than with fma.rz;
 ``sr_f32`` below keeps the reference's float formulation, and the bit-exact GPU
 test shows the two agree.
 
+``compensated_sum`` restates the Kahan accumulation kernel (float_ew.py:944-1037),
+which exists only as GPU kernel text in the reference.
+
 Parity status: pinned by known answers in tests/test_sround.py, among them the
 case of neon's tests/test_backend_sr.py:52-71 (1.1 at one mantissa bit gives
 only 1.0 or 1.5, with the up-probability equal to the discarded fraction).
@@ -182,4 +185,27 @@ def store(val, dtype, rounding=0, urand=None):
         return sr_f32(val, urand, mb) if mb else np.asarray(val, np.float32)
     if dtype == np.float16:
         return sr_f16(val, urand, mb) if mb else nearest_f16(val)
+    if dtype.name == "bfloat16":            # no counterpart in the reference: fp32 rule, 7 bits at most
+        if mb:
+            return sr_f32(val, urand, min(mb, 7)).astype(dtype)     # exact: low 16 bits are clear
+        return np.asarray(val, np.float32).astype(dtype)
     return sr_int(val, urand, dtype) if mb else nearest_int(val, dtype)
+
+
+def compensated_sum(s, c, a, cmp_scale=1.0, add_scale=1.0, rounding=0, urand=None):
+    """One step of the Kahan accumulation kernel (float_ew.py:958-993): returns the new
+    (sum, cmp) arrays in the dtype of ``s``.  fp32 arithmetic; the new sum is rounded
+    with ``store`` (stochastically when ``rounding``), the compensation to nearest.
+    The kernel text leaves a*add_scale - c*cmp_scale to the compiler, which may fuse
+    it; the difference is taken exactly here and rounded once, which is the same
+    value whenever the two products are exact (scales that are powers of two)."""
+    dtype = np.asarray(s).dtype
+    s32 = np.asarray(s).astype(np.float32)
+    c32 = np.asarray(c).astype(np.float32)
+    a32 = np.asarray(a).astype(np.float32)
+    y32 = (a32.astype(np.float64) * np.float64(np.float32(add_scale))
+           - c32.astype(np.float64) * np.float64(np.float32(cmp_scale))).astype(np.float32)
+    t = store((s32 + y32).astype(np.float32), dtype, rounding, urand)
+    t32 = t.astype(np.float32)
+    cmp_new = store(((t32 - s32).astype(np.float32) - y32).astype(np.float32), dtype)
+    return t, cmp_new

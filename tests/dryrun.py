@@ -91,6 +91,14 @@ class DryRunBackend(B200Backend):
         self.dots = getattr(self, "dots", 0) + 1
         return C
 
+    def copy_transpose(self, a, out, axes=None, repeat=1):
+        axes = tuple(range(len(a.shape) - 1, -1, -1)) if axes is None else tuple(axes)
+        assert a.dtype == out.dtype and a.size == out.size and a.gpudata != out.gpudata
+        assert all(out.shape[i] == a.shape[x] for i, x in enumerate(axes))
+        self.launches += 1
+        self.shuffles = getattr(self, "shuffles", 0) + 1
+        return out
+
     def _run_stack(self, out, stack):
         st = Statement(stack)
         passes = self._planner.plan(st, self._scratch_alloc, rounding=self._rounding_bits(out))

@@ -114,3 +114,33 @@ def test_neon_layers_run_unmodified(neon_env):
         layer.fprop(x)
         layer.bprop(err)
         assert len(be.passes) - before >= expected[type(layer).__name__], type(layer).__name__
+
+
+def test_neon_array_iterator_runs_unmodified(neon_env):
+    """ArrayIterator (neon/data/dataiterator.py:86-202): the dataset sits on the device as
+    (examples, features); every minibatch is one copy_transpose of a row slice into the
+    (features, batch) buffer plus one onehot statement for the labels, and the last, short
+    minibatch wraps around to the first examples."""
+    be = neon_env
+    # the module file itself: the neon.data package also pulls in readers that need h5py
+    import importlib.util
+    spec = importlib.util.spec_from_file_location(
+        "neon_dataiterator_unmodified", os.path.join(REFERENCE, "neon", "data", "dataiterator.py"))
+    module = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(module)
+    ArrayIterator = module.ArrayIterator
+    rng = np.random.RandomState(0)
+    ndata, nfeat, nclass = 200, 12, 5
+    X = rng.rand(ndata, nfeat).astype(np.float32)
+    y = rng.randint(0, nclass, ndata)
+    it = ArrayIterator(X, y, nclass=nclass)
+    expected = -(-ndata // be.bsz)
+    assert it.nbatches == expected
+    shuffles, passes, batches = getattr(be, "shuffles", 0), len(be.passes), 0
+    for xb, yb in it:
+        assert tuple(xb.shape) == (nfeat, be.bsz) and tuple(yb.shape) == (nclass, be.bsz)
+        batches += 1
+    assert batches == expected          # (the iterator now starts its next epoch after the wrapped part)
+    # one transpose + one onehot per minibatch, one more of each for the wrapped part
+    assert be.shuffles - shuffles == batches + 1
+    assert len(be.passes) - passes == batches + 1
