@@ -12,9 +12,10 @@
 //   tile  when the input's unit-stride dimension and the output's unit-stride
 //         dimension differ: a T x T element tile goes through shared memory so
 //         that global reads run along the input's fast dimension and global
-//         writes along the output's.  T = 32 elements of 4 or 8 bytes, 64 of 2
-//         bytes, 128 of 1 byte, so a warp always moves 128 contiguous bytes
-//         per row (as one 32-bit access per lane when alignment allows).
+//         writes along the output's.  Lanes move 16-byte vectors (8 or 4 bytes
+//         when the two tile dimensions are short), sixteen lanes to a row, and
+//         each thread transposes an N x N micro-block in registers, so shared
+//         memory sees only whole vectors and no bank conflicts.
 //   copy  otherwise (same fast dimension, or no unit stride at all): lanes run
 //         along the output's innermost dimension; when that dimension is
 //         contiguous in both tensors and everything is 16-byte aligned the
@@ -67,98 +68,146 @@ __device__ __forceinline__ void rest_offsets(const ShP& p, int first, i64 r, i64
     }
 }
 
-// dims[0]: input stride 1 (index i);  dims[1]: output stride 1 (index o)
-template <int ES>
+// ---- vectors of U bytes held as 32-bit words; element k of such a vector
+template <int ES> __device__ __forceinline__ u64 vget(const u32* w, int k) {
+    if constexpr (ES == 8) return (u64)w[2 * k] | ((u64)w[2 * k + 1] << 32);
+    else if constexpr (ES == 4) return w[k];
+    else if constexpr (ES == 2) return (w[k >> 1] >> (16 * (k & 1))) & 0xffffu;
+    else return (w[k >> 2] >> (8 * (k & 3))) & 0xffu;
+}
+template <int ES> __device__ __forceinline__ void vor(u32* w, int k, u64 x) {      // into a zeroed vector
+    if constexpr (ES == 8) { w[2 * k] = (u32)x; w[2 * k + 1] = (u32)(x >> 32); }
+    else if constexpr (ES == 4) w[k] = (u32)x;
+    else if constexpr (ES == 2) w[k >> 1] |= (u32)x << (16 * (k & 1));
+    else w[k >> 2] |= (u32)x << (8 * (k & 3));
+}
+template <int U> __device__ __forceinline__ void vld_global(const unsigned char* p, u32* w) {
+    if constexpr (U == 16) { const uint4 a = __ldg(reinterpret_cast<const uint4*>(p)); w[0] = a.x; w[1] = a.y; w[2] = a.z; w[3] = a.w; }
+    else if constexpr (U == 8) { const uint2 a = __ldg(reinterpret_cast<const uint2*>(p)); w[0] = a.x; w[1] = a.y; }
+    else w[0] = __ldg(reinterpret_cast<const u32*>(p));
+}
+template <int U> __device__ __forceinline__ void vst(void* p, const u32* w) {
+    if constexpr (U == 16) *reinterpret_cast<uint4*>(p) = make_uint4(w[0], w[1], w[2], w[3]);
+    else if constexpr (U == 8) *reinterpret_cast<uint2*>(p) = make_uint2(w[0], w[1]);
+    else *reinterpret_cast<u32*>(p) = w[0];
+}
+template <int U> __device__ __forceinline__ void vld_shared(const void* p, u32* w) {
+    if constexpr (U == 16) { const uint4 a = *reinterpret_cast<const uint4*>(p); w[0] = a.x; w[1] = a.y; w[2] = a.z; w[3] = a.w; }
+    else if constexpr (U == 8) { const uint2 a = *reinterpret_cast<const uint2*>(p); w[0] = a.x; w[1] = a.y; }
+    else w[0] = *reinterpret_cast<const u32*>(p);
+}
+
+// Tile kernel.  dims[0]: input stride 1 (index i);  dims[1]: output stride 1 (index o).
+// A lane moves vectors of U bytes = N elements.  The tile is T x T elements, T = 16 N:
+// thread (l, r) loads the N x N micro-block at columns i = N l .., rows o = N r .. as N
+// vectors (sixteen lanes cover 16 U contiguous bytes of an input row), transposes it in
+// registers, and stores N vectors into the shared tile, which is laid out [i][o] so that
+// the second phase reads whole vectors along o and writes 16 U contiguous bytes of an
+// output row.  Column vectors of tile row i are rotated by i / N: both phases then touch
+// every bank group once per wavefront.
+template <int ES, int U>
 __global__ void __launch_bounds__(256) shuffle_tile_kernel(const __grid_constant__ ShP p) {
     typedef typename elem_t<ES>::type E;
-    constexpr int VEC = ES >= 4 ? 1 : 4 / ES;      // elements per 32-bit word
-    constexpr int T = 32 * VEC;
-    __shared__ __align__(16) E tile[T][T + VEC];   // [o][i]; the pad keeps column reads off one bank
+    constexpr int N = U / ES;
+    constexpr int T = 16 * N;
+    constexpr int UW = U / 4;
+    __shared__ __align__(16) u32 tile[T][16 * UW];
 
-    const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+    const int l = threadIdx.x & 15, r = threadIdx.x >> 4;
     i64 b = blockIdx.x;
     const i64 t0 = b % p.tiles0; b /= p.tiles0;
     const i64 t1 = b % p.tiles1; b /= p.tiles1;
     i64 so = 0, dof = 0;
     rest_offsets(p, 2, b, so, dof);
-    const i64 i0 = t0 * T, o0 = t1 * T;
+    const i64 ni = p.n[0], no = p.n[1];
     const E* __restrict__ src = reinterpret_cast<const E*>(p.src) + so;
     E* __restrict__ dst = reinterpret_cast<E*>(p.dst) + dof;
-    const i64 ni = p.n[0], no = p.n[1];
 
-    // global -> shared, lanes along i
-#pragma unroll 4
-    for (int ol = ty; ol < T; ol += 8) {
-        const i64 o = o0 + ol;
-        if (o >= no) break;
-        const i64 i = i0 + tx * VEC;
-        const E* row = src + o * p.ss[1];
-        bool done = false;
-        if constexpr (VEC > 1) {
-            if (p.src_vec && i + VEC <= ni) {
-                const u32 w = __ldg(reinterpret_cast<const u32*>(row + i));
-                *reinterpret_cast<u32*>(&tile[ol][tx * VEC]) = w;
-                done = true;
+    {   // global -> registers -> shared
+        const i64 i = t0 * T + N * l;
+        const i64 o = t1 * T + N * r;
+        u32 in[N][UW];
+        const bool whole = p.src_vec && i + N <= ni;
+#pragma unroll
+        for (int v = 0; v < N; ++v) {
+#pragma unroll
+            for (int q = 0; q < UW; ++q) in[v][q] = 0;
+            if (o + v < no) {
+                const E* row = src + (o + v) * p.ss[1] + i;
+                if (whole) vld_global<U>(reinterpret_cast<const unsigned char*>(row), in[v]);
+                else {
+#pragma unroll
+                    for (int e = 0; e < N; ++e)
+                        if (i + e < ni) vor<ES>(in[v], e, (u64)__ldg(row + e));
+                }
             }
         }
-        if (!done) {
 #pragma unroll
-            for (int v = 0; v < VEC; ++v)
-                if (i + v < ni) tile[ol][tx * VEC + v] = __ldg(row + i + v);
+        for (int w = 0; w < N; ++w) {
+            u32 out[UW];
+#pragma unroll
+            for (int q = 0; q < UW; ++q) out[q] = 0;
+#pragma unroll
+            for (int v = 0; v < N; ++v) vor<ES>(out, v, vget<ES>(in[v], w));
+            vst<U>(&tile[N * l + w][((r + l) & 15) * UW], out);
         }
     }
     __syncthreads();
-    // shared -> global, lanes along o
-#pragma unroll 4
-    for (int il = ty; il < T; il += 8) {
-        const i64 i = i0 + il;
-        if (i >= ni) break;
-        const i64 o = o0 + tx * VEC;
-        E* row = dst + i * p.ds[0];
-        bool done = false;
-        if constexpr (VEC > 1) {
-            if (p.dst_vec && o + VEC <= no) {
-                u32 w = 0;
+    {   // shared -> global: lane l covers o = N l .., thread row r covers i = N r ..
+        const i64 o = t1 * T + N * l;
+        const bool whole = p.dst_vec && o + N <= no;
 #pragma unroll
-                for (int v = 0; v < VEC; ++v) w |= (u32)tile[tx * VEC + v][il] << (8 * ES * v);
-                *reinterpret_cast<u32*>(row + o) = w;
-                done = true;
+        for (int w = 0; w < N; ++w) {
+            const i64 i = t0 * T + N * r + w;
+            if (i >= ni || o >= no) continue;
+            u32 x[UW];
+            vld_shared<U>(&tile[N * r + w][((l + r) & 15) * UW], x);
+            E* row = dst + i * p.ds[0] + o;
+            if (whole) vst<U>(row, x);
+            else {
+#pragma unroll
+                for (int e = 0; e < N; ++e)
+                    if (o + e < no) row[e] = (E)vget<ES>(x, e);
             }
-        }
-        if (!done) {
-#pragma unroll
-            for (int v = 0; v < VEC; ++v)
-                if (o + v < no) row[o + v] = tile[tx * VEC + v][il];
         }
     }
 }
 
-// dims[0]: lane dimension with any strides; a block moves 1024 consecutive indices of it
+// Copy kernel.  dims[0]: lane dimension (any strides), dims[1]: the next one (extent 1 when
+// there is none).  The 256 threads form bx lanes x (256 / bx) rows, bx a power of two picked by
+// the host so that short lane dimensions still fill the block; a thread moves up to four
+// elements, bx apart.
 template <int ES>
 __global__ void __launch_bounds__(256) shuffle_copy_kernel(const __grid_constant__ ShP p) {
     typedef typename elem_t<ES>::type E;
+    const int bx_log2 = p.src_vec;                     // (field reused by this kernel)
+    const int bx = 1 << bx_log2;
+    const int tx = threadIdx.x & (bx - 1), ty = threadIdx.x >> bx_log2;
     i64 b = blockIdx.x;
-    const i64 c = b % p.tiles0; b /= p.tiles0;
+    const i64 t0 = b % p.tiles0; b /= p.tiles0;
+    const i64 t1 = b % p.tiles1; b /= p.tiles1;
     i64 so = 0, dof = 0;
-    rest_offsets(p, 1, b, so, dof);
-    const E* __restrict__ src = reinterpret_cast<const E*>(p.src) + so;
-    E* __restrict__ dst = reinterpret_cast<E*>(p.dst) + dof;
-    const i64 base = c * 1024 + threadIdx.x;
+    rest_offsets(p, 2, b, so, dof);
+    const i64 j = t1 * (256 >> bx_log2) + ty;
+    if (j >= p.n[1]) return;
+    const E* __restrict__ src = reinterpret_cast<const E*>(p.src) + so + j * p.ss[1];
+    E* __restrict__ dst = reinterpret_cast<E*>(p.dst) + dof + j * p.ds[1];
+    const i64 base = t0 * (4 * bx) + tx;
     E v[4];
 #pragma unroll
     for (int u = 0; u < 4; ++u) {
-        const i64 i = base + u * 256;
+        const i64 i = base + u * bx;
         if (i < p.n[0]) v[u] = src[i * p.ss[0]];
     }
 #pragma unroll
     for (int u = 0; u < 4; ++u) {
-        const i64 i = base + u * 256;
+        const i64 i = base + u * bx;
         if (i < p.n[0]) dst[i * p.ds[0]] = v[u];
     }
 }
 
-template <int ES> cudaError_t launch_tile(const ShP& p, unsigned grid, cudaStream_t s) {
-    shuffle_tile_kernel<ES><<<grid, 256, 0, s>>>(p);
+template <int ES, int U> cudaError_t launch_tile(const ShP& p, unsigned grid, cudaStream_t s) {
+    shuffle_tile_kernel<ES, U><<<grid, 256, 0, s>>>(p);
     return cudaGetLastError();
 }
 template <int ES> cudaError_t launch_copy(const ShP& p, unsigned grid, cudaStream_t s) {
@@ -239,9 +288,17 @@ extern "C" b200_status b200_dimshuffle(uint64_t dst, uint64_t src, int32_t elem_
             }
         }
     }
+    if (!tiled) {
+        // second block dimension of the copy kernel: the innermost of the other dimensions
+        for (int d = nd - 1; d >= 0; --d)
+            if (d != lead[0]) { lead[1] = d; break; }
+    }
     int k = 0;
-    for (int j = 0; j < 2; ++j)
-        if (lead[j] >= 0) { p.n[k] = n[lead[j]]; p.ds[k] = ds[lead[j]]; p.ss[k] = ss[lead[j]]; ++k; }
+    for (int j = 0; j < 2; ++j) {
+        if (lead[j] >= 0) { p.n[k] = n[lead[j]]; p.ds[k] = ds[lead[j]]; p.ss[k] = ss[lead[j]]; }
+        else { p.n[k] = 1; p.ds[k] = 0; p.ss[k] = 0; }
+        ++k;
+    }
     i64 rest = 1;
     for (int d = 0; d < nd; ++d) {
         if (d == lead[0] || d == lead[1]) continue;
@@ -254,26 +311,55 @@ extern "C" b200_status b200_dimshuffle(uint64_t dst, uint64_t src, int32_t elem_
     cudaStream_t s = static_cast<cudaStream_t>(b200_detail_stream(stream));
     cudaError_t e;
     i64 blocks;
+    int U = 0;                                   // bytes a lane of the tile kernel moves at once
     if (tiled) {
-        const int T = es >= 4 ? 32 : 32 * (4 / es);
+        // the widest vector whose tiles (T = 16 U / es elements a side) waste the least area
+        i64 best = 0;
+        for (int u = es == 1 ? 8 : 16; u >= 2 * es && u >= 4; u >>= 1) {
+            const i64 T = 16 * (u / es);
+            const i64 area = ((p.n[0] + T - 1) / T * T) * ((p.n[1] + T - 1) / T * T);
+            if (!U || area < best) { U = u; best = area; }
+        }
+        const int T = 16 * (U / es);
         p.tiles0 = (p.n[0] + T - 1) / T;
         p.tiles1 = (p.n[1] + T - 1) / T;
         blocks = p.tiles0 * p.tiles1 * rest;
-        bool sv = src % 4 == 0, dv = dst % 4 == 0;
+        bool sv = src % U == 0, dv = dst % U == 0;
         for (int d = 0; d < k; ++d) {
-            if (d != 0 && (p.ss[d] * es) % 4) sv = false;
-            if (d != 1 && (p.ds[d] * es) % 4) dv = false;
+            if (d != 0 && (p.ss[d] * es) % U) sv = false;
+            if (d != 1 && (p.ds[d] * es) % U) dv = false;
         }
         p.src_vec = sv; p.dst_vec = dv;
     } else {
-        p.tiles0 = (p.n[0] + 1023) / 1024;
-        blocks = p.tiles0 * rest;
+        // lanes along dims[0]: the widest of 256/128/64/32 that wastes the fewest slots of the
+        // 4 bx elements a block row covers
+        int bx_log2 = 8;
+        if (p.n[1] > 1) {
+            i64 best = (p.n[0] + 1023) / 1024 * 1024;
+            for (int bl = 7; bl >= 5; --bl) {
+                const i64 chunk = 4ll << bl;
+                const i64 padded = (p.n[0] + chunk - 1) / chunk * chunk;
+                if (padded < best) { best = padded; bx_log2 = bl; }
+            }
+        }
+        p.src_vec = bx_log2;
+        p.tiles0 = (p.n[0] + (4ll << bx_log2) - 1) / (4ll << bx_log2);
+        p.tiles1 = (p.n[1] + (256 >> bx_log2) - 1) / (256 >> bx_log2);
+        blocks = p.tiles0 * p.tiles1 * rest;
     }
     if (blocks > 0x7fffffffll) return b200_detail_fail(B200_ERR_UNSUPPORTED, "b200_dimshuffle: more than 2^31 blocks");
     const unsigned grid = (unsigned)blocks;
     if (tiled) {
-        e = es == 1 ? launch_tile<1>(p, grid, s) : es == 2 ? launch_tile<2>(p, grid, s)
-          : es == 4 ? launch_tile<4>(p, grid, s) : launch_tile<8>(p, grid, s);
+        switch (es * 100 + U) {
+        case 108: e = launch_tile<1, 8>(p, grid, s); break;
+        case 104: e = launch_tile<1, 4>(p, grid, s); break;
+        case 216: e = launch_tile<2, 16>(p, grid, s); break;
+        case 208: e = launch_tile<2, 8>(p, grid, s); break;
+        case 204: e = launch_tile<2, 4>(p, grid, s); break;
+        case 416: e = launch_tile<4, 16>(p, grid, s); break;
+        case 408: e = launch_tile<4, 8>(p, grid, s); break;
+        default: e = launch_tile<8, 16>(p, grid, s); break;
+        }
     } else {
         e = es == 1 ? launch_copy<1>(p, grid, s) : es == 2 ? launch_copy<2>(p, grid, s)
           : es == 4 ? launch_copy<4>(p, grid, s) : es == 8 ? launch_copy<8>(p, grid, s) : launch_copy<16>(p, grid, s);
