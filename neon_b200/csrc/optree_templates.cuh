@@ -161,11 +161,11 @@ DEV float rcp_approx(float x) { float r; asm("rcp.approx.ftz.f32 %0, %1;" : "=f"
 DEV float fast_sqrt(float x) { float r; asm("sqrt.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(x)); return r; }
 DEV float fast_div(float a, float b) { float r; asm("div.approx.f32 %0, %1, %2;" : "=f"(r) : "f"(a), "f"(b)); return r; }
 // tanh: odd polynomial x + x^3 Q(x^2) below 0.6 (least-squares fit, 1.2 ulp),
-// 1 - 2t/(1+t) with t = e^(-2|x|) above it
+// 1 - 2/(e^(2|x|) + 1) with the sign of x above it
 DEV float fast_tanh(float x) {
     const float ax = fabsf(x);
-    const float t = ex2_approx(ax * -2.885390082f);
-    float big = __fmaf_rn(t * -2.0f, rcp_approx(1.0f + t), 1.0f);
+    const float e = ex2_approx(ax * 2.885390082f);
+    float big = __fmaf_rn(rcp_approx(e + 1.0f), -2.0f, 1.0f);
     big = copysignf(big, x);
     const float u = x * x;
     float q = __fmaf_rn(u, -0.005895146634429693f, 0.02079596184194088f);
@@ -189,12 +189,13 @@ DEV u32 rng_hash(const Rng& g, u32 lo, u32 hi) {
     return x;
 }
 DEV u32 rng_bits(const Rng& g, u64 idx) { return rng_hash(g, (u32)idx, (u32)(idx >> 32)); }
-// 16-bit float stores share one hash between elements 2q and 2q+1: the even one
-// reads it as is, the odd one with its halves swapped
-// 16-bit float stores need 13 random bits per element, so eight neighbouring
-// elements share ONE hash: group = idx >> 3 is hashed, the four element pairs of
-// the group take successive steps of a linear congruential chain from it, and
-// the odd element of a pair reads its word with the halves swapped.
+// 16-bit float stores need at most 13 random bits per element (the top bits of
+// the word), so eight neighbouring elements share ONE hash: group = idx >> 3 is
+// hashed, the four element pairs of the group take successive steps of a linear
+// congruential chain from it, the even element of a pair reads the pair's word
+// as it is and the odd element reads it rotated left by 19, so that at the full
+// fp16 width the even element's rounding is decided by the word's top 13 bits
+// and the odd element's by its low 13 bits.
 DEV u32 rng_chain(u32 h) { return h * 0x2C9277B5u + 0xAC564B05u; }
 DEV u32 rng_chain_word(u32 h) { return h ^ (h >> 16); }
 DEV u32 rng_bits_pair(const Rng& g, u64 idx) {
@@ -202,7 +203,7 @@ DEV u32 rng_bits_pair(const Rng& g, u64 idx) {
     const int s = (int)(idx >> 1) & 3;
     for (int j = 0; j < s; ++j) h = rng_chain(h);
     const u32 w = s ? rng_chain_word(h) : h;
-    return (idx & 1) ? __funnelshift_l(w, w, 16) : w;
+    return (idx & 1) ? __funnelshift_l(w, w, 19) : w;
 }
 DEV float frand(const Rng& g, u64 idx) { return __uint2float_rn(rng_bits(g, idx)) * 2.3283064365386963e-10f; }
 
@@ -297,7 +298,10 @@ template <int DT, int V, bool SR> DEV void cvt_out(const float* v, u32* w, const
 // PAIR: 16-bit float stores (eight elements per hash).  ALIGNED: idx0 % V == 0 and
 // step == 1, so a vector never straddles a group or a 2^32 boundary and the
 // 64-bit arithmetic is done once per vector instead of once per lane.
-template <int V, bool PAIR, bool ALIGNED> DEV void rng_lanes(const Rng& g, u64 idx0, i64 step, u32* ur) {
+// TOP13: the caller only looks at the top 13 bits of each word (an fp16 store at 10
+// mantissa bits), so the odd element's rotation can be a plain shift.
+template <int V, bool PAIR, bool ALIGNED, bool TOP13 = false>
+DEV void rng_lanes(const Rng& g, u64 idx0, i64 step, u32* ur) {
     if constexpr (ALIGNED && V > 1) {
         if constexpr (PAIR) {
             // V divides 8 and idx0 % V == 0: the vector lies inside one group of eight
@@ -309,7 +313,7 @@ template <int V, bool PAIR, bool ALIGNED> DEV void rng_lanes(const Rng& g, u64 i
             for (int j = 0; j < V / 2; ++j) {
                 const u32 w = (V == 8) ? (j ? rng_chain_word(h) : h) : ((s0 + j) ? rng_chain_word(h) : h);
                 ur[2 * j] = w;
-                ur[2 * j + 1] = __funnelshift_l(w, w, 16);
+                ur[2 * j + 1] = TOP13 ? (w << 19) : __funnelshift_l(w, w, 19);
                 h = rng_chain(h);
             }
         } else {

@@ -1301,7 +1301,12 @@ class Planner(object):
             aligned = "true" if (ra == 1 and (st.flat or ncols % V == 0)) else "false"
             if st.flat and self._lin is not None:
                 aligned = "true" if aligned_flat else "false"
-            st_lines.append("const SrCtx c = sr_ctx(p.sr_mb); const Rng g{p.rk0, p.rk1}; u32 ur[V];")
+            # the bit count is a literal (plans are cached per rounding setting), so shifts and
+            # masks fold; at the full mantissa width of a 16-bit float the mask is dropped, the
+            # truncating conversion that follows clears the same bits
+            full = (odt == DT_CODES["f2"] and int(rounding) == 10) or (odt == DT_CODES["bf2"] and int(rounding) == 7)
+            st_lines.append("SrCtx c = sr_ctx(%d);%s const Rng g{p.rk0, p.rk1}; u32 ur[V];"
+                            % (int(rounding), " c.mask = 0xffffffffu;" if full else ""))
             if st.flat and self._lin is None:
                 lin_expr = "(u64)n"                       # one row: the element index is n itself
             elif st.flat:
@@ -1310,7 +1315,8 @@ class Planner(object):
                 lin_expr = "(u64)(p.lin_0 + %s * p.lin_r + %s)" % (row, col)     # lin_c is 1
             else:
                 lin_expr = "(u64)(p.lin_0 + %s * p.lin_r + %s * p.lin_c)" % (row, col)
-            st_lines.append("rng_lanes<V, %s, %s>(g, %s, %s, ur);" % (pair, aligned, lin_expr, step))
+            top13 = "true" if (odt == DT_CODES["f2"] and int(rounding) == 10) else "false"
+            st_lines.append("rng_lanes<V, %s, %s, %s>(g, %s, %s, ur);" % (pair, aligned, top13, lin_expr, step))
             st_lines.append("st_f<%s, V, true>(p.o, %s, v, c, ur);" % (DT_NAMES[odt], o_off))
         else:
             st_lines.append("SrCtx c; c.shift = 0; c.mask = 0;")

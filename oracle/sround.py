@@ -80,7 +80,9 @@ def rng_bits_pair(key0, key1, idx):
     """Random word of element ``idx`` of a 16-bit float store: the eight elements of
     group idx >> 3 share one hash; pair s = (idx >> 1) & 3 of the group takes s steps
     of the chain h -> h * 0x2C9277B5 + 0xAC564B05 (and, past the first, h ^ (h >> 16));
-    the odd element of a pair reads the word with its 16-bit halves swapped."""
+    the even element of a pair reads the word as it is, the odd element reads it rotated
+    left by 19 bits (at the full fp16 width the word's top 13 bits decide the even element's
+    rounding and its low 13 bits the odd element's)."""
     idx = np.asarray(idx, dtype=np.uint64)
     h = rng_bits(key0, key1, idx >> np.uint64(3)).astype(np.uint64)
     s = ((idx >> np.uint64(1)) & np.uint64(3)).astype(np.int64)
@@ -89,8 +91,8 @@ def rng_bits_pair(key0, key1, idx):
         nxt = (h * np.uint64(0x2C9277B5) + np.uint64(0xAC564B05)) & m
         h = np.where(s >= step, nxt, h)
     w = np.where(s > 0, h ^ (h >> np.uint64(16)), h).astype(U32)
-    swapped = ((w << U32(16)) | (w >> U32(16))).astype(U32)
-    return np.where((idx & np.uint64(1)).astype(bool), swapped, w).astype(U32)
+    shifted = ((w << U32(19)) | (w >> U32(13))).astype(U32)
+    return np.where((idx & np.uint64(1)).astype(bool), shifted, w).astype(U32)
 
 
 def frand(bits):

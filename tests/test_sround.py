@@ -110,13 +110,13 @@ def test_generator_is_a_pure_function_of_seed_launch_and_index():
 
 def test_pair_words_of_sixteen_bit_stores():
     """Eight neighbours share one hash: element 0 of a group reads it unchanged, an odd element
-    reads its pair's word with the halves swapped, later pairs step a congruential chain."""
+    reads its pair's word rotated left by 19 bits, later pairs step a congruential chain."""
     k = sround.launch_key(7, 3)
     idx = np.arange(64, dtype=np.uint64)
     w = sround.rng_bits_pair(k[0], k[1], idx)
     h = sround.rng_bits(k[0], k[1], idx >> np.uint64(3))
     assert np.array_equal(w[0::8], h[0::8])
-    assert np.array_equal(w[1::2], ((w[0::2] << U32(16)) | (w[0::2] >> U32(16))))
+    assert np.array_equal(w[1::2], ((w[0::2] << U32(19)) | (w[0::2] >> U32(13))).astype(U32))
     h1 = (h[2::8].astype(np.uint64) * np.uint64(0x2C9277B5) + np.uint64(0xAC564B05)) & np.uint64(0xFFFFFFFF)
     assert np.array_equal(w[2::8], (h1 ^ (h1 >> np.uint64(16))).astype(U32))
     # the top 13 bits, which decide an fp16 store at 10 bits, are uniform per element
