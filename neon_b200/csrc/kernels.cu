@@ -28,7 +28,7 @@ template <int DT, int OP, bool ABS>
 struct FullRed {
     template <int V>
     struct S {
-        enum { NRED = 1 };
+        enum { NRED = 1, FUSED = (OP == b200::OP_SUM && !ABS && DT != b200::F32) ? 1 : 0 };
         static DEV constexpr int op(int) { return OP; }
         struct H { int unused_; };
         struct L { u32 a0[(b200::dt_size<DT>::value * V + 3) / 4]; };
@@ -39,6 +39,13 @@ struct FullRed {
             b200::cvt_in<DT, V>(l.a0, a0);
 #pragma unroll
             for (int i = 0; i < V; ++i) out[0][i] = ABS ? fabsf(a0[i]) : a0[i];
+        }
+        // plain sums of 16-bit floats: the add takes the stored value as it is
+        static DEV void accum(const RP&, const H&, const L& l, i64, i64, float (&acc)[1][V]) {
+            if constexpr (DT != b200::F32) {
+#pragma unroll
+                for (int i = 0; i < V; ++i) acc[0][i] = b200::mx_add<DT, V>(l.a0, i, acc[0][i]);
+            }
         }
         static DEV void epilogue(const RP& p, i64, const float* r, const int*) {
             *reinterpret_cast<float*>(p.o) = r[0];

@@ -151,6 +151,41 @@ template <int DT, int V, bool NC> DEV void ld_w(u64 base, i64 off, u32* w) {
 // int32 index load (take / one-hot addressing)
 DEV int ld_idx(u64 base, i64 off) { return __ldg(reinterpret_cast<const int*>(base) + off); }
 
+// ------------------------------------------------------------------ mixed-precision add / subtract
+// d = a + c and d = a - c with a a stored 16-bit float and c, d fp32: one instruction
+// (add.f32.f16 / sub.f32.f16, sm_100) instead of a conversion followed by an fp32 add.  The
+// 16-bit operand is converted exactly, so the result is bit for bit that of cvt + add.rn.f32.
+// `w` are the loaded words of a V-element vector, `i` the lane (a constant once unrolled).
+template <int DT, int HI, bool SUB> DEV float mx_half(u32 w, float c) {
+    float d;
+    if constexpr (DT == F16) {
+        if constexpr (SUB) {
+            if constexpr (HI) asm("{.reg .b16 lo, hi; mov.b32 {lo, hi}, %1; sub.rn.f32.f16 %0, hi, %2;}" : "=f"(d) : "r"(w), "f"(c));
+            else asm("{.reg .b16 lo, hi; mov.b32 {lo, hi}, %1; sub.rn.f32.f16 %0, lo, %2;}" : "=f"(d) : "r"(w), "f"(c));
+        } else {
+            if constexpr (HI) asm("{.reg .b16 lo, hi; mov.b32 {lo, hi}, %1; add.rn.f32.f16 %0, hi, %2;}" : "=f"(d) : "r"(w), "f"(c));
+            else asm("{.reg .b16 lo, hi; mov.b32 {lo, hi}, %1; add.rn.f32.f16 %0, lo, %2;}" : "=f"(d) : "r"(w), "f"(c));
+        }
+    } else {
+        if constexpr (SUB) {
+            if constexpr (HI) asm("{.reg .b16 lo, hi; mov.b32 {lo, hi}, %1; sub.rn.f32.bf16 %0, hi, %2;}" : "=f"(d) : "r"(w), "f"(c));
+            else asm("{.reg .b16 lo, hi; mov.b32 {lo, hi}, %1; sub.rn.f32.bf16 %0, lo, %2;}" : "=f"(d) : "r"(w), "f"(c));
+        } else {
+            if constexpr (HI) asm("{.reg .b16 lo, hi; mov.b32 {lo, hi}, %1; add.rn.f32.bf16 %0, hi, %2;}" : "=f"(d) : "r"(w), "f"(c));
+            else asm("{.reg .b16 lo, hi; mov.b32 {lo, hi}, %1; add.rn.f32.bf16 %0, lo, %2;}" : "=f"(d) : "r"(w), "f"(c));
+        }
+    }
+    return d;
+}
+template <int DT, int V> DEV float mx_add(const u32* w, int i, float c) {
+    if constexpr (V == 1) return mx_half<DT, 0, false>(w[0], c);
+    else return (i & 1) ? mx_half<DT, 1, false>(w[i >> 1], c) : mx_half<DT, 0, false>(w[i >> 1], c);
+}
+template <int DT, int V> DEV float mx_sub(const u32* w, int i, float c) {
+    if constexpr (V == 1) return mx_half<DT, 0, true>(w[0], c);
+    else return (i & 1) ? mx_half<DT, 1, true>(w[i >> 1], c) : mx_half<DT, 0, true>(w[i >> 1], c);
+}
+
 // ------------------------------------------------------------------ fast math
 // Used by generated code unless the backend asks for IEEE / libm versions.
 // Each stays within a few fp32 ulp (far inside the 1e-5 parity bound) and
@@ -379,6 +414,25 @@ DEV void red_merge(int op, float& a, int& ai, float b, int bi) {
 //         division per thread) for statements that need element coordinates.
 // IDX32: the host guarantees that element counts and byte offsets fit 32 bits, so vector
 //        indices are computed in 32-bit arithmetic (widening multiply-adds for addresses).
+// One evaluated vector into the per-lane accumulators.  Generated code sets S::FUSED and
+// provides S::accum when every reduction of the pass is a sum and the accumulation can absorb
+// an operand's conversion (mx_add); otherwise eval + the generic reduction step.  Lane i has
+// element index idx0 + i * idx_step (arg reductions).
+template <class S, class P, int NR, int V>
+DEV void accumulate(const P& p, const typename S::H& h, const typename S::L& l, i64 k, i64 n,
+                    int idx0, int idx_step, float (&acc)[NR][V], int (&acci)[NR][V]) {
+    if constexpr (S::FUSED) {
+        S::accum(p, h, l, k, n, acc);
+    } else {
+        float out[NR][V];
+        S::eval(p, h, l, k, n, out);
+#pragma unroll
+        for (int r = 0; r < NR; ++r)
+#pragma unroll
+            for (int i = 0; i < V; ++i) red_acc(S::op(r), acc[r][i], acci[r][i], out[r][i], idx0 + i * idx_step);
+    }
+}
+
 template <template <int> class SV, class P, int V, int BLOCK, int UNROLL, int MODE, bool IDX32 = false>
 DEV void ew_kernel(const P& p) {
     typedef SV<V> S;
@@ -480,12 +534,7 @@ DEV void red_rows_kernel(const P& p) {
             for (int u = 0; u < UNROLL; ++u) {
                 if (v + (i64)u * TPR < v1) {
                     const i64 n = (v + (i64)u * TPR) * V;
-                    float out[NR][V];
-                    S::eval(p, h, l[u], k, n, out);
-#pragma unroll
-                    for (int r = 0; r < NR; ++r)
-#pragma unroll
-                        for (int i = 0; i < V; ++i) red_acc(S::op(r), acc[r][i], acci[r][i], out[r][i], (int)(n + i));
+                    accumulate<S, P, NR, V>(p, h, l[u], k, n, (int)n, 1, acc, acci);
                 }
             }
         }
@@ -624,12 +673,7 @@ DEV void red_cols_kernel(const P& p) {
 #pragma unroll
             for (int u = 0; u < UNROLL; ++u) {
                 if (n + (i64)u * RH < n1) {
-                    float out[NR][V];
-                    S::eval(p, h, l[u], k0, n + (i64)u * RH, out);
-#pragma unroll
-                    for (int r = 0; r < NR; ++r)
-#pragma unroll
-                        for (int i = 0; i < V; ++i) red_acc(S::op(r), acc[r][i], acci[r][i], out[r][i], (int)(n + (i64)u * RH));
+                    accumulate<S, P, NR, V>(p, h, l[u], k0, n + (i64)u * RH, (int)(n + (i64)u * RH), 0, acc, acci);
                 }
             }
         }
@@ -747,6 +791,14 @@ DEV u32 cluster_count() { u32 r; asm volatile("mov.u32 %0, %%nclusterid.x;" : "=
 DEV void cluster_barrier() {
     asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
+// The same barrier when only warp 0 has written something its cluster peers will read (the
+// block's exchange slot): warp 0 arrives with release semantics, the other warps relaxed, so
+// they do not have to wait until their own earlier global stores have drained.
+DEV void cluster_barrier_warp0_releases() {
+    if ((threadIdx.x >> 5) == 0) asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+    else asm volatile("barrier.cluster.arrive.relaxed.aligned;" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
 DEV u32 dsmem_ld(const void* local, u32 rank) {
     u32 addr, v;
     asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(addr) : "r"(smem_u32(local)), "r"(rank));
@@ -759,6 +811,9 @@ DEV void mbar_init(u64* bar, u32 count) {
 }
 DEV void mbar_expect_tx(u64* bar, u32 bytes) {
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+DEV void mbar_arrive(u64* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
 DEV bool mbar_try_wait(u64* bar, u32 parity) {
     u32 ok;
@@ -794,8 +849,12 @@ template <int C, int THREADS, int UNROLL> DEV void rr_begin(RowCtx& cx, i64 nvec
     cx.nc = (cx.v1 - cx.v0 + cx.cv - 1) / cx.cv;
     cx.phase = 0; cx.row_parity = 0; cx.failed = false;
     if (threadIdx.x == 0) {
-        for (u32 c = 0; c < cx.nc; ++c)
+        for (u32 c = 0; c < cx.nc; ++c) {
+            // bars[c]: chunk c has landed (one arrival + its bytes); bars[RR_MAX_CHUNKS + c]:
+            // every warp is done reading chunk c in the row's last pass
             asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bars + c)), "r"(1) : "memory");
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bars + RR_MAX_CHUNKS + c)), "r"(THREADS / 32) : "memory");
+        }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     __syncthreads();
@@ -838,7 +897,7 @@ DEV void rr_row_end(RowCtx& cx) {
 
 // One pass over this block's slice, chunk by chunk (operands already point at shared memory).
 //   WAIT     first pass of a row: wait for each chunk's copies before touching it
-//   RELEASE  last pass of a row: once all threads are done with a chunk, start the copies of
+//   RELEASE  last pass of a row: once all warps are done with a chunk, start the copies of
 //            the same chunk of the next row (knext), so loads overlap the rest of this pass
 //   NR == 0  element-wise pass (stores through S::store), else reductions into a / ai
 template <template <int> class SV, class ST, class P, int V, int THREADS, int UNROLL, bool WAIT, bool RELEASE>
@@ -866,21 +925,25 @@ DEV void rr_pass(const P& q, const P& p, i64 k, i64 knext, RowCtx& cx, unsigned 
         for (int u = 0; u < UNROLL; ++u) {
             if (vb + tid + u * THREADS < cx.v1) {
                 const i64 n = (i64)((vb + tid + u * THREADS) * (u32)V);
-                float out[NA][V];
-                S::eval(q, h, l[u], k, n, out);
                 if constexpr (NR == 0) {
+                    float out[1][V];
+                    S::eval(q, h, l[u], k, n, out);
                     S::store(q, k, n, out[0]);
                 } else {
-#pragma unroll
-                    for (int r = 0; r < NR; ++r)
-#pragma unroll
-                        for (int i = 0; i < V; ++i) red_acc(S::op(r), acc[r][i], acci[r][i], out[r][i], (int)(n + i));
+                    accumulate<S, P, NA, V>(q, h, l[u], k, n, (int)n, 1, acc, acci);
                 }
             }
         }
         if constexpr (RELEASE) {
-            __syncthreads();                      // every thread has read its part of chunk c
-            if (tid == 0 && knext < p.K && !cx.failed) ST::issue(p, cx, knext, c, dyn, bars);
+            // each warp reports that it is done with chunk c; thread 0 alone waits for all of
+            // them (bounded) and then starts the next row's copies into the chunk, so the
+            // other warps run on into the next chunk without a block-wide barrier
+            __syncwarp();
+            if ((tid & 31) == 0) mbar_arrive(bars + RR_MAX_CHUNKS + c);
+            if (tid == 0 && knext < p.K) {
+                rr_wait_chunk(cx, bars + RR_MAX_CHUNKS + c, p.status, p.wait_ns);
+                if (!cx.failed) ST::issue(p, cx, knext, c, dyn, bars);
+            }
         }
     }
     if constexpr (NR > 0) {
@@ -923,7 +986,7 @@ DEV void rr_combine(const RowCtx& cx, float* a, int* ai, u32* slots /* [2 pariti
 #pragma unroll
             for (int r = 0; r < NR; ++r) { mine[2 * r] = __float_as_uint(a[r]); mine[2 * r + 1] = (u32)ai[r]; }
         }
-        cluster_barrier();
+        cluster_barrier_warp0_releases();
 #pragma unroll
         for (int r = 0; r < NR; ++r) {
             a[r] = __uint_as_float(dsmem_ld(mine + 2 * r, 0)); ai[r] = (int)dsmem_ld(mine + 2 * r + 1, 0);

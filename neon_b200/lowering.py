@@ -686,7 +686,8 @@ class Planner(object):
             ops = " : ".join("r == %d ? %s" % (j, RED_CODE[r.op]) for j, r in enumerate(rs[:-1]))
             ops = (ops + " : " if ops else "") + RED_CODE[rs[-1].op]
             tail = ["out[%d][i] = %s;" % (j, e) for j, e in enumerate(outs)]
-            parts.append(self._struct("S%d" % i, em, tail, len(rs), ops, None, None))
+            parts.append(self._struct("S%d" % i, em, tail, len(rs), ops, None, None,
+                                      acc_tail=self._accum_tail(em, rs, outs)))
         if red_out:
             parts.append(self._struct("SF", fin, [], 0, "OP_SUM", fin.h_lines + [store], None, epilogue_only=True))
         else:
@@ -710,7 +711,7 @@ class Planner(object):
 
         body = []
         body.append("extern __shared__ __align__(128) unsigned char dyn[];")
-        body.append("__shared__ u64 bars[RR_MAX_CHUNKS];")
+        body.append("__shared__ u64 bars[2 * RR_MAX_CHUNKS];")
         body.append("__shared__ float sv[%d][%d]; __shared__ int si[%d][%d];" % (nrmax, threads // 32, nrmax, threads // 32))
         body.append("__shared__ u32 slots[%d][2][%d][2]; __shared__ u32 s_res[%d];" % (len(ems), nrmax, nres))
         body.append("RowCtx cx; rr_begin<%d, %d, %d>(cx, p.nvec, bars);" % (C, threads, unroll))
@@ -770,7 +771,37 @@ class Planner(object):
         return pz
 
     @staticmethod
-    def _struct(name, em, eval_tail, nred, ops, ep_lines, st_lines, epilogue_only=False):
+    def _accum_tail(em, rs, outs):
+        """Lines of S::accum for a pass whose reductions are all sums and where at least one
+        sums a stored 16-bit float tensor as it is (the add then takes the stored value);
+        None when the generic eval + reduction step should be used."""
+        if any(r.op != "sum" for r in rs):
+            return None
+        lines, fused = [], False
+        for j, (r, e) in enumerate(zip(rs, outs)):
+            half = em.half_leaf(r.args[0])
+            if half is not None:
+                fused = True
+                lines.append("acc[%d][i] = mx_add<%s, V>(%s, i, acc[%d][i]);" % (j, DT_NAMES[half[1]], half[0], j))
+            else:
+                lines.append("acc[%d][i] += %s;" % (j, e))
+        return lines if fused else None
+
+    @staticmethod
+    def _accum_fn(em, acc_tail, nred, ind):
+        if acc_tail is None:
+            return ["    enum { FUSED = 0 };"]
+        body = list(em.e_pre)
+        body.append("_Pragma(\"unroll\") for (int i = 0; i < V; ++i) {")
+        body.extend("    " + x for x in em.e_lines)
+        body.extend("    " + x for x in acc_tail)
+        body.append("}")
+        return ["    enum { FUSED = 1 };",
+                "    static DEV void accum(const P& p, const H& h, const L& l, i64 k, i64 n, float (&acc)[%d][V]) {" % nred
+                + ind + ind.join(body) + "\n    }"]
+
+    @staticmethod
+    def _struct(name, em, eval_tail, nred, ops, ep_lines, st_lines, epilogue_only=False, acc_tail=None):
         ind = "\n        "
         nout = max(nred, 1)
         parts = ["template <int V> struct %s {" % name]
@@ -788,6 +819,9 @@ class Planner(object):
             body.append("}")
             parts.append("    static DEV void eval(const P& p, const H& h, const L& l, i64 k, i64 n, float (&out)[%d][V]) {" % nout
                          + ind + ind.join(body) + "\n    }")
+            parts.extend(Planner._accum_fn(em, acc_tail, nout, ind))
+        else:
+            parts.append("    enum { FUSED = 0 };")
         if st_lines is not None:
             parts.append("    static DEV void store(const P& p, i64 k, i64 n, const float* v) {" + ind + ind.join(st_lines) + "\n    }")
         if ep_lines is not None:
@@ -1058,6 +1092,17 @@ class Planner(object):
                         self.h_lines.append("{ const int i = 0; (void)i; h.%s = 1.0f / %s; }" % (hname, ref))
                 rcp = ("h.%s[i]" % hname) if self.lk else ("h.%s" % hname)
                 expr = "(%s * %s)" % (self.elem(n.args[0]), rcp)
+            elif n.kind == "b" and n.op in ("add", "sub") and self.mixed_operand(n) is not None:
+                # one operand is a stored 16-bit float: the add converts it on the fly
+                j = self.mixed_operand(n)
+                raw, dt = self.half_leaf(n.args[j])
+                other = self.elem(n.args[1 - j])
+                if n.op == "add":
+                    expr = "mx_add<%s, V>(%s, i, %s)" % (DT_NAMES[dt], raw, other)
+                elif j == 0:
+                    expr = "mx_sub<%s, V>(%s, i, %s)" % (DT_NAMES[dt], raw, other)
+                else:                                   # c - a = -(a - c), exactly
+                    expr = "(-mx_sub<%s, V>(%s, i, %s))" % (DT_NAMES[dt], raw, other)
             else:
                 args = [self.elem(a) for a in n.args]
                 expr = (self.unary[n.op] if n.kind == "u" else self.binary[n.op]).format(*args)
@@ -1065,6 +1110,28 @@ class Planner(object):
             self.e_lines.append("const float %s = %s;" % (name, expr))
             self.names[key] = name
             return name
+
+        def half_leaf(self, n):
+            """(words of the loaded vector, dtype code) when n is a 16-bit float tensor read one
+            element per lane, else None."""
+            if n.kind != "t" or not self.var_n(n) or (self.lk and not self.var_k(n)):
+                return None
+            o, pre = self._leaf(n)
+            if o.dt not in (DT_CODES["f2"], DT_CODES["bf2"]):
+                return None
+            self.elem(n)                                # declares the load
+            return "l.a_" + pre, o.dt
+
+        def mixed_operand(self, n):
+            """Index of the operand of add/sub node n that a mixed-precision instruction can take
+            in its stored form, or None."""
+            for j in (0, 1):
+                if self.half_leaf(n.args[j]) is not None and n.args[1 - j].kind != "c":
+                    return j
+            for j in (0, 1):
+                if self.half_leaf(n.args[j]) is not None:
+                    return j
+            return None
 
         def coords(self):
             """(row, col) expressions of lane i in eval scope."""
@@ -1154,6 +1221,7 @@ class Planner(object):
         for r in reds:
             outs.append(em.elem(r.args[0]))
         eval_tail = ["out[%d][i] = %s;" % (i, e) for i, e in enumerate(outs)]
+        acc_tail = self._accum_tail(em, reds, outs)
 
         # epilogue: raw results to scratch, or the root expression into the output
         ep = self._Emit(st, f, ka, ra, False, res_buf, reds[0].level - 1, (self.unary, self.binary))
@@ -1243,7 +1311,7 @@ class Planner(object):
             f.u64("counters", 0)
         ops = " : ".join("r == %d ? %s" % (i, RED_CODE[r.op]) for i, r in enumerate(reds[:-1]))
         ops = (ops + " : " if ops else "") + RED_CODE[reds[-1].op]
-        src, pz.name = self._source(f, em, eval_tail, nr, ops, ep_lines, None, call)
+        src, pz.name = self._source(f, em, eval_tail, nr, ops, ep_lines, None, call, acc_tail=acc_tail)
         pz.source, pz.fields, pz.grid, pz.block = src, f, grid, (BLOCK, 1, 1)
         pz.uses_rng = em.uses_rng
         pz.desc = "%s V=%d K=%d N=%d split=%d grid=%s" % (pz.kind, V, K, N, split, grid)
@@ -1366,7 +1434,7 @@ class Planner(object):
         return pz
 
     @staticmethod
-    def _source(f, em, eval_tail, nred, ops, ep_lines, st_lines, call, min_blocks=1):
+    def _source(f, em, eval_tail, nred, ops, ep_lines, st_lines, call, min_blocks=1, acc_tail=None):
         ind = "\n        "
         nout = max(nred, 1)
         parts = ['#include "optree_templates.cuh"', "using namespace b200;", f.decl(), "template <int V> struct S {"]
@@ -1383,6 +1451,7 @@ class Planner(object):
         body.append("}")
         parts.append("    static DEV void eval(const P& p, const H& h, const L& l, i64 k, i64 n, float (&out)[%d][V]) {" % nout
                      + ind + ind.join(body) + "\n    }")
+        parts.extend(Planner._accum_fn(em, acc_tail, nout, ind))
         if st_lines is not None:
             parts.append("    static DEV void store(const P& p, i64 k, i64 n, const float* v) {" + ind + ind.join(st_lines) + "\n    }")
         if ep_lines is not None:
