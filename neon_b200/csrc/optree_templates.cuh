@@ -914,23 +914,40 @@ DEV void rr_pass(const P& q, const P& p, i64 k, i64 knext, RowCtx& cx, unsigned 
         for (int i = 0; i < V; ++i) { acc[r][i] = red_init(S::op(r)); acci[r][i] = -1; }
     typename S::H h;
     S::load_h(q, k, h);
+    const u32 nfull = (cx.v1 - cx.v0) / cx.cv;       // chunks in which every thread has all its vectors
     for (u32 c = 0; c < cx.nc; ++c) {
         if constexpr (WAIT) rr_wait_chunk(cx, bars + c, p.status, p.wait_ns);
-        const u32 vb = cx.v0 + c * cx.cv;
+        const u32 vb = cx.v0 + c * cx.cv + tid;
         typename S::L l[UNROLL];
+        if (c < nfull) {                             // no bounds checks
 #pragma unroll
-        for (int u = 0; u < UNROLL; ++u)
-            if (vb + tid + u * THREADS < cx.v1) S::load_l(q, k, (i64)((vb + tid + u * THREADS) * (u32)V), l[u]);
+            for (int u = 0; u < UNROLL; ++u) S::load_l(q, k, (i64)((vb + u * THREADS) * (u32)V), l[u]);
 #pragma unroll
-        for (int u = 0; u < UNROLL; ++u) {
-            if (vb + tid + u * THREADS < cx.v1) {
-                const i64 n = (i64)((vb + tid + u * THREADS) * (u32)V);
+            for (int u = 0; u < UNROLL; ++u) {
+                const i64 n = (i64)((vb + u * THREADS) * (u32)V);
                 if constexpr (NR == 0) {
                     float out[1][V];
                     S::eval(q, h, l[u], k, n, out);
                     S::store(q, k, n, out[0]);
                 } else {
                     accumulate<S, P, NA, V>(q, h, l[u], k, n, (int)n, 1, acc, acci);
+                }
+            }
+        } else {
+#pragma unroll
+            for (int u = 0; u < UNROLL; ++u)
+                if (vb + u * THREADS < cx.v1) S::load_l(q, k, (i64)((vb + u * THREADS) * (u32)V), l[u]);
+#pragma unroll
+            for (int u = 0; u < UNROLL; ++u) {
+                if (vb + u * THREADS < cx.v1) {
+                    const i64 n = (i64)((vb + u * THREADS) * (u32)V);
+                    if constexpr (NR == 0) {
+                        float out[1][V];
+                        S::eval(q, h, l[u], k, n, out);
+                        S::store(q, k, n, out[0]);
+                    } else {
+                        accumulate<S, P, NA, V>(q, h, l[u], k, n, (int)n, 1, acc, acci);
+                    }
                 }
             }
         }
@@ -947,6 +964,8 @@ DEV void rr_pass(const P& q, const P& p, i64 k, i64 knext, RowCtx& cx, unsigned 
         }
     }
     if constexpr (NR > 0) {
+        // lanes of a thread, then the threads of a warp; lane 0 leaves the warp's result in sv/si
+        const int warp = tid >> 5, lane = tid & 31;
 #pragma unroll
         for (int r = 0; r < NR; ++r) {
             a[r] = acc[r][0]; ai[r] = acci[r][0];
@@ -955,43 +974,56 @@ DEV void rr_pass(const P& q, const P& p, i64 k, i64 knext, RowCtx& cx, unsigned 
 #pragma unroll
             for (int o = 16; o > 0; o >>= 1) {
                 float b = __shfl_xor_sync(0xffffffffu, a[r], o);
-                int bi = __shfl_xor_sync(0xffffffffu, ai[r], o);
+                int bi = red_is_arg(S::op(r)) ? __shfl_xor_sync(0xffffffffu, ai[r], o) : 0;
                 red_merge(S::op(r), a[r], ai[r], b, bi);
             }
-        }
-        const int warp = tid >> 5, lane = tid & 31;
-        __syncthreads();                          // sv/si may still be read from the previous pass
-        if (lane == 0) {
-#pragma unroll
-            for (int r = 0; r < NR; ++r) { sv[r][warp] = a[r]; si[r][warp] = ai[r]; }
-        }
-        __syncthreads();
-#pragma unroll
-        for (int r = 0; r < NR; ++r) {            // every thread folds the warp results, in warp order
-            a[r] = sv[r][0]; ai[r] = si[r][0];
-            for (int w = 1; w < THREADS / 32; ++w) red_merge(S::op(r), a[r], ai[r], sv[r][w], si[r][w]);
+            if (lane == 0) { sv[r][warp] = a[r]; if (red_is_arg(S::op(r))) si[r][warp] = ai[r]; }
         }
     }
 }
 
-// exchange the block results of one pass inside the cluster and leave the row's
-// result in res[0..NR): value bits, or the index for arg reductions
-template <template <int> class SV, int V, int C>
-DEV void rr_combine(const RowCtx& cx, float* a, int* ai, u32* slots /* [2 parities][NR][2] of this pass */, u32* res) {
+// Block results of one pass -> row result, left in res[0..NR) (value bits, or the index for arg
+// reductions) for every thread to read, and in a / ai of warp 0.  Warp 0 does the combining,
+// lane w standing for warp w and then for block w of the cluster, with xor butterflies (a fixed
+// order, so results repeat exactly); the other warps only take part in the barriers.
+template <template <int> class SV, int V, int C, int THREADS>
+DEV void rr_combine(const RowCtx& cx, float* a, int* ai, float (*sv)[THREADS / 32], int (*si)[THREADS / 32],
+                    u32* slots /* [2 parities][NR][2] of this pass */, u32* res) {
     typedef SV<V> S;
     constexpr int NR = S::NRED;
-    if constexpr (C > 1) {
-        u32* mine = slots + cx.row_parity * NR * 2;
-        if (threadIdx.x == 0) {
-#pragma unroll
-            for (int r = 0; r < NR; ++r) { mine[2 * r] = __float_as_uint(a[r]); mine[2 * r + 1] = (u32)ai[r]; }
-        }
-        cluster_barrier_warp0_releases();
+    constexpr int NW = THREADS / 32;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    u32* mine = slots + cx.row_parity * NR * 2;
+    __syncthreads();                                  // the warps' results are in sv / si
+    if (warp == 0) {
 #pragma unroll
         for (int r = 0; r < NR; ++r) {
-            a[r] = __uint_as_float(dsmem_ld(mine + 2 * r, 0)); ai[r] = (int)dsmem_ld(mine + 2 * r + 1, 0);
-            for (u32 c = 1; c < (u32)C; ++c)
-                red_merge(S::op(r), a[r], ai[r], __uint_as_float(dsmem_ld(mine + 2 * r, c)), (int)dsmem_ld(mine + 2 * r + 1, c));
+            a[r] = lane < NW ? sv[r][lane] : 0.f;
+            ai[r] = (red_is_arg(S::op(r)) && lane < NW) ? si[r][lane] : -1;
+#pragma unroll
+            for (int o = NW / 2; o > 0; o >>= 1) {
+                float b = __shfl_xor_sync(0xffffffffu, a[r], o);
+                int bi = red_is_arg(S::op(r)) ? __shfl_xor_sync(0xffffffffu, ai[r], o) : 0;
+                red_merge(S::op(r), a[r], ai[r], b, bi);
+            }
+            if (C > 1 && lane == 0) { mine[2 * r] = __float_as_uint(a[r]); mine[2 * r + 1] = (u32)ai[r]; }
+        }
+    }
+    if constexpr (C > 1) {
+        cluster_barrier_warp0_releases();
+        if (warp == 0) {
+#pragma unroll
+            for (int r = 0; r < NR; ++r) {
+                const u32 peer = lane < C ? (u32)lane : 0u;
+                a[r] = __uint_as_float(dsmem_ld(mine + 2 * r, peer));
+                ai[r] = red_is_arg(S::op(r)) ? (int)dsmem_ld(mine + 2 * r + 1, peer) : -1;
+#pragma unroll
+                for (int o = C / 2; o > 0; o >>= 1) {
+                    float b = __shfl_xor_sync(0xffffffffu, a[r], o);
+                    int bi = red_is_arg(S::op(r)) ? __shfl_xor_sync(0xffffffffu, ai[r], o) : 0;
+                    red_merge(S::op(r), a[r], ai[r], b, bi);
+                }
+            }
         }
     }
     if (threadIdx.x == 0) {

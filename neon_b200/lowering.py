@@ -729,17 +729,19 @@ class Planner(object):
         body.append("    const i64 knext = k + kstep;")
         body.append("    float a[%d]; int ai[%d];" % (nrmax, nrmax))
         n_launch = len(ems) + (0 if red_out else 1)
+        dyn_cur, bars_cur = "dyn", "bars"
         for i, (em, rs, outs) in enumerate(ems):
             last = red_out and i == len(ems) - 1
-            body.append("    rr_pass<S%d, ST, P, %d, %d, %d, %s, %s>(q, p, k, knext, cx, dyn, bars, a, ai, sv, si);"
-                        % (i, V, threads, unroll, "true" if i == 0 else "false", "true" if last else "false"))
-            body.append("    rr_combine<S%d, %d, %d>(cx, a, ai, &slots[%d][0][0][0], &s_res[%d]);"
-                        % (i, V, C, i, slot_of[rs[0].nid]))
+            body.append("    rr_pass<S%d, ST, P, %d, %d, %d, %s, %s>(q, p, k, knext, cx, %s, %s, a, ai, sv, si);"
+                        % (i, V, threads, unroll, "true" if i == 0 else "false", "true" if last else "false",
+                           dyn_cur, bars_cur))
+            body.append("    rr_combine<S%d, %d, %d, %d>(cx, a, ai, sv, si, &slots[%d][0][0][0], &s_res[%d]);"
+                        % (i, V, C, threads, i, slot_of[rs[0].nid]))
         if red_out:
             body.append("    if (threadIdx.x == 0 && cx.rank == 0) SF<%d>::epilogue(q, k, a, ai);" % V)
         else:
-            body.append("    rr_pass<SE, ST, P, %d, %d, %d, false, true>(q, p, k, knext, cx, dyn, bars, a, ai, sv, si);"
-                        % (V, threads, unroll))
+            body.append("    rr_pass<SE, ST, P, %d, %d, %d, false, true>(q, p, k, knext, cx, %s, %s, a, ai, sv, si);"
+                        % (V, threads, unroll, dyn_cur, bars_cur))
         body.append("    rr_row_end(cx);")
         body.append("}")
         if C > 1:
