@@ -258,6 +258,26 @@ def other_workloads(name, be, world, rank):
             y[:] = (x - be.mean(x, axis=1)) / be.sqrt(be.var(x, axis=1) + 1e-5) * gamma + beta
         n = r * c
         return [("batchnorm stats+normalise", st_bn, 4 * n + 2048)], n
+    if name == "transpose":
+        # the data-feed step in front of every fprop (ArrayIterator): (examples, features) rows
+        # to (features, batch) columns; one large matrix each of fp32, fp16 and uint8
+        stmts = []
+        r, c = 8192, 8192
+        for dt in (np.float32, np.float16, np.uint8):
+            a = be.zeros((r, c), dtype=dt)
+            out = be.empty((c, r), dtype=dt)
+            stmts.append(("copy_transpose %s" % np.dtype(dt).name,
+                          (lambda a=a, out=out: be.copy_transpose(a, out)), 2 * a.nbytes))
+        return stmts, r * c
+    if name == "kahan":
+        n = 100000000
+        stmts = []
+        for dt in (np.float32, np.float16):
+            s_, c_, a_ = (be.zeros((n, 1), dtype=dt) for _ in range(3))
+            s_.rounding = True
+            stmts.append(("compensated_sum %s, stochastic rounding" % np.dtype(dt).name,
+                          (lambda s_=s_, c_=c_, a_=a_: be.compensated_sum(s_, c_, a_)), 5 * s_.nbytes))
+        return stmts, n
     raise SystemExit("unknown workload %s" % name)
 
 
@@ -337,7 +357,7 @@ def main():
     ap.add_argument("--cols", type=int, default=COLS)
     ap.add_argument("--e2e-steps", type=int, default=3)
     ap.add_argument("--no-cpu", action="store_true")
-    ap.add_argument("--workload", default="cfg5", help="cfg5 (default, the reported metric) or cfg1..cfg4")
+    ap.add_argument("--workload", default="cfg5", help="cfg5 (default, the reported metric), cfg1..cfg4, transpose (data-feed copy_transpose) or kahan (compensated_sum)")
     args = ap.parse_args()
 
     rank = int(os.environ.get("RANK", "0"))

@@ -57,13 +57,15 @@ template <> struct elem_t<4> { typedef unsigned int type; };
 template <> struct elem_t<8> { typedef unsigned long long type; };
 template <> struct elem_t<16> { typedef uint4 type; };
 
-// offsets of the block's slice in the dimensions from `first` on
-__device__ __forceinline__ void rest_offsets(const ShP& p, int first, i64 r, i64& so, i64& dof) {
+// offsets of the block's slice in the dimensions from `first` on (the grid has fewer than 2^31
+// blocks, so block coordinates are 32-bit quantities)
+__device__ __forceinline__ void rest_offsets(const ShP& p, int first, u32 r, i64& so, i64& dof) {
     for (int d = p.nd - 1; d >= first; --d) {
-        const i64 q = r / p.n[d];
-        const i64 c = r - q * p.n[d];
-        so += c * p.ss[d];
-        dof += c * p.ds[d];
+        const u32 nd = (u32)p.n[d];
+        const u32 q = r / nd;
+        const u32 c = r - q * nd;
+        so += (i64)c * p.ss[d];
+        dof += (i64)c * p.ds[d];
         r = q;
     }
 }
@@ -114,9 +116,10 @@ __global__ void __launch_bounds__(256) shuffle_tile_kernel(const __grid_constant
     __shared__ __align__(16) u32 tile[T][16 * UW];
 
     const int l = threadIdx.x & 15, r = threadIdx.x >> 4;
-    i64 b = blockIdx.x;
-    const i64 t0 = b % p.tiles0; b /= p.tiles0;
-    const i64 t1 = b % p.tiles1; b /= p.tiles1;
+    u32 b = blockIdx.x;
+    const u32 nt0 = (u32)p.tiles0, nt1 = (u32)p.tiles1;
+    const i64 t0 = b % nt0; b /= nt0;
+    const i64 t1 = b % nt1; b /= nt1;
     i64 so = 0, dof = 0;
     rest_offsets(p, 2, b, so, dof);
     const i64 ni = p.n[0], no = p.n[1];
@@ -145,10 +148,26 @@ __global__ void __launch_bounds__(256) shuffle_tile_kernel(const __grid_constant
 #pragma unroll
         for (int w = 0; w < N; ++w) {
             u32 out[UW];
+            if constexpr (ES == 2) {
+                // element w of rows 2q and 2q+1 -> word q: one byte permute
 #pragma unroll
-            for (int q = 0; q < UW; ++q) out[q] = 0;
+                for (int q = 0; q < UW; ++q)
+                    out[q] = __byte_perm(in[2 * q][w >> 1], in[2 * q + 1][w >> 1], (w & 1) ? 0x7632 : 0x5410);
+            } else if constexpr (ES == 1) {
+                // byte w of rows 4q .. 4q+3 -> word q: two permutes pick the byte from row pairs, one joins them
+                const u32 sel = ((4u + (w & 3)) << 4) | (u32)(w & 3);
 #pragma unroll
-            for (int v = 0; v < N; ++v) vor<ES>(out, v, vget<ES>(in[v], w));
+                for (int q = 0; q < UW; ++q) {
+                    const u32 lo = __byte_perm(in[4 * q][w >> 2], in[4 * q + 1][w >> 2], sel);
+                    const u32 hi = __byte_perm(in[4 * q + 2][w >> 2], in[4 * q + 3][w >> 2], sel);
+                    out[q] = __byte_perm(lo, hi, 0x5410);
+                }
+            } else {
+#pragma unroll
+                for (int q = 0; q < UW; ++q) out[q] = 0;
+#pragma unroll
+                for (int v = 0; v < N; ++v) vor<ES>(out, v, vget<ES>(in[v], w));
+            }
             vst<U>(&tile[N * l + w][((r + l) & 15) * UW], out);
         }
     }
@@ -183,9 +202,10 @@ __global__ void __launch_bounds__(256) shuffle_copy_kernel(const __grid_constant
     const int bx_log2 = p.src_vec;                     // (field reused by this kernel)
     const int bx = 1 << bx_log2;
     const int tx = threadIdx.x & (bx - 1), ty = threadIdx.x >> bx_log2;
-    i64 b = blockIdx.x;
-    const i64 t0 = b % p.tiles0; b /= p.tiles0;
-    const i64 t1 = b % p.tiles1; b /= p.tiles1;
+    u32 b = blockIdx.x;
+    const u32 nt0 = (u32)p.tiles0, nt1 = (u32)p.tiles1;
+    const i64 t0 = b % nt0; b /= nt0;
+    const i64 t1 = b % nt1; b /= nt1;
     i64 so = 0, dof = 0;
     rest_offsets(p, 2, b, so, dof);
     const i64 j = t1 * (256 >> bx_log2) + ty;
@@ -313,12 +333,15 @@ extern "C" b200_status b200_dimshuffle(uint64_t dst, uint64_t src, int32_t elem_
     i64 blocks;
     int U = 0;                                   // bytes a lane of the tile kernel moves at once
     if (tiled) {
-        // the widest vector whose tiles (T = 16 U / es elements a side) waste the least area
-        i64 best = 0;
+        // vector width: tiles are T = 16 U / es elements a side, so short dimensions waste part of
+        // a wide tile, while narrow vectors move fewer bytes per instruction (measured: about 0.7 of
+        // the 16-byte rate at 8 bytes, 0.4 at 4).  Take the smallest padded area / rate.
+        double best = 0;
         for (int u = es == 1 ? 8 : 16; u >= 2 * es && u >= 4; u >>= 1) {
             const i64 T = 16 * (u / es);
-            const i64 area = ((p.n[0] + T - 1) / T * T) * ((p.n[1] + T - 1) / T * T);
-            if (!U || area < best) { U = u; best = area; }
+            const double area = (double)((p.n[0] + T - 1) / T * T) * (double)((p.n[1] + T - 1) / T * T);
+            const double cost = area / (u == 16 ? 1.0 : u == 8 ? (es == 1 ? 1.0 : 0.7) : (es == 1 ? 0.7 : 0.4));
+            if (!U || cost < best) { U = u; best = cost; }
         }
         const int T = 16 * (U / es);
         p.tiles0 = (p.n[0] + T - 1) / T;
