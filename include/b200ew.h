@@ -207,6 +207,15 @@ b200_status b200_dimshuffle(uint64_t dst, uint64_t src, int32_t elem_bytes, int3
 b200_status b200_compensated_sum(uint64_t sum, uint64_t cmp, uint64_t add, int32_t dtype, uint64_t count,
                                  float cmp_scale, float add_scale, int32_t rounding_bits, uint64_t stream);
 
+/* ---- histogram of binary orders of magnitude
+ * replaces GPUTensor.hist -> _compute_hist (neon/backends/nervanagpu.py:619-637,
+ * neon/backends/float_ew.py:1069-1158): hist[b] = number of elements with
+ * clamp(round(log2|x|) - offset, 0, nbins - 1) == b, for a contiguous f32/f16/bf16 array.
+ * `hist` (nbins int32 counters) is zeroed by the call.  nbins <= B200_HIST_MAX_BINS. */
+#define B200_HIST_MAX_BINS 128
+b200_status b200_log2_hist(uint64_t in, int32_t dtype, uint64_t count, uint64_t hist, int32_t nbins,
+                           int32_t offset, uint64_t stream);
+
 /* ---- the same reduction for callers that cannot allocate device memory
  * No counterpart in the reference.  Meant for hosts where cudaMalloc is off
  * limits when the call is made (a framework pool owns the device, a latency-

@@ -116,6 +116,8 @@ class B200Backend(OpTreeBackend):
         self.launch_log = None             # set to a list to record (kind, desc) per launch
         self.trace = []                    # with bench=True: one record per launch (name, geometry, ms)
         self._trace_events = None
+        self.hist_bins, self.hist_offset = None, None
+        self.set_hist_buffers(hist_bins, hist_offset)
         super(B200Backend, self).__init__(rng_seed, default_dtype, compat_mode=compat_mode,
                                           deterministic=deterministic)
 
@@ -505,6 +507,48 @@ class B200Backend(OpTreeBackend):
                           [a.strides[x] for x in axes], self.stream)
         self.launches += max(int(repeat), 1)
         return out
+
+    # ------------------------------------------------------------------ log2 histograms (nervanagpu.py:826-834, 1077-1097)
+    def set_hist_buffers(self, hist_bins, hist_offset):
+        """Bins (one per power of two) and the power of two of bin 0 for ``tensor.hist(tag)``."""
+        if hist_bins != self.hist_bins or hist_offset != self.hist_offset:
+            if not 0 < int(hist_bins) <= 128:
+                raise ValueError("between 1 and 128 histogram bins")
+            self.hist_bins, self.hist_offset = int(hist_bins), int(hist_offset)
+            self.hist_map = dict()
+            self.hist_idx = 0
+            self.hist_max = 4 * 4096
+            self._hist_block = None          # hist_max rows of hist_bins counters, allocated at first use
+
+    def _hist_tensor(self, tag):
+        """The next free row of the histogram buffer as a (1, hist_bins) int32 tensor, remembered by tag."""
+        assert self.hist_idx < self.hist_max
+        if self._hist_block is None:
+            self._hist_block = self.zeros((self.hist_max, self.hist_bins), dtype=np.int32)
+        row = self._hist_block[self.hist_idx:self.hist_idx + 1]
+        row.name = tag
+        self.hist_map[tag] = self.hist_idx
+        self.hist_idx += 1
+        return row
+
+    def dump_hist_data(self):
+        """(tensor of all histograms taken so far, {tag: row}); starts a new collection."""
+        if self._hist_block is None:
+            self._hist_block = self.zeros((self.hist_max, self.hist_bins), dtype=np.int32)
+        hist_data = self._hist_block[0:self.hist_idx] if self.hist_idx else self._hist_block[0:0]
+        hist_map = self.hist_map
+        self.hist_map = dict()
+        self.hist_idx = 0
+        return hist_data, hist_map
+
+    def _compute_hist(self, tensor, hist_tensor):
+        """hist_tensor[b] = number of elements of tensor with round(log2|x|) - hist_offset == b,
+        clamped to the first and last bin (neon/backends/float_ew.py:1069-1158)."""
+        if not tensor.is_contiguous or tensor.take_array is not None:
+            raise ValueError("histogram of a contiguous tensor only")
+        rt.log2_hist(tensor.gpudata, dtype_code(tensor.dtype), tensor.size, hist_tensor.gpudata,
+                     self.hist_bins, self.hist_offset, self.stream)
+        self.launches += 1
 
     def compensated_sum(self, sum_tensor, cmp_tensor, add_tensor, cmp_scale=1.0, add_scale=1.0):
         """Kahan-compensated ``sum_tensor += add_tensor*add_scale`` with the lost low-order

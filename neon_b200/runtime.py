@@ -79,6 +79,7 @@ SIGNATURES = {
                         u64, i32, C.c_int64, C.c_int64, i32, i32, i32, C.c_float, C.c_float, u64]),
     "b200_dimshuffle": (i32, [u64, u64, i32, i32, P(C.c_int64), P(C.c_int64), P(C.c_int64), u64]),
     "b200_compensated_sum": (i32, [u64, u64, u64, i32, u64, C.c_float, C.c_float, i32, u64]),
+    "b200_log2_hist": (i32, [u64, i32, u64, u64, i32, i32, u64]),
     "b200_reduce_full_noalloc_max_count": (u64, []),
     "b200_reduce_full_noalloc": (i32, [u64, i32, u64, i32, i32, u64, u64]),
     "b200_comm_unique_id": (i32, [P(C.c_uint8)]),
@@ -355,6 +356,10 @@ def dimshuffle(dst, src, elem_bytes, shape, dst_strides, src_strides, stream=0):
 def compensated_sum(sum_ptr, cmp_ptr, add_ptr, dtype, count, cmp_scale, add_scale, rounding_bits, stream=0):
     check(lib().b200_compensated_sum(sum_ptr, cmp_ptr, add_ptr, dtype, count, cmp_scale, add_scale,
                                      rounding_bits, stream))
+
+
+def log2_hist(src, dtype, count, hist, nbins, offset, stream=0):
+    check(lib().b200_log2_hist(src, dtype, count, hist, nbins, offset, stream))
 
 
 def reduce_full_noalloc(src, dtype, count, op, absolute, out, stream=0):

@@ -326,4 +326,10 @@ class B200Tensor(Tensor):
                               name=name, rounding=self.rounding, _block=self._block)
 
     def hist(self, tag):
-        raise NotImplementedError("histogram kernel is outside the op-tree path")
+        """Histogram of round(log2|x|) of the tensor's values in the backend's bins
+        (nervanagpu.py:619-637); ``tag`` names the histogram in ``dump_hist_data``."""
+        if not self.is_contiguous or self.take_array is not None:
+            raise ValueError("histogram of a contiguous tensor only")
+        hist_tensor = self.backend._hist_tensor(tag)
+        self.backend._compute_hist(self, hist_tensor)
+        return hist_tensor

@@ -281,6 +281,19 @@ class OracleBackend(OpTreeBackend):
     def zeros_like(self, other, name=None, persist_values=True):
         return self.zeros(other.shape, dtype=self.default_dtype, name=name)
 
+    @staticmethod
+    def log2_hist(values, nbins=64, offset=-48):
+        """Counts per bin of clamp(round(log2|x|) - offset, 0, nbins - 1), with C's round (halves
+        away from zero), zero and NaN in bin 0 and infinity in the last bin: what the kernel text
+        of float_ew.py:1086-1100 computes in fp32 (GPU only in the reference)."""
+        a = np.abs(np.asarray(values).astype(np.float32)).ravel()
+        with np.errstate(divide="ignore", invalid="ignore"):
+            lg = np.log2(a).astype(np.float32)
+            t = np.where(lg >= 0, np.floor(lg + np.float32(0.5)), np.ceil(lg - np.float32(0.5))) - np.float32(offset)
+        bins = np.where(~(t > 0), 0, np.where(t < nbins - 1, t, nbins - 1))
+        bins = np.nan_to_num(bins, nan=0.0).astype(np.int64)
+        return np.bincount(bins, minlength=nbins).astype(np.int32)
+
     def copy_transpose(self, a, out, axes=None, repeat=1):
         """numpy.transpose into ``out`` (nervanacpu.py:1046-1051)."""
         out._tensor[:] = np.transpose(a._tensor, axes).copy()

@@ -59,3 +59,17 @@ def test_onehot_assignment_matches_reference_rule():
     want = np.zeros((4, 5), np.float32)
     want[[2, 0, 3, 1, 1], np.arange(5)] = 1
     assert np.array_equal(out.get(), want)
+
+
+def test_log2_histogram_known_answers():
+    """float_ew.py:1086-1100: bin = clamp(round(log2|x|) - offset, 0, nbins - 1); with offset -48,
+    1.0 is bin 48, 1.5 and 2.0 bin 49, 2.9 and 3.0 bin 50; zero, NaN and anything at or below
+    2^-48 fall into bin 0, infinity and anything from 2^15 up into bin 63."""
+    v = np.array([1.0, 2.0, 3.0, 0.0, np.inf, np.nan, 2.0 ** -48, 2.0 ** -60, 1.5, 2.9, 2.0 ** 15, 2.0 ** 20],
+                 np.float32)
+    h = OracleBackend.log2_hist(v, 64, -48)
+    assert {i: int(c) for i, c in enumerate(h) if c} == {0: 4, 48: 1, 49: 2, 50: 2, 63: 3}
+    assert h.dtype == np.int32 and h.sum() == v.size
+    # negative logs round away from zero too: 2^-1.6 -> -2, 2^-1.4 -> -1
+    h = OracleBackend.log2_hist(np.array([2.0 ** -1.6, 2.0 ** -1.4], np.float32), 8, -4)
+    assert {i: int(c) for i, c in enumerate(h) if c} == {2: 1, 3: 1}

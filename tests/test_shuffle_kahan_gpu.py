@@ -188,3 +188,53 @@ def test_compensated_sum_reset_period_and_argument_checks(b200):
     big = be.zeros((64, 4))
     with pytest.raises(ValueError):
         be.compensated_sum(big[:, 0:1], c, a)
+
+
+# ---------------------------------------------------------------- log2 histogram
+def _values_away_from_bin_edges(rng, n, lo=-30, hi=12):
+    """Magnitudes 2^(k + f) with f at least 0.02 away from the rounding edge at 0.5."""
+    k = rng.randint(lo, hi, n)
+    f = rng.uniform(-0.48, 0.48, n)
+    return (np.exp2(k + f) * rng.choice([-1.0, 1.0], n)).astype(np.float32)
+
+
+@pytest.mark.parametrize("dtype", [np.float32, np.float16])
+def test_log2_histogram_matches_the_restated_kernel(b200, dtype):
+    from oracle.numpy_backend import OracleBackend
+    be = b200
+    rng = np.random.RandomState(9)
+    lo, hi = (-30, 12) if dtype == np.float32 else (-12, 12)
+    for n in (1, 7, 1000, 100003, 1 << 20):
+        h = _values_away_from_bin_edges(rng, n, lo, hi).astype(dtype).reshape(n, 1)
+        if n >= 1000:
+            h[5] = 0.0
+            h[6] = np.inf
+            h[7] = np.nan
+            h[8] = -np.inf
+        t = be.array(h, dtype=dtype)
+        got = t.hist("n%d" % n)
+        assert tuple(got.shape) == (1, be.hist_bins) and got.dtype == np.int32
+        want = OracleBackend.log2_hist(h, be.hist_bins, be.hist_offset)
+        assert np.array_equal(got.get().ravel(), want), (n, dtype)
+        assert int(got.get().sum()) == n
+    data, tags = be.dump_hist_data()
+    assert tuple(data.shape) == (5, be.hist_bins) and sorted(tags) == sorted("n%d" % n for n in (1, 7, 1000, 100003, 1 << 20))
+    assert int(data.get()[tags["n1000"]].sum()) == 1000
+    assert be.hist_idx == 0 and be.hist_map == {}
+
+
+def test_log2_histogram_bins_and_offset_can_be_changed(b200):
+    from oracle.numpy_backend import OracleBackend
+    be = b200
+    old = (be.hist_bins, be.hist_offset)
+    try:
+        be.set_hist_buffers(16, -8)
+        rng = np.random.RandomState(10)
+        h = _values_away_from_bin_edges(rng, 5000, -20, 20).reshape(50, 100)
+        got = be.array(h).hist("w")
+        assert tuple(got.shape) == (1, 16)
+        assert np.array_equal(got.get().ravel(), OracleBackend.log2_hist(h, 16, -8))
+        with pytest.raises(ValueError):
+            be.array(h)[:, 0:10].hist("view")
+    finally:
+        be.set_hist_buffers(*old)
