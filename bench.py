@@ -41,9 +41,9 @@ METRIC = "compound-optree effective HBM GB/s"
 WORKLOAD = ("cfg5: z=tanh(x)*sqrt(|y|)+0.5*x*y (fp16, stochastic rounding), "
             "total=sum(z), peak=max|z|")
 # dram__bytes_read.sum + dram__bytes_write.sum of the z kernel divided by its elements, from the
-# ncu capture of a 2^26-element launch (profiles/ew_kernel_cfg5_fp16_chain.md: 268.5 MB + 103.2 MB);
+# ncu capture of a 2^26-element launch (profiles/ew_kernel_cfg5_fp16_chain.md: 268.5 MB + 102.6 MB);
 # traffic grows in proportion to the elements, so a full launch is this times its element count
-Z_DRAM_BYTES_PER_ELEMENT = (268.460288e6 + 103.152128e6) / (1 << 26)
+Z_DRAM_BYTES_PER_ELEMENT = (268.459264e6 + 102.589184e6) / (1 << 26)
 
 
 def measured_peak():
@@ -322,6 +322,23 @@ def run_other(args, be, rank, world, barrier, max_over_ranks):
         be.record_mark(ev1)
         be.synchronize()
         graph_ms = be.get_time(ev0, ev1) / args.steps
+    # working sets that stay in L2 between steps: the same statements again with L2 flushed
+    # (a 256 MiB fill) before each one, timed per statement so that the fill is not counted
+    cold = None
+    if world == 1 and n_local * 4 < 100e6:
+        flush = be.empty((1 << 26, 1))
+        cold_marks = [[(be.init_mark(), be.init_mark()) for _ in stmts] for _ in range(args.steps)]
+        for s in range(args.steps):
+            for i, (_, fn, _) in enumerate(stmts):
+                flush.fill(0)
+                be.record_mark(cold_marks[s][i][0])
+                fn()
+                be.record_mark(cold_marks[s][i][1])
+        be.synchronize()
+        cold_ms = sum(float(np.median([be.get_time(*cold_marks[s][i]) for s in range(args.steps)]))
+                      for i in range(len(stmts)))
+        cold = {"ms_per_step": cold_ms, "GBps": sum(b for _, _, b in stmts) / cold_ms / 1e6,
+                "note": "L2 flushed (256 MiB fill) before every statement; sum of per-statement medians"}
     if rank != 0:
         return
     per = []
@@ -341,6 +358,7 @@ def run_other(args, be, rank, world, barrier, max_over_ranks):
                    "l2": "working set is L2-resident between steps" if n_local * 4 < 100e6 else "exceeds L2"},
         "pct_of_measured_peak_per_gpu": 100.0 * value / world / peak_gbs, "peak_kind": peak_kind,
         "statements": per, "gpu_launches": launches,
+        "cold": cold,
         "graph_replay": None if graph_ms is None else {
             "ms_per_step": graph_ms, "GBps": nbytes_step / graph_ms / 1e6,
             "note": "statement sequence recorded once with be.capture(), replayed with one call"},

@@ -799,6 +799,12 @@ DEV void cluster_barrier_warp0_releases() {
     else asm volatile("barrier.cluster.arrive.relaxed.aligned;" ::: "memory");
     asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
+// store into the same shared-memory location of block `rank` of this cluster
+DEV void dsmem_st(void* local, u32 rank, u32 v) {
+    u32 addr;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(addr) : "r"(smem_u32(local)), "r"(rank));
+    asm volatile("st.shared::cluster.u32 [%0], %1;" ::"r"(addr), "r"(v) : "memory");
+}
 DEV u32 dsmem_ld(const void* local, u32 rank) {
     u32 addr, v;
     asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(addr) : "r"(smem_u32(local)), "r"(rank));
@@ -985,15 +991,17 @@ DEV void rr_pass(const P& q, const P& p, i64 k, i64 knext, RowCtx& cx, unsigned 
 // Block results of one pass -> row result, left in res[0..NR) (value bits, or the index for arg
 // reductions) for every thread to read, and in a / ai of warp 0.  Warp 0 does the combining,
 // lane w standing for warp w and then for block w of the cluster, with xor butterflies (a fixed
-// order, so results repeat exactly); the other warps only take part in the barriers.
+// order, so results repeat exactly); the other warps only take part in the barriers.  Blocks
+// PUSH their result into every peer's slots before the cluster barrier, so that after it each
+// block reads only its own shared memory.
 template <template <int> class SV, int V, int C, int THREADS>
 DEV void rr_combine(const RowCtx& cx, float* a, int* ai, float (*sv)[THREADS / 32], int (*si)[THREADS / 32],
-                    u32* slots /* [2 parities][NR][2] of this pass */, u32* res) {
+                    u32* slots /* [2 parities][NR][C][2] of this pass */, u32* res) {
     typedef SV<V> S;
     constexpr int NR = S::NRED;
     constexpr int NW = THREADS / 32;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    u32* mine = slots + cx.row_parity * NR * 2;
+    u32* mine = slots + cx.row_parity * NR * C * 2;
     __syncthreads();                                  // the warps' results are in sv / si
     if (warp == 0) {
 #pragma unroll
@@ -1006,7 +1014,11 @@ DEV void rr_combine(const RowCtx& cx, float* a, int* ai, float (*sv)[THREADS / 3
                 int bi = red_is_arg(S::op(r)) ? __shfl_xor_sync(0xffffffffu, ai[r], o) : 0;
                 red_merge(S::op(r), a[r], ai[r], b, bi);
             }
-            if (C > 1 && lane == 0) { mine[2 * r] = __float_as_uint(a[r]); mine[2 * r + 1] = (u32)ai[r]; }
+            if (C > 1 && lane < C) {                  // lane w writes this block's entry at block w
+                u32* entry = mine + (r * C + (int)cx.rank) * 2;
+                dsmem_st(entry, (u32)lane, __float_as_uint(a[r]));
+                if (red_is_arg(S::op(r))) dsmem_st(entry + 1, (u32)lane, (u32)ai[r]);
+            }
         }
     }
     if constexpr (C > 1) {
@@ -1014,9 +1026,9 @@ DEV void rr_combine(const RowCtx& cx, float* a, int* ai, float (*sv)[THREADS / 3
         if (warp == 0) {
 #pragma unroll
             for (int r = 0; r < NR; ++r) {
-                const u32 peer = lane < C ? (u32)lane : 0u;
-                a[r] = __uint_as_float(dsmem_ld(mine + 2 * r, peer));
-                ai[r] = red_is_arg(S::op(r)) ? (int)dsmem_ld(mine + 2 * r + 1, peer) : -1;
+                const u32* entry = mine + (r * C + (lane < C ? lane : 0)) * 2;
+                a[r] = __uint_as_float(entry[0]);
+                ai[r] = red_is_arg(S::op(r)) ? (int)entry[1] : -1;
 #pragma unroll
                 for (int o = C / 2; o > 0; o >>= 1) {
                     float b = __shfl_xor_sync(0xffffffffu, a[r], o);

@@ -713,7 +713,7 @@ class Planner(object):
         body.append("extern __shared__ __align__(128) unsigned char dyn[];")
         body.append("__shared__ u64 bars[2 * RR_MAX_CHUNKS];")
         body.append("__shared__ float sv[%d][%d]; __shared__ int si[%d][%d];" % (nrmax, threads // 32, nrmax, threads // 32))
-        body.append("__shared__ u32 slots[%d][2][%d][2]; __shared__ u32 s_res[%d];" % (len(ems), nrmax, nres))
+        body.append("__shared__ u32 slots[%d][2][%d][%d][2]; __shared__ u32 s_res[%d];" % (len(ems), nrmax, C, nres))
         body.append("RowCtx cx; rr_begin<%d, %d, %d>(cx, p.nvec, bars);" % (C, threads, unroll))
         body.append("const i64 n0 = (i64)cx.v0 * %d;" % V)
         body.append("const i64 kfirst = %s, kstep = %s;" % (("cluster_index()", "cluster_count()") if C > 1
@@ -735,7 +735,7 @@ class Planner(object):
             body.append("    rr_pass<S%d, ST, P, %d, %d, %d, %s, %s>(q, p, k, knext, cx, %s, %s, a, ai, sv, si);"
                         % (i, V, threads, unroll, "true" if i == 0 else "false", "true" if last else "false",
                            dyn_cur, bars_cur))
-            body.append("    rr_combine<S%d, %d, %d, %d>(cx, a, ai, sv, si, &slots[%d][0][0][0], &s_res[%d]);"
+            body.append("    rr_combine<S%d, %d, %d, %d>(cx, a, ai, sv, si, &slots[%d][0][0][0][0], &s_res[%d]);"
                         % (i, V, C, threads, i, slot_of[rs[0].nid]))
         if red_out:
             body.append("    if (threadIdx.x == 0 && cx.rank == 0) SF<%d>::epilogue(q, k, a, ai);" % V)
