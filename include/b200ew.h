@@ -210,7 +210,8 @@ b200_status b200_compensated_sum(uint64_t sum, uint64_t cmp, uint64_t add, int32
 /* ---- histogram of binary orders of magnitude
  * replaces GPUTensor.hist -> _compute_hist (neon/backends/nervanagpu.py:619-637,
  * neon/backends/float_ew.py:1069-1158): hist[b] = number of elements with
- * clamp(round(log2|x|) - offset, 0, nbins - 1) == b, for a contiguous f32/f16/bf16 array.
+ * clamp(round(log2|x|) - offset, 0, nbins - 1) == b, for a contiguous array of any supported
+ * dtype (integers are binned by their value converted to float).
  * `hist` (nbins int32 counters) is zeroed by the call.  nbins <= B200_HIST_MAX_BINS. */
 #define B200_HIST_MAX_BINS 128
 b200_status b200_log2_hist(uint64_t in, int32_t dtype, uint64_t count, uint64_t hist, int32_t nbins,

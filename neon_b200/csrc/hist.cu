@@ -91,8 +91,7 @@ extern "C" b200_status b200_log2_hist(uint64_t in, int32_t dtype, uint64_t count
                                      int32_t offset, uint64_t stream) {
     if (!in || !hist) return b200_detail_fail(B200_ERR_INVALID, "b200_log2_hist: null device pointer");
     if (nbins < 1 || nbins > kMaxBins) return b200_detail_fail(B200_ERR_INVALID, "b200_log2_hist: 1 to 128 bins");
-    if (dtype != B200_F32 && dtype != B200_F16 && dtype != B200_BF16)
-        return b200_detail_fail(B200_ERR_UNSUPPORTED, "b200_log2_hist: only f32, f16 and bf16 tensors");
+    if (dtype < B200_F32 || dtype > B200_U8) return b200_detail_fail(B200_ERR_INVALID, "b200_log2_hist: unknown dtype");
     if (hist % 4) return b200_detail_fail(B200_ERR_INVALID, "b200_log2_hist: histogram not 4-byte aligned");
     cudaStream_t s = static_cast<cudaStream_t>(b200_detail_stream(stream));
     cudaError_t e = cudaMemsetAsync(reinterpret_cast<void*>(hist), 0, 4u * (unsigned)nbins, s);
@@ -104,9 +103,17 @@ extern "C" b200_status b200_log2_hist(uint64_t in, int32_t dtype, uint64_t count
             HP p;
             p.in = in; p.hist = hist; p.count = (i64)count; p.nvec = 0; p.nbins = nbins; p.offset = offset;
             const bool aligned = in % 16 == 0;
-            if (dtype == B200_F32) e = launch<b200::F32>(p, aligned, sms, s);
-            else if (dtype == B200_F16) e = launch<b200::F16>(p, aligned, sms, s);
-            else e = launch<b200::BF16>(p, aligned, sms, s);
+            switch (dtype) {                  // integer tensors are binned by their value as a float
+            case B200_F32: e = launch<b200::F32>(p, aligned, sms, s); break;
+            case B200_F16: e = launch<b200::F16>(p, aligned, sms, s); break;
+            case B200_BF16: e = launch<b200::BF16>(p, aligned, sms, s); break;
+            case B200_I32: e = launch<b200::I32>(p, aligned, sms, s); break;
+            case B200_U32: e = launch<b200::U32>(p, aligned, sms, s); break;
+            case B200_I16: e = launch<b200::I16>(p, aligned, sms, s); break;
+            case B200_U16: e = launch<b200::U16>(p, aligned, sms, s); break;
+            case B200_I8: e = launch<b200::I8>(p, aligned, sms, s); break;
+            default: e = launch<b200::U8>(p, aligned, sms, s); break;
+            }
         }
     }
     if (e != cudaSuccess) {

@@ -73,3 +73,35 @@ def test_log2_histogram_known_answers():
     # negative logs round away from zero too: 2^-1.6 -> -2, 2^-1.4 -> -1
     h = OracleBackend.log2_hist(np.array([2.0 ** -1.6, 2.0 ** -1.4], np.float32), 8, -4)
     assert {i: int(c) for i, c in enumerate(h) if c} == {2: 1, 3: 1}
+
+
+def _reference_test_hist(inp, nbins=64, offset=-48):
+    """The numpy formulation neon's own histogram test compares backends with
+    (tests/test_backend_hist.py:25-43): np.histogram of rint(log2|x|) over unit bins."""
+    bins = np.arange(nbins + 1) + float(offset)
+    bins[0] = -float("Inf")
+    with np.errstate(divide="ignore"):
+        v = np.rint(np.log2(np.abs(inp.astype(np.float32))))
+    return np.histogram(v, density=False, bins=bins)[0]
+
+
+HIST_EDGE_INPUTS = [                                  # tests/test_backend_hist.py:101-108
+    ("edges", np.array([2 ** -48, 2 ** 15], dtype=np.float32)),
+    ("rounding", np.array([2 ** 5, 63.99998856, 2 ** 6, 2 ** -3, 2 ** -4, 0.11262291, 92.22483826], dtype=np.float32)),
+    ("fp16 rounding", np.array([45.21875], dtype=np.float16)),
+]
+
+
+def test_log2_histogram_agrees_with_the_reference_tests_formulation():
+    """Edge-case inputs of neon's histogram test, and its parametrised sweep (normal(64, 4) data
+    as float32 and uint8, bins (64, -48) and (32, 0)): the restated kernel gives the counts of the
+    test's np.histogram formulation."""
+    for tag, inp in HIST_EDGE_INPUTS:
+        assert np.array_equal(OracleBackend.log2_hist(inp), _reference_test_hist(inp)), tag
+    rng = np.random.RandomState(0)
+    for nbins, offset in ((64, -48), (32, 0)):
+        for dim in ((64, 32768), (64, 1)):
+            for dtype in (np.float32, np.uint8):
+                inp = rng.normal(64, 4, dim[0] * dim[1]).reshape(dim).astype(dtype)
+                assert np.array_equal(OracleBackend.log2_hist(inp, nbins, offset),
+                                      _reference_test_hist(inp, nbins, offset)), (nbins, offset, dim, dtype)

@@ -238,3 +238,30 @@ def test_log2_histogram_bins_and_offset_can_be_changed(b200):
             be.array(h)[:, 0:10].hist("view")
     finally:
         be.set_hist_buffers(*old)
+
+
+def test_log2_histogram_on_the_reference_tests_inputs(b200):
+    """tests/test_backend_hist.py: the edge cases, dump_hist_data, and normal(64, 4) data stored as
+    float32 and as uint8 with (64, -48) and (32, 0) bins."""
+    from oracle.numpy_backend import OracleBackend
+    from tests.test_oracle import HIST_EDGE_INPUTS
+    be = b200
+    old = (be.hist_bins, be.hist_offset)
+    try:
+        for tag, inp in HIST_EDGE_INPUTS:
+            got = be.array(inp.reshape(-1, 1), dtype=inp.dtype).hist(tag)
+            assert np.array_equal(got.get().ravel(), OracleBackend.log2_hist(inp)), tag
+        data, tags = be.dump_hist_data()
+        for tag, inp in HIST_EDGE_INPUTS:
+            assert np.array_equal(data.get()[tags[tag]], OracleBackend.log2_hist(inp)), tag
+        rng = np.random.RandomState(0)
+        for nbins, offset in ((64, -48), (32, 0)):
+            be.set_hist_buffers(nbins, offset)
+            for dim in ((64, 32768), (64, 1)):
+                for dtype in (np.float32, np.uint8, np.float16, np.int8):
+                    inp = rng.normal(64, 4, dim[0] * dim[1]).reshape(dim).astype(dtype)
+                    got = be.array(inp, dtype=dtype).hist("x")
+                    assert np.array_equal(got.get().ravel(), OracleBackend.log2_hist(inp, nbins, offset)), (nbins, dim, dtype)
+            be.dump_hist_data()
+    finally:
+        be.set_hist_buffers(*old)
