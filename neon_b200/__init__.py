@@ -16,6 +16,12 @@ def gen_backend(*args, **kwargs):
     return _gen(*args, **kwargs)
 
 
+def Autodiff(op_tree, be, next_error=None):
+    """Symbolic gradients of an op-tree (see neon_b200/autodiff.py)."""
+    from .autodiff import Autodiff as _Autodiff
+    return _Autodiff(op_tree, be, next_error)
+
+
 def __getattr__(name):
     if name in ("B200Backend", "B200Tensor"):
         from . import backend, tensor

@@ -111,6 +111,7 @@ class OracleTensor(Tensor):
         self.dtype = dtype
         self.base = base
         self.rounding = 0
+        self.is_trans = False
 
     @property
     def is_contiguous(self):
@@ -131,8 +132,10 @@ class OracleTensor(Tensor):
         shape = list(sub.shape)
         while len(shape) > 2 and 1 in shape:
             shape.remove(1)
-        return OracleTensor(self.backend, ary=sub.reshape(shape),
+        view = OracleTensor(self.backend, ary=sub.reshape(shape),
                             dtype=sub.dtype, base=self)
+        view.is_trans = self.is_trans
+        return view
 
     def _assign(self, value):
         if isinstance(value, (OracleTensor, OpTreeNode)):
@@ -182,8 +185,10 @@ class OracleTensor(Tensor):
 
     @property
     def T(self):
-        return OracleTensor(self.backend, ary=self._tensor.transpose(),
+        view = OracleTensor(self.backend, ary=self._tensor.transpose(),
                             dtype=self._tensor.dtype, base=self)
+        view.is_trans = not self.is_trans
+        return view
 
     def transpose(self, out=None):
         if out:

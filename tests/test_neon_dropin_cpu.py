@@ -144,3 +144,37 @@ def test_neon_array_iterator_runs_unmodified(neon_env):
     # one transpose + one onehot per minibatch, one more of each for the wrapped part
     assert be.shuffles - shuffles == batches + 1
     assert len(be.passes) - passes == batches + 1
+
+
+def test_neon_batchnorm_autodiff_layer_uses_the_routed_autodiff(neon_env):
+    """BatchNormAutodiff (neon/layers/layer.py:2583-2651) builds its fprop as one op-tree and asks
+    ``Autodiff`` for the three gradients on every bprop.  neon's class refuses foreign op-tree
+    nodes; after ``register()`` the name the layer module sees dispatches on the backend.  (The
+    layer's own ``fprop`` calls ``init_buffers``, which its base class no longer has in this neon
+    version, so the test takes the layer's op-tree builder and repeats the three lines of its
+    ``bprop``.)"""
+    be = neon_env
+    import neon_b200.neon_plugin as plugin
+    plugin.register()
+    import neon.layers.layer as layer_module
+    from neon.layers.layer import BatchNormAutodiff
+    assert getattr(layer_module.Autodiff, "_b200_router", False)
+    nfm = 10
+    layer = BatchNormAutodiff()
+    layer.x = be.empty((nfm, be.bsz))
+    layer.gamma, layer.beta = be.empty((nfm, 1)), be.empty((nfm, 1))
+    layer.grad_gamma, layer.grad_beta = be.empty((nfm, 1)), be.empty((nfm, 1))
+    layer.deltas = be.empty((nfm, be.bsz))
+    layer.fprop_op_tree = layer.get_forward_optree()
+    y = be.empty((nfm, be.bsz))
+    y[:] = layer.fprop_op_tree
+    before = len(be.passes)
+    ad = layer_module.Autodiff(layer.fprop_op_tree, be, next_error=layer.deltas)
+    ad.back_prop_grad([layer.x, layer.gamma, layer.beta], [layer.deltas, layer.grad_gamma, layer.grad_beta])
+    assert len(be.passes) - before >= 3          # grad_gamma, grad_beta, deltas
+    assert layer_module.Autodiff(layer.fprop_op_tree, be, next_error=layer.deltas) is ad      # memoised
+    # neon's own backends still get neon's class
+    from neon.backends.nervanacpu import NervanaCPU
+    cpu = NervanaCPU()
+    t = cpu.array(np.ones((2, 2), np.float32))
+    assert type(layer_module.Autodiff(t * t, cpu)).__module__ == "neon.backends.autodiff"
