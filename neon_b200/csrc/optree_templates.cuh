@@ -195,6 +195,15 @@ DEV float ex2_approx(float x) { float r; asm("ex2.approx.ftz.f32 %0, %1;" : "=f"
 DEV float rcp_approx(float x) { float r; asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(x)); return r; }
 DEV float fast_sqrt(float x) { float r; asm("sqrt.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(x)); return r; }
 DEV float fast_div(float a, float b) { float r; asm("div.approx.f32 %0, %1, %2;" : "=f"(r) : "f"(a), "f"(b)); return r; }
+// exp: 2^(x log2 e) with the product carried in two pieces (t + r), so that the error does not
+// grow with |x| as it does for ex2(x * log2e) alone; at most 3 ulp.  Results below the normal
+// range are flushed to zero.
+DEV float fast_exp(float x) {
+    const float t = x * 1.44269502162933349609375f;              // log2(e) rounded to fp32
+    float r = __fmaf_rn(x, 1.44269502162933349609375f, -t);      // what that product lost, exactly
+    r = __fmaf_rn(x, 1.925963033500011e-8f, r);                  // + x * (log2(e) - its fp32 value)
+    return ex2_approx(t) * (1.0f + r * 0.693147182464599609375f);   // 2^(t + r) ~ 2^t (1 + r ln 2)
+}
 // tanh: odd polynomial x + x^3 Q(x^2) below 0.6 (least-squares fit, 1.2 ulp),
 // 1 - 2/(e^(2|x|) + 1) with the sign of x above it
 DEV float fast_tanh(float x) {
@@ -880,7 +889,7 @@ DEV void rr_issue_row(const P& p, const RowCtx& cx, i64 k, unsigned char* dyn, u
 }
 DEV u64 global_ns() { u64 t; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t)); return t; }
 // Wait for one chunk, for at most limit_ns.  When the time runs out the thread
-// records it in *status and stops waiting; rr_row_end makes that the verdict of
+// records it in *status and stops waiting; rr_row_end makes that the outcome for
 // the whole block, which then stops staging (its results are meaningless, the
 // host raises on the status) but keeps taking part in every barrier so that its
 // cluster peers are never left waiting.

@@ -68,9 +68,11 @@ UNARY_FAST = dict(UNARY_C)
 UNARY_FAST.update({
     "sqrt": "fast_sqrt({0})",
     "tanh": "fast_tanh({0})",
-    "sig": "rcp_approx(1.0f + expf(-{0}))",
-    "sig2": "rcp_approx(1.0f + exp2f(-{0}))",
-    "tanh2": "fast_div(exp2f(2.0f * {0}) - 1.0f, exp2f(2.0f * {0}) + 1.0f)",
+    "exp": "fast_exp({0})",
+    "exp2": "ex2_approx({0})",
+    "sig": "rcp_approx(1.0f + fast_exp(-{0}))",
+    "sig2": "rcp_approx(1.0f + ex2_approx(-{0}))",
+    "tanh2": "fast_div(ex2_approx(2.0f * {0}) - 1.0f, ex2_approx(2.0f * {0}) + 1.0f)",
 })
 BINARY_FAST = dict(BINARY_C)
 BINARY_FAST.update({"div": "fast_div({0}, {1})"})
@@ -526,6 +528,8 @@ class Planner(object):
         self.rowres = True                 # keep rows in cluster shared memory across passes when they fit
         self.smem_cap = 200 * 1024         # dynamic shared memory a row-resident block may ask for
         self.rowres_slice_cap = 100 * 1024 # preferred largest slice of a row per block (two blocks per SM)
+        self.rowres_unroll = 2             # vectors per thread and chunk in the row-resident kernel
+        self.rowres_threads = None         # cap on its block size (None: as many as the registers allow)
         self.status_ptr = 0                # device int the kernels set when a bounded wait gives up
         self.wait_limit_ns = 2000000000    # how long a block waits for its staged row slice
         self.debug_starve_bytes = 0        # tests only: announce this many bytes that never arrive
@@ -655,7 +659,9 @@ class Planner(object):
         threads = 1024 // blocks_per_sm
         while threads > 256 and seg_vecs < 2 * threads:
             threads //= 2
-        unroll = 2
+        unroll = self.rowres_unroll
+        if self.rowres_threads:
+            threads = min(threads, int(self.rowres_threads))
         if (seg_vecs + threads * unroll - 1) // (threads * unroll) > 32:      # RR_MAX_CHUNKS mbarriers
             return None
         nrmax = max(len(rs) for _, rs, _ in ems)

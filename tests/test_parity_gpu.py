@@ -275,6 +275,24 @@ def test_fast_math_stays_within_a_few_ulp(b200):
     out[:] = x / be.array(pos)
     ref = xs.astype(np.float64) / pos.astype(np.float64)
     assert (np.abs(out.get() - ref) / np.maximum(np.spacing(np.abs(ref).astype(np.float32)), 1e-45)).max() <= 3.0
+    # exp over the whole range of normal results, sig, exp2
+    es = np.concatenate([np.linspace(-87.0, 88.5, 300001), np.linspace(-1, 1, 100001)]).astype(np.float32)
+    es = es[: (es.size // 8) * 8].reshape(8, -1)
+    e, eo = be.array(es), be.empty(es.shape)
+    eo[:] = be.exp(e)
+    ref = np.exp(es.astype(np.float64))
+    assert (np.abs(eo.get() - ref) / np.spacing(ref.astype(np.float32))).max() <= 4.0
+    eo[:] = be.exp2(e)
+    ref = np.exp2(es.astype(np.float64))
+    assert (np.abs(eo.get() - ref) / np.spacing(ref.astype(np.float32))).max() <= 3.0
+    eo[:] = be.sig(e)
+    ref = 1.0 / (1.0 + np.exp(-es.astype(np.float64)))
+    ok = ref > 1e-37
+    assert (np.abs(eo.get() - ref)[ok] / np.spacing(ref.astype(np.float32))[ok]).max() <= 6.0
+    big = be.array(np.array([[100.0, -104.0, 89.0, -200.0]], np.float32))
+    bo = be.empty((1, 4))
+    bo[:] = be.exp(big)
+    assert np.isinf(bo.get()[0, 0]) and bo.get()[0, 1] == 0.0 and np.isinf(bo.get()[0, 2]) and bo.get()[0, 3] == 0.0
 
 
 def test_stochastic_rounding_one_bit_distribution(b200):
