@@ -536,3 +536,46 @@ def test_onehot_and_views(b200):
     assert np.array_equal(x.T.get(), np.arange(48).reshape(6, 8).T)
     assert np.array_equal(x.reshape(8, 6).get(), np.arange(48).reshape(8, 6))
     assert np.array_equal(x[3].get(), np.arange(48).reshape(6, 8)[3:4])
+
+
+def test_more_than_two_to_the_32_elements(b200):
+    """Element indices past 2^32 (the 64-bit paths of the flat element-wise kernel, the
+    whole-tensor reduction, a row reduction and the random words of a stochastic store): a
+    (65536, 65540) fp16 tensor, 4.3e9 elements, checked through values planted near its end."""
+    be = b200
+    rows, cols = 65536, 65540
+    x = be.empty((rows, cols), dtype=np.float16)
+    x[:] = 0.5
+    tail = np.arange(1, 11, dtype=np.float16).reshape(1, 10)
+    x[rows - 1:rows, cols - 10:cols] = be.array(tail, dtype=np.float16)        # the very last ten elements
+    x[rows - 2:rows - 1, 0:10] = be.array(-tail, dtype=np.float16)
+    z = be.empty((rows, cols), dtype=np.float16)
+    z[:] = x * 2.0 + 1.0                                    # flat kernel, indices up to 2^32 + 2^18
+    assert np.array_equal(z[rows - 1:rows, cols - 12:cols].get().ravel(),
+                          np.concatenate([[2.0, 2.0], 2.0 * np.arange(1, 11) + 1.0]).astype(np.float16))
+    assert np.array_equal(z[rows - 2:rows - 1, 0:12].get().ravel(),
+                          np.concatenate([-2.0 * np.arange(1, 11) + 1.0, [2.0, 2.0]]).astype(np.float16))
+    assert float(z[0:1, 0:1].get()[0, 0]) == 2.0
+    peak, low, total = be.empty((1, 1)), be.empty((1, 1)), be.empty((1, 1))
+    peak[:] = be.max(z)
+    low[:] = be.min(z)
+    total[:] = be.sum(x)
+    assert float(peak.get()[0, 0]) == 21.0 and float(low.get()[0, 0]) == -19.0
+    want = 0.5 * (rows * cols - 20)                         # the planted values cancel
+    assert abs(float(total.get()[0, 0]) - want) <= 1e-5 * want
+    rowsum = be.empty((rows, 1))
+    rowsum[:] = be.sum(x, axis=1)
+    got = rowsum.get().ravel()
+    assert got[0] == 0.5 * cols and abs(got[-1] - (0.5 * (cols - 10) + 55.0)) < 1e-3 * cols
+    assert abs(got[-2] - (0.5 * (cols - 10) - 55.0)) < 1e-3 * cols
+    # stochastic store: the words used at the far end are those of the far element indices
+    from oracle import sround
+    z.rounding = True
+    seed, launch = be.rng_get_state()[1]
+    z[:] = x * 1.0009765625                                 # 0.5 * (1 + 2^-10): needs rounding at 10 bits
+    key = sround.launch_key(int(seed), int(launch))
+    last = np.arange(rows * cols - 16, rows * cols, dtype=np.uint64)
+    vals = (x[rows - 1:rows, cols - 16:cols].get().astype(np.float32) * np.float32(1.0009765625)).ravel()
+    ur = sround.rng_bits_pair(key[0], key[1], last)
+    want = sround.store(vals, np.float16, True, ur)
+    assert np.array_equal(z[rows - 1:rows, cols - 16:cols].get().ravel().view(np.uint16), want.view(np.uint16))
