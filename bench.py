@@ -467,7 +467,6 @@ def main():
     e2e_steps = max(1, args.e2e_steps)
     barrier()
     be.synchronize()
-    t0 = time.perf_counter()
     be.record_mark(ev0)
     for s in range(e2e_steps):
         rt.memcpy_h2d(x.ptr, hx_p, nbytes, be.stream, sync=False)

@@ -47,7 +47,8 @@ struct ShP {
     u64 dst, src;
     i64 n[kMaxDims], ds[kMaxDims], ss[kMaxDims];
     i64 tiles0, tiles1;
-    int nd, src_vec, dst_vec, pad_;
+    int nd, src_vec, dst_vec;    // tile kernel: vector access allowed on the input / output side
+    int bx_log2;                  // copy kernel: log2 of the lanes along dims[0]
 };
 
 template <int ES> struct elem_t;
@@ -199,7 +200,7 @@ __global__ void __launch_bounds__(256) shuffle_tile_kernel(const __grid_constant
 template <int ES>
 __global__ void __launch_bounds__(256) shuffle_copy_kernel(const __grid_constant__ ShP p) {
     typedef typename elem_t<ES>::type E;
-    const int bx_log2 = p.src_vec;                     // (field reused by this kernel)
+    const int bx_log2 = p.bx_log2;
     const int bx = 1 << bx_log2;
     const int tx = threadIdx.x & (bx - 1), ty = threadIdx.x >> bx_log2;
     u32 b = blockIdx.x;
@@ -282,7 +283,7 @@ extern "C" b200_status b200_dimshuffle(uint64_t dst, uint64_t src, int32_t elem_
     const bool tiled = od >= 0 && id >= 0 && od != id && n[od] >= 8 && n[id] >= 8;
 
     ShP p;
-    p.dst = dst; p.src = src; p.pad_ = 0; p.src_vec = 0; p.dst_vec = 0; p.tiles1 = 1;
+    p.dst = dst; p.src = src; p.bx_log2 = 8; p.src_vec = 0; p.dst_vec = 0; p.tiles1 = 1;
     int es = elem_bytes;
     int lead[2] = {-1, -1};
     if (tiled) { lead[0] = id; lead[1] = od; }
@@ -365,7 +366,7 @@ extern "C" b200_status b200_dimshuffle(uint64_t dst, uint64_t src, int32_t elem_
                 if (padded < best) { best = padded; bx_log2 = bl; }
             }
         }
-        p.src_vec = bx_log2;
+        p.bx_log2 = bx_log2;
         p.tiles0 = (p.n[0] + (4ll << bx_log2) - 1) / (4ll << bx_log2);
         p.tiles1 = (p.n[1] + (256 >> bx_log2) - 1) / (256 >> bx_log2);
         blocks = p.tiles0 * p.tiles1 * rest;

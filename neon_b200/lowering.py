@@ -557,7 +557,7 @@ class Planner(object):
             pz = self._rowres_pass(st, reds, levels, ka, ra, full_shape, rounding, root_is_k and out_is_k)
             if pz is not None:
                 return [pz]
-        for li, lv in enumerate(levels):
+        for lv in levels:
             rs = [n for n in reds if n.level == lv]
             final = fuse_final and (lv == levels[-1]) and root_is_k and out_is_k and st.root.level == lv
             K = full_shape[ka]
@@ -734,7 +734,6 @@ class Planner(object):
         body.append("for (i64 k = kfirst; k < p.K; k += kstep) {")
         body.append("    const i64 knext = k + kstep;")
         body.append("    float a[%d]; int ai[%d];" % (nrmax, nrmax))
-        n_launch = len(ems) + (0 if red_out else 1)
         dyn_cur, bars_cur = "dyn", "bars"
         for i, (em, rs, outs) in enumerate(ems):
             last = red_out and i == len(ems) - 1
@@ -994,8 +993,6 @@ class Planner(object):
             key = ("h", n.nid)
             if key in self.names:
                 return self.names[key]
-            W = "V" if self.lk else "1"
-            idx = "[i]" if self.lk else "[0]"
             if n.kind == "c":
                 self.f.f32("c%d" % n.nid, n.value)
                 name = "p.c%d" % n.nid

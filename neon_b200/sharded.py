@@ -198,7 +198,6 @@ class ShardedBackend(B200Backend):
         the rank, so that is the first occurrence, as numpy.argmax gives it."""
         from .tensor import B200Tensor
         W = self.world_size
-        val = B200Tensor(self, (1, count), np.float32, gpudata=addr_v)
         idx = B200Tensor(self, (1, count), np.int32, gpudata=addr_i)
         c0 = like.c0 if like.flat_of is None else 0
         idx[:] = idx + float(c0)                                   # local -> global column

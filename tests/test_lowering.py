@@ -4,7 +4,7 @@ for malformed programs is kept."""
 import numpy as np
 import pytest
 
-from tests.cases import cfg2, cfg4, standard_cases
+from tests.cases import cfg4, standard_cases
 from tests.dryrun import DryRunBackend
 
 
