@@ -1404,8 +1404,9 @@ class Planner(object):
             grid = ((nvec + BLOCK * unroll - 1) // (BLOCK * unroll), min(K, 65535), (K + 65534) // 65535)
         else:
             mode = 1 if st.flat else 0
-            if st.flat and self._lin is not None:
-                # flat view of a column shard: blocks must not straddle rows
+            if st.flat and self._lin is not None and "lin_0" in f.values:
+                # flat view of a column shard whose kernel needs element coordinates (random
+                # words): blocks must not straddle rows
                 cl = self._lin[2]
                 while unroll > 1 and cl % (BLOCK * unroll * V):
                     unroll //= 2

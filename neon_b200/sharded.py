@@ -157,6 +157,34 @@ class ShardedBackend(B200Backend):
         t = self.empty(ary.shape, dtype=dtype, name=name, parallel=True)
         return t.set(ary.astype(t.dtype))
 
+    # ---- temporaries of split statements: a part that spans the sharded columns is itself a shard
+    @staticmethod
+    def _sharded_columns(expr):
+        """Global column count of the sharded tensors under ``expr`` (None when there are none)."""
+        todo = [expr]
+        while todo:
+            node = todo.pop()
+            if isinstance(node, ShardedTensor):
+                return node.shape[1]
+            if type(node) is OpTreeNode:
+                todo.extend(n for n in (node[1], node[2]) if n is not None)
+        return None
+
+    def _materialise(self, expr, shape, stmts):
+        shape = tuple(shape)
+        if type(expr) is not tuple:
+            g = self._sharded_columns(expr)
+            if g is not None and g > 1 and len(shape) == 2 and shape[1] == g:
+                key = ("sharded",) + shape
+                used = self._temps_used.get(key, 0)
+                self._temps_used[key] = used + 1
+                pool = self._temps.setdefault(key, [])
+                while len(pool) <= used:
+                    pool.append(self.empty(shape, dtype=self.default_dtype, parallel=True))
+                stmts.append((pool[used], expr))
+                return pool[used]
+        return super(ShardedBackend, self)._materialise(expr, shape, stmts)
+
     # ---- one statement
     def _run_stack(self, out, stack):
         sharded = [s for s in stack if isinstance(s, ShardedTensor)]

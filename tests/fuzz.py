@@ -89,12 +89,22 @@ def host_arrays(spec):
     return arrays
 
 
-def build(be, spec, arrays, compute_dtype=None):
-    """Create the tensors on ``be`` and run the statement; returns the output tensor (full base)."""
+def shardable(spec, world):
+    """Statements a column-sharded backend can take as they are: no views, a column count the
+    ranks can share evenly."""
+    return (spec.shape[1] > 1 and spec.shape[1] % world == 0 and not spec.out_view
+            and all(view == "none" for _, _, view in spec.leaves))
+
+
+def build(be, spec, arrays, compute_dtype=None, full_kw=None):
+    """Create the tensors on ``be`` and run the statement; returns the output tensor (full base).
+    ``full_kw``: extra keywords for tensors that span all columns (e.g. parallel=True)."""
+    full_kw = full_kw or {}
     leaves = []
     for (shape, dtype, view), a in zip(spec.leaves, arrays):
         dt = compute_dtype if compute_dtype is not None else dtype
-        t = be.array(a, dtype=dt)
+        kw = full_kw if shape[1] == spec.shape[1] else {}
+        t = be.array(a, dtype=dt, **kw)
         if view == "slice":
             t = t[2:2 + shape[0], 1:1 + shape[1]]
         elif view == "trans":
@@ -172,6 +182,6 @@ def build(be, spec, arrays, compute_dtype=None):
         base = be.zeros((oshape[0] + 2, oshape[1] + 4), dtype=odt)
         base[1:1 + oshape[0], 3:3 + oshape[1]] = tree
         return base
-    out = be.zeros(oshape, dtype=odt)
+    out = be.zeros(oshape, dtype=odt, **(full_kw if oshape[1] == spec.shape[1] else {}))
     out[:] = tree
     return out

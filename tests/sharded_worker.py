@@ -77,6 +77,27 @@ def main():
     z64 = z_sharded.astype(np.float64)
     check_output("sharded total", total.get(), np.array([[z64.sum()]]), np.float32, scale=float(np.abs(z64).sum()))
     assert float(peak.get()[0, 0]) == float(np.abs(z_sharded).max())
+    # ---- seeded random statements (tests/fuzz.py) over column-sharded tensors
+    from tests import fuzz
+    ran = 0
+    for seed in range(400):
+        spec = fuzz.Spec(seed)
+        if not fuzz.shardable(spec, world):
+            continue
+        arrays = fuzz.host_arrays(spec)
+        got = fuzz.build(be, spec, arrays, full_kw={"parallel": True})
+        if got is None:
+            continue
+        with np.errstate(all="ignore"):
+            want = fuzz.build(OracleBackend(default_dtype=np.float64), spec, arrays, compute_dtype=np.float64)
+        g, w = got.get(), want.get()
+        ran += 1
+        if spec.red is not None and spec.red[0].startswith("arg"):
+            continue                                   # near-ties of computed values may pick other positions
+        if spec.red is not None and spec.red[0] == "min":
+            continue                                   # minima of differences are ill-conditioned in fp32
+        check_output("sharded fuzz seed %d" % seed, g, w, g.dtype)
+    assert ran > 40, ran
     be.host_barrier()
     if rank == 0:
         print("SHARDED-OK world=%d collectives=%d" % (world, be.collectives))

@@ -112,6 +112,22 @@ def _worker(rank, world, port, out):
     gathered = [None] * world
     dist.all_gather_object(gathered, [(p.kind, p.grid) for p in be.plans] + be.calls)
     assert all(g == gathered[0] for g in gathered)
+
+    # seeded random statements over sharded tensors plan on every rank (the GPU run checks values)
+    from tests import fuzz
+    be.array = lambda ary, dtype=None, parallel=False, **kw: be.empty(np.asarray(ary).shape, dtype, parallel=parallel)
+    planned = 0
+    for seed in range(400):
+        spec = fuzz.Spec(seed)
+        if not fuzz.shardable(spec, world):
+            continue
+        if spec.red is not None and spec.red[0].startswith("arg"):
+            continue                                # the merge of arg results reads device memory
+        be.plans, be.calls, be.passes = [], [], []
+        res = fuzz.build(be, spec, fuzz.host_arrays(spec), full_kw={"parallel": True})
+        assert res is None or be.plans or be.passes, seed   # (statements without a sharded operand run unsharded)
+        planned += 1
+    assert planned > 40
     out.put((rank, "ok"))
 
 
