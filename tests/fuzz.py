@@ -154,6 +154,8 @@ def build(be, spec, arrays, compute_dtype=None, full_kw=None):
             return be.maximum(a, b)
         return be.minimum(a, b)
 
+    if not leaves:
+        return None                      # a tree of constants only: nothing to compare
     tree = ev(spec.tree)
     if isinstance(tree, float):
         tree = leaves[0] * 0.0 + tree if leaves else None
