@@ -579,3 +579,41 @@ def test_more_than_two_to_the_32_elements(b200):
     ur = sround.rng_bits_pair(key[0], key[1], last)
     want = sround.store(vals, np.float16, True, ur)
     assert np.array_equal(z[rows - 1:rows, cols - 16:cols].get().ravel().view(np.uint16), want.view(np.uint16))
+
+
+def test_stochastic_rounding_bit_exact_over_random_shapes(b200):
+    """The stored bits are the restated rule applied to the random word of each element's
+    row-major index, whatever the shape (vector width, scalar tails), the kernel (flat, 2-d with a
+    broadcast operand, store into a view), the storage type and the number of kept bits."""
+    be = b200
+    rng = np.random.RandomState(0)
+    dims = (1, 2, 3, 7, 8, 9, 15, 16, 17, 31, 33, 64, 100, 127, 129, 255, 257, 1000, 1024, 4099)
+    try:
+        import ml_dtypes
+        bf = ml_dtypes.bfloat16
+    except ImportError:
+        bf = None
+    for trial in range(90):
+        R, C = int(rng.choice(dims)), int(rng.choice(dims))
+        odt = (bf or np.float16) if trial % 5 == 0 else (np.float16, np.float32)[trial % 2]
+        bits = (True, 3, 7, 10, 12)[trial % 5]
+        mode = trial % 3                      # 0 flat, 1 broadcast column operand, 2 output view
+        xh = rng.uniform(-4, 4, (R, C)).astype(np.float16)
+        x = be.array(xh, dtype=np.float16)
+        z = be.zeros((R + 3, C + 5), dtype=odt)[1:1 + R, 2:2 + C] if mode == 2 else be.empty((R, C), dtype=odt)
+        z.rounding = bits
+        seed, launch = be.rng_get_state()[1]
+        if mode == 1:
+            ch = rng.uniform(-1, 1, (R, 1)).astype(np.float16).astype(np.float32)
+            z[:] = 0.3330078125 * x + be.array(ch)
+            val = (np.float32(0.3330078125) * xh.astype(np.float32) + ch).astype(np.float32)
+        else:
+            z[:] = x * 1.0009765625
+            val = (xh.astype(np.float32) * np.float32(1.0009765625)).astype(np.float32)
+        key = sround.launch_key(int(seed), int(launch))
+        idx = np.arange(R * C, dtype=np.uint64)
+        two_byte = np.dtype(odt).itemsize == 2
+        ur = (sround.rng_bits_pair if two_byte else sround.rng_bits)(key[0], key[1], idx).reshape(R, C)
+        want = sround.store(val, odt, bits, ur)
+        got = z.get()
+        assert np.array_equal(got.view(np.uint8), want.view(np.uint8)), (trial, (R, C), np.dtype(odt).name, bits, mode)
