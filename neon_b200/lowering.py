@@ -188,9 +188,10 @@ def program_key(stack):
     for s in stack:
         if isinstance(s, Tensor):
             ix = seen.setdefault(id(s), len(seen))
-            key.append((ix, s.dtype.str, s.shape, s.strides, s.ptr & 15,
-                        s.take_array[1] if s.take_array else None,
-                        s is not out and shares_memory(s, out)))
+            pk = getattr(s, "_plan_key", None)
+            if pk is None:
+                pk = (s.dtype.str, s.shape, s.strides, s.ptr & 15, s.take_array[1] if s.take_array else None)
+            key.append((ix, pk, s is not out and shares_memory(s, out)))
         elif type(s) is dict:
             idx = s.get("idx")
             key.append((s["op"], s.get("axis"), None if idx is None else seen.setdefault(id(idx), len(seen))))

@@ -106,6 +106,9 @@ class B200Tensor(Tensor):
         else:
             self._block = _block
             self.gpudata = int(gpudata)
+        # what the plan cache needs to know about this tensor (none of it changes afterwards)
+        self._plan_key = (dtype.str, self.shape, self.strides, self.gpudata & 15,
+                          take_array[1] if take_array else None)
 
     # ---- description
     def __str__(self):
