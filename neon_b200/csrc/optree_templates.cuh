@@ -1032,26 +1032,30 @@ DEV void rr_combine(const RowCtx& cx, float* a, int* ai, float (*sv)[THREADS / 3
     }
     if constexpr (C > 1) {
         cluster_barrier_warp0_releases();
-        if (warp == 0) {
+        // every warp folds the C block results for itself (same values, same order) and leaves
+        // them in res: no hand-over between warps, so no block barrier.  res of this pass is next
+        // written one row later, after a cluster barrier every warp has passed since reading it.
 #pragma unroll
-            for (int r = 0; r < NR; ++r) {
-                const u32* entry = mine + (r * C + (lane < C ? lane : 0)) * 2;
-                a[r] = __uint_as_float(entry[0]);
-                ai[r] = red_is_arg(S::op(r)) ? (int)entry[1] : -1;
+        for (int r = 0; r < NR; ++r) {
+            const u32* entry = mine + (r * C + (lane < C ? lane : 0)) * 2;
+            a[r] = __uint_as_float(entry[0]);
+            ai[r] = red_is_arg(S::op(r)) ? (int)entry[1] : -1;
 #pragma unroll
-                for (int o = C / 2; o > 0; o >>= 1) {
-                    float b = __shfl_xor_sync(0xffffffffu, a[r], o);
-                    int bi = red_is_arg(S::op(r)) ? __shfl_xor_sync(0xffffffffu, ai[r], o) : 0;
-                    red_merge(S::op(r), a[r], ai[r], b, bi);
-                }
+            for (int o = C / 2; o > 0; o >>= 1) {
+                float b = __shfl_xor_sync(0xffffffffu, a[r], o);
+                int bi = red_is_arg(S::op(r)) ? __shfl_xor_sync(0xffffffffu, ai[r], o) : 0;
+                red_merge(S::op(r), a[r], ai[r], b, bi);
             }
+            if (lane == 0) res[r] = red_is_arg(S::op(r)) ? (u32)ai[r] : __float_as_uint(a[r]);
         }
-    }
-    if (threadIdx.x == 0) {
+        __syncwarp();
+    } else {
+        if (threadIdx.x == 0) {
 #pragma unroll
-        for (int r = 0; r < NR; ++r) res[r] = red_is_arg(S::op(r)) ? (u32)ai[r] : __float_as_uint(a[r]);
+            for (int r = 0; r < NR; ++r) res[r] = red_is_arg(S::op(r)) ? (u32)ai[r] : __float_as_uint(a[r]);
+        }
+        __syncthreads();
     }
-    __syncthreads();
 }
 
 }  // namespace b200
