@@ -5,7 +5,9 @@
  *   1. sums 1e6 floats with the fixed-function reduction (caller scratch) and
  *      with the no-allocation variant, twice, and compares with the host sum;
  *   2. instantiates a kernel from source at run time (the path the op-tree
- *      engine uses: NVRTC + cache + launch with one by-value parameter block).
+ *      engine uses: NVRTC + cache + launch with one by-value parameter block);
+ *   3. transposes a 300 x 500 float matrix with b200_dimshuffle, takes the log2
+ *      histogram of its values and runs one Kahan accumulation step on it.
  * Exit status 0 = all checks passed.
  */
 #include "b200ew.h"
@@ -81,6 +83,41 @@ int main(int argc, char **argv) {
     CHECK(b200_reduce_full(x, B200_F32, n, B200_SUM, 0, out, scratch, 0));
     CHECK(b200_memcpy_d2h(&got, out, 4, 0, 1));
     if (fabs(got - 2.0 * want) > 1e-5 * n * 0.5) { fprintf(stderr, "after scale: %g vs %g\n", got, 2.0 * want); return 1; }
+
+    /* 3. fixed-function kernels on a 300 x 500 matrix m[r][c] = r + c / 1000 */
+    {
+        enum { R = 300, C = 500 };
+        float *m = (float *)malloc(R * C * sizeof(float)), *t = (float *)malloc(R * C * sizeof(float));
+        for (int r = 0; r < R; ++r) for (int c = 0; c < C; ++c) m[r * C + c] = (float)r + (float)c / 1000.0f;
+        uint64_t dm = 0, dt = 0, dh = 0, dc = 0;
+        CHECK(b200_malloc(R * C * 4, &dm));
+        CHECK(b200_malloc(R * C * 4, &dt));
+        CHECK(b200_malloc(64 * 4, &dh));
+        CHECK(b200_malloc(R * C * 4, &dc));
+        CHECK(b200_memcpy_h2d(dm, m, R * C * 4, 0, 1));
+        /* output (C, R): output dimension 0 walks the input's columns (stride 1), dimension 1 its rows */
+        const int64_t shape[2] = {C, R}, dst_strides[2] = {R, 1}, src_strides[2] = {1, C};
+        CHECK(b200_dimshuffle(dt, dm, 4, 2, shape, dst_strides, src_strides, 0));
+        CHECK(b200_memcpy_d2h(t, dt, R * C * 4, 0, 1));
+        for (int r = 0; r < R; ++r) for (int c = 0; c < C; ++c)
+            if (t[c * R + r] != m[r * C + c]) { fprintf(stderr, "dimshuffle at (%d, %d)\n", r, c); return 1; }
+        if (b200_dimshuffle(dm, dm, 4, 2, shape, dst_strides, src_strides, 0) != B200_ERR_INVALID) return 1;
+        /* histogram: values in [2^k - .., ..) -> bin k + 48; row 0 (values below 0.5) lands in low bins */
+        int hist[64], total = 0, top = 0;
+        CHECK(b200_log2_hist(dm, B200_F32, R * C, dh, 64, -48, 0));
+        CHECK(b200_memcpy_d2h(hist, dh, sizeof hist, 0, 1));
+        for (int b = 0; b < 64; ++b) total += hist[b];
+        for (int b = 48 + 8; b < 64; ++b) top += hist[b];       /* round(log2 x) >= 8: x >= 2^7.5 = 181.02 */
+        if (total != R * C || top != (R - 182) * C + 480) { fprintf(stderr, "hist: %d %d\n", total, top); return 1; }
+        /* Kahan step: sum = m, cmp = 0, add = m  ->  sum = 2 m exactly, cmp = 0 */
+        CHECK(b200_memset(dc, 0, 4, R * C, 0));
+        CHECK(b200_memcpy_d2d(dt, dm, R * C * 4, 0));
+        CHECK(b200_compensated_sum(dm, dc, dt, B200_F32, R * C, 1.0f, 1.0f, 0, 0));
+        CHECK(b200_memcpy_d2h(t, dm, R * C * 4, 0, 1));
+        for (int i = 0; i < R * C; ++i) if (t[i] != 2.0f * m[i]) { fprintf(stderr, "kahan at %d\n", i); return 1; }
+        CHECK(b200_free(dm)); CHECK(b200_free(dt)); CHECK(b200_free(dh)); CHECK(b200_free(dc));
+        free(m); free(t);
+    }
 
     CHECK(b200_free(x));
     CHECK(b200_free(out));
