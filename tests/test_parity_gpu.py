@@ -617,3 +617,60 @@ def test_stochastic_rounding_bit_exact_over_random_shapes(b200):
         want = sround.store(val, odt, bits, ur)
         got = z.get()
         assert np.array_equal(got.view(np.uint8), want.view(np.uint8)), (trial, (R, C), np.dtype(odt).name, bits, mode)
+
+
+def test_random_views_read_and_write_like_numpy(b200):
+    """Slices with steps, integer subscripts (kept as extent-1 axes, nervanagpu.py:262-275),
+    negative indices, transposes of views and reshapes: ``get`` returns what numpy indexing
+    returns, and assigning through the view changes exactly the viewed elements."""
+    be = b200
+    rng = np.random.RandomState(42)
+    for trial in range(60):
+        R, C = int(rng.randint(2, 70)), int(rng.randint(2, 90))
+        dtype = (np.float32, np.float16, np.int32)[trial % 3]
+        h = (rng.randn(R, C) * 8).astype(dtype)
+        t = be.array(h, dtype=dtype)
+
+        def rand_slice(n):
+            a, b = sorted(rng.randint(0, n + 1, 2))
+            if a == b:
+                b = min(n, a + 1)
+                a = b - 1
+            step = int(rng.choice([1, 1, 2, 3]))
+            start = int(a) - n if (a > 0 and rng.rand() < 0.2) else int(a)      # sometimes counted from the end
+            return slice(start, int(b), step)
+        kind = trial % 5
+        if kind == 0:
+            key = (rand_slice(R), rand_slice(C))
+        elif kind == 1:
+            key = (int(rng.randint(-R, R)), rand_slice(C))
+        elif kind == 2:
+            key = (rand_slice(R), int(rng.randint(-C, C)))
+        elif kind == 3:
+            key = (rand_slice(R),)
+        else:
+            key = (Ellipsis, rand_slice(C))
+        view = t[key]
+        want = h[key]
+        if want.ndim == 1:                    # an integer subscript keeps its axis with extent 1
+            want = want.reshape((1, -1)) if isinstance(key[0], (int, np.integer)) else want.reshape((-1, 1))
+        assert tuple(view.shape) == want.shape, (trial, key, view.shape, want.shape)
+        assert np.array_equal(view.get(), want), (trial, key)
+        assert np.array_equal(view.T.get(), want.T), (trial, key)
+        # write through the view
+        new = (rng.randn(*want.shape) * 8).astype(dtype)
+        view[:] = be.array(new, dtype=dtype)
+        ref = h.copy()
+        ref[key] = new.reshape(ref[key].shape)
+        assert np.array_equal(t.get(), ref), (trial, key)
+        view[:] = 3
+        ref[key] = 3
+        assert np.array_equal(t.get(), ref), (trial, key)
+    # reshape of a contiguous tensor and of a row slice; refusal for a column slice
+    h = rng.randn(12, 10).astype(np.float32)
+    t = be.array(h)
+    assert np.array_equal(t.reshape((20, 6)).get(), h.reshape(20, 6))
+    assert np.array_equal(t[2:8].reshape((6, 10)).get(), h[2:8])
+    assert np.array_equal(t[2:8].reshape((30, 2)).get(), h[2:8].reshape(30, 2))
+    with pytest.raises(ValueError):
+        t[:, 2:8].reshape((36, 2))
