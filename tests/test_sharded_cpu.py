@@ -131,9 +131,9 @@ def _worker(rank, world, port, out):
     out.put((rank, "ok"))
 
 
-@pytest.mark.timeout(180)
-def test_two_rank_host_logic_over_gloo():
-    world = 2
+@pytest.mark.timeout(300)
+@pytest.mark.parametrize("world", [2, 4])
+def test_multi_rank_host_logic_over_gloo(world):
     port = _free_port()
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
@@ -144,4 +144,4 @@ def test_two_rank_host_logic_over_gloo():
         p.join(150)
     assert all(p.exitcode == 0 for p in procs), [p.exitcode for p in procs]
     got = sorted(q.get(timeout=5) for _ in range(world))
-    assert got == [(0, "ok"), (1, "ok")]
+    assert got == [(r, "ok") for r in range(world)]
