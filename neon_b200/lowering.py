@@ -628,6 +628,14 @@ class Planner(object):
         V = self._pick_v(lane_ops, N, True, extra=extra_ops)
         if V == 1 or N % V:
             return None
+        # the staging copies are cp.async.bulk: source, destination and byte count must be
+        # multiples of 16.  Slices and chunks start and end on V-element boundaries, so every
+        # staged operand needs V elements to be a whole number of 16-byte units, a 16-byte
+        # aligned base and a row pitch that keeps rows 16-byte aligned.
+        for o in staged.values():
+            isz = DT_SIZE[o.dt]
+            if (V * isz) % 16 or o.ptr % 16 or (o._frame_strides[0] * isz) % 16 or (N * isz) % 16:
+                return None
         nvec = N // V
         row_bytes = sum(DT_SIZE[o.dt] for o in staged.values())          # per element
         C = None

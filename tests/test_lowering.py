@@ -63,6 +63,32 @@ def test_rows_that_fit_cluster_shared_memory_become_one_row_resident_kernel():
     assert "rowres" not in [p.kind for p in be.passes]
 
 
+def test_rows_that_would_stage_on_8_byte_boundaries_are_not_row_resident():
+    """The row-resident kernel stages rows with bulk copies, which need 16-byte aligned
+    addresses and sizes: fp32 rows of 4n+2 elements and fp16 rows of 8n+4 elements put
+    every other row 8 bytes off, so those statements take the multi-pass kernels."""
+    be = DryRunBackend()
+    be.compile = False
+    for shape, dt in (((128, 4098), np.float32), ((128, 8196), np.float16), ((128, 1026), np.float32),
+                      ((128, 2052), np.float16)):
+        x, y = be.empty(shape, dt), be.empty(shape, dt)
+        be.passes = []
+        y[:] = (x - be.mean(x, axis=1)) / (be.std(x, axis=1) + 1e-3)
+        assert "rowres" not in [p.kind for p in be.passes], shape
+    # the same row lengths rounded to whole 16-byte units do stay resident
+    for shape, dt in (((128, 4096), np.float32), ((128, 8192), np.float16)):
+        x, y = be.empty(shape, dt), be.empty(shape, dt)
+        be.passes = []
+        y[:] = (x - be.mean(x, axis=1)) / (be.std(x, axis=1) + 1e-3)
+        assert [p.kind for p in be.passes] == ["rowres"], shape
+    # a view that starts 8 bytes into a 16-byte unit
+    base = be.empty((128, 4100), np.float32)
+    x, y = base[:, 2:4098], be.empty((128, 4096), np.float32)
+    be.passes = []
+    y[:] = (x - be.mean(x, axis=1)) / (be.std(x, axis=1) + 1e-3)
+    assert "rowres" not in [p.kind for p in be.passes]
+
+
 def test_whole_tensor_reduction_is_one_flat_pass():
     be = DryRunBackend()
     be.compile = False

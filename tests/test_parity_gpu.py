@@ -97,6 +97,25 @@ def test_row_resident_cluster_kernel_matches_checker(case, b200):
     _compare(case, got, _oracle64(case))
 
 
+@pytest.mark.parametrize("shape,dtype", [((128, 4098), np.float32), ((128, 8196), np.float16),
+                                         ((128, 1026), np.float32), ((128, 2052), np.float16)])
+def test_rows_off_16_byte_boundaries_take_the_multi_pass_kernels(shape, dtype, b200):
+    """Row lengths that would put staged rows on 8-byte boundaries (bulk copies need 16) must
+    not reach the row-resident kernel, and must still give the right answer."""
+    def run(be, t):
+        x = t["x"]
+        t["out"][:] = (x - be.mean(x, axis=1)) / (be.std(x, axis=1) + 1e-3)
+    case = cases.Case("standardise_rows_%dx%d_%s" % (shape + (np.dtype(dtype).name,)),
+                      lambda rng: {"x": rng.uniform(-1, 1, shape).astype(dtype)},
+                      {"out": (shape, np.float32)}, run)
+    b200.launch_log = []
+    got = cases.run_case(b200, case)
+    kinds = [k for k, _ in b200.launch_log]
+    b200.launch_log = None
+    assert "rowres" not in kinds, kinds
+    _compare(case, got, _oracle64(case))
+
+
 def test_bounded_wait_reports_instead_of_hanging():
     """The one software wait in the kernels (a block waiting for its TMA-staged row slice)
     has a time limit.  Announce 16 bytes that never arrive, give it 20 ms: the kernel must
