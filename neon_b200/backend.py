@@ -86,6 +86,7 @@ class B200Backend(OpTreeBackend):
                  scratch_size=0, hist_bins=64, hist_offset=-48, compat_mode=None,
                  enable_winograd=True, cache_dir=None, num_devices=None, max_devices=None,
                  precise_math=False):
+        self.enable_winograd = enable_winograd        # read by neon's fixtures; no convolutions here
         if default_dtype not in (np.float16, np.float32) and np.dtype(default_dtype).name != "bfloat16":
             raise ValueError("Default data type for the b200 backend must be float16 or 32")
         if rt.device_count() <= int(device_id):
@@ -155,6 +156,10 @@ class B200Backend(OpTreeBackend):
         self.rng.set_state(save)
         self.init_rng_state_dev = (dev_seed, 0)
         rt.rng_set_state(self.init_rng_state_dev)
+        # one device context per backend, its generator always live: the bookkeeping NervanaGPU
+        # exposes per CUDA context (nervanagpu.py:901-941), which neon's RNG tests look at
+        self.context_rand_state_map = {self.device_id: self.init_rng_state_dev}
+        self.context_rand_state_alive = {self.device_id: True}
         return self.rng
 
     def rng_reset(self):
@@ -464,6 +469,34 @@ class B200Backend(OpTreeBackend):
 
     def make_binary_mask(self, out, keepthresh=0.5):
         self.dropout(keep=keepthresh, out=out)
+
+    def binarize(self, ary, out, stochastic=True):
+        """out = +1 / -1 from ary (neon/backends/nervanagpu.py:3120-3136): the sign of ary, or,
+        stochastically, +1 with probability clip((ary + 1) / 2, 0, 1).  One fused statement."""
+        if stochastic:
+            p = self.clip((ary + 1) / 2.0, 0, 1)
+            out[:] = 2 * self.less_equal(self.rand(), p) - 1
+        else:
+            out[:] = 2 * self.greater_equal(ary, 0) - 1
+        return out
+
+    def shift(self, ary, shift_ary, value=True, out=None):
+        """out = ary scaled by a power of two taken from shift_ary (nervanagpu.py:1863-1894,
+        kernel text backends/kernels/cuda/binary.py:174-227): with ``value`` the power of two
+        nearest to |shift_ary| in the log domain, carrying its sign (0 gives 0); otherwise
+        2**shift_ary for integer-valued shift_ary.  shift_ary broadcasts like any operand."""
+        if not hasattr(ary, "shape"):
+            ary = self.array(np.array(ary))
+        if not hasattr(shift_ary, "shape"):
+            shift_ary = self.array(np.array(shift_ary))
+        if out is None:
+            out = self.empty_like(ary)
+        if value:
+            e = OpTreeNode.build("round", self.log2(self.absolute(shift_ary)), None)
+            out[:] = ary * self.sgn(shift_ary) * self.exp2(e)
+        else:
+            out[:] = ary * self.exp2(shift_ary)
+        return out
 
     def fill_normal(self, ary, mean=0, stdv=1):
         ary[:] = (self.rng.standard_normal(ary.shape) * stdv + mean).astype(ary.dtype)

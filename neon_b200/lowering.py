@@ -55,6 +55,7 @@ UNARY_C = {
     "tanh": "tanhf({0})",
     "tanh2": "((exp2f(2.0f * {0}) - 1.0f) / (exp2f(2.0f * {0}) + 1.0f))",
     "finite": "(isfinite({0}) ? 1.0f : 0.0f)",
+    "round": "roundf({0})",
 }
 BINARY_C = {
     "add": "({0} + {1})", "sub": "({0} - {1})", "mul": "({0} * {1})", "div": "({0} / {1})",
@@ -85,6 +86,7 @@ UNARY_HOST = {
     "sig2": lambda a: _f(1) / (_f(1) + np.exp2(-a)), "tanh": np.tanh,
     "tanh2": lambda a: (np.exp2(_f(2) * a) - _f(1)) / (np.exp2(_f(2) * a) + _f(1)),
     "finite": lambda a: _f(np.isfinite(a)),
+    "round": lambda a: np.where(a >= 0, np.floor(a + _f(0.5)), np.ceil(a - _f(0.5))).astype(np.float32),
 }
 BINARY_HOST = {
     "add": lambda a, b: a + b, "sub": lambda a, b: a - b, "mul": lambda a, b: a * b,

@@ -9,22 +9,58 @@ line choice work (neon keeps its backends in a name -> class registry filled by
     plugin.register()
     be = neon.backends.gen_backend(backend='b200', rng_seed=0, batch_size=128)
 
-``register`` also routes ``Autodiff`` as neon's layers see it (``BatchNormAutodiff``,
-neon/layers/layer.py:2583-2651) to this package's implementation when the backend is
-this one: neon's class only accepts neon's own op-tree node type.
+What ``register`` does besides the registry entry:
+
+* neon code tests ``isinstance(x, neon.backends.backend.Tensor)`` in a few places
+  (layer configuration, initializers, the helpers of neon's tests), so this
+  package's tensor base class is re-parented onto neon's ``Tensor``;
+* ``Autodiff`` as neon's layers see it (``BatchNormAutodiff``,
+  neon/layers/layer.py:2583-2651) is routed to this package's implementation when
+  the backend is this one: neon's class only accepts neon's own op-tree node type;
+* with ``as_gpu=True`` the backend also answers to the name ``'gpu'`` and, where
+  neon's own ``nervanagpu`` module cannot be imported (it needs pycuda), a module
+  of that name is provided whose ``NervanaGPU`` / ``GPUTensor`` are this package's
+  classes.  That is how neon's own test files, which ask for ``'gpu'``, are run
+  against this backend.
 """
 
+import sys
+import types
 
-def register():
+
+def register(as_gpu=False, backend_cls=None):
     from neon.backends.backend import Backend
-    from .backend import B200Backend
-    Backend.backends["b200"] = B200Backend
+    if backend_cls is None:
+        from .backend import B200Backend as backend_cls
+    _adopt_tensor_base()
+    Backend.backends["b200"] = backend_cls
     _route_autodiff()
-    return B200Backend
+    if as_gpu:
+        Backend.backends["gpu"] = backend_cls
+        try:
+            from neon.backends import nervanagpu                      # noqa: F401
+        except ImportError:
+            mod = types.ModuleType("neon.backends.nervanagpu")
+            mod.NervanaGPU = backend_cls
+            mod.GPUTensor = getattr(backend_cls, "tensor_cls", None)
+            sys.modules["neon.backends.nervanagpu"] = mod
+            import neon.backends
+            neon.backends.nervanagpu = mod
+    return backend_cls
+
+
+def _adopt_tensor_base():
+    """Make neon's Tensor a base class of this package's Tensor (after its own operator
+    mix-in, so arithmetic keeps building this package's op-tree nodes)."""
+    from neon.backends.backend import Tensor as NeonTensor
+    from .optree import Tensor, _Operators
+    if NeonTensor not in Tensor.__mro__:
+        Tensor.__bases__ = (_Operators, NeonTensor)
 
 
 def _route_autodiff():
     import neon.backends
+    import neon.backends.autodiff
     import neon.layers.layer as layer_module
     from .autodiff import autodiff
     from .optree import OpTreeBackend
@@ -38,4 +74,5 @@ def _route_autodiff():
         return theirs(op_tree, be, next_error)
     Autodiff._b200_router = True
     neon.backends.Autodiff = Autodiff
+    neon.backends.autodiff.Autodiff = Autodiff
     layer_module.Autodiff = Autodiff

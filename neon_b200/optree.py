@@ -22,11 +22,13 @@ import numpy as np
 
 
 class OpCollection(object):
-    """Names of the operations an op-tree may hold (backend.py:30-42)."""
+    """Names of the operations an op-tree may hold (backend.py:30-42), plus ``round``
+    (C's roundf, halves away from zero): the rounding neon's GPU ``shift`` kernel applies
+    to log2|b| (backends/kernels/cuda/binary.py:184), used by ``B200Backend.shift``."""
     zero_operand_ops = {"rand", "onehot"}
     unary_ops = {"finite", "neg", "abs", "sgn", "sqrt", "sqr", "exp", "log",
                  "exp2", "log2", "sig", "sig2", "tanh", "tanh2", "transpose",
-                 "safelog", "rint", "binarize"}
+                 "safelog", "rint", "binarize", "round"}
     binary_ops = {"assign", "add", "sub", "mul", "div", "eq", "ne", "lt", "le",
                   "gt", "ge", "pow", "minimum", "maximum", "dot", "shift"}
     reduction_ops = {"sum", "max", "min", "argmax", "argmin"}

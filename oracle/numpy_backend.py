@@ -87,6 +87,8 @@ NUMPY_OPS = {
 # so finite() can be checked too.  Not part of nervanacpu.py.
 GPU_ONLY_OPS = {
     "finite": lambda x: np.isfinite(x).astype(np.float32),
+    # C's roundf as the GPU shift kernel uses it (kernels/cuda/binary.py:184)
+    "round": lambda x: np.where(x >= 0, np.floor(x + 0.5), np.ceil(x - 0.5)),
 }
 
 

@@ -1,27 +1,30 @@
 """
 Generate tests/golden/optree_golden.npz from the real neon NervanaCPU backend.
 
-Run where a neon source checkout is available (it cannot run on a machine
-without one, which is why the outputs are committed):
+Run where a neon source checkout is available (the outputs are committed so that
+the comparisons also work on a machine without one):
 
     python tests/golden/make_golden.py [/path/to/neon/checkout]
 
 (default: $NEON_REFERENCE, else a directory named "reference" beside this repository)
 
-neon is imported unmodified from the checkout.  Three modules it wants are not
-installed and have nothing to do with the numpy backend, so stand-ins are put in
-``sys.modules`` before the import: ``future`` (py2/3 helpers), ``appdirs``
-(cache-directory lookup) and the build-generated ``neon.version``.
+neon is imported unmodified from the checkout (oracle/neon_ref.py supplies stand-ins
+for three modules it wants that are not installed and have nothing to do with the
+numpy backend).
 
 For every case of ``tests/cases.py::standard_cases`` the script runs the case on
 ``NervanaCPU`` with float32 and with float64 tensors and stores a fingerprint of
 each resulting tensor (the whole array when small, else a strided sample plus
 float64 sum and abs-sum) under ``<case>/<dtype>/<tensor>/<field>``.
+
+A second file, ``neon_callers_golden.npz``, holds the float64 NervanaCPU results of
+``tests/neon_cases.py`` -- neon's own optimizers, layers, costs and
+``compound_fprop_bn`` / ``compound_bprop_bn`` run on seeded inputs -- under
+``<case>/<array>/<field>``.
 """
 
 import os
 import sys
-import types
 
 import numpy as np
 
@@ -29,31 +32,10 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, os.path.dirname(os.path.dirname(HERE)))
 
 
-def import_reference_cpu(path):
-    """Import neon's NervanaCPU from the checkout at ``path``."""
-    def mod(name, **attrs):
-        m = types.ModuleType(name)
-        m.__dict__.update(attrs)
-        sys.modules[name] = m
-        return m
-
-    def with_metaclass(meta, *bases):
-        return meta("_with_metaclass_base", bases or (object,), {})
-
-    if "future" not in sys.modules:
-        fut = mod("future")
-        fut.utils = mod("future.utils", with_metaclass=with_metaclass, native_str=str,
-                        native=lambda x: x)
-        fut.standard_library = mod("future.standard_library", install_aliases=lambda: None)
-        fut.builtins = mod("future.builtins")
-    if "appdirs" not in sys.modules:
-        mod("appdirs", user_cache_dir=lambda *a, **k: "/tmp/neon_cache",
-            user_data_dir=lambda *a, **k: "/tmp/neon_data")
-    mod("neon.version", VERSION="reference-checkout", SHORT_VERSION="ref")
-    if path not in sys.path:
-        sys.path.insert(0, path)
-    from neon.backends.nervanacpu import NervanaCPU
-    return NervanaCPU
+def import_reference_cpu(path=None):
+    """Import neon's NervanaCPU from the checkout at ``path`` (see oracle/neon_ref.py)."""
+    from oracle import neon_ref
+    return neon_ref.import_reference_cpu(path)
 
 
 def main():
@@ -74,6 +56,21 @@ def main():
                 for field, val in summarize(arr).items():
                     store["%s/%s/%s/%s" % (case.name, np.dtype(dt).name, k, field)] = val
     out = os.path.join(HERE, "optree_golden.npz")
+    np.savez_compressed(out, **store)
+    print("wrote %s: %d entries, %.1f KiB" % (out, len(store), os.path.getsize(out) / 1024.))
+
+    # neon's own optimizers, layers, costs and batch-norm entry points driving NervanaCPU (float64)
+    from oracle.neon_ref import numpy_compat
+    from tests.neon_cases import neon_caller_cases
+    store = {}
+    with numpy_compat():
+        for name, run in neon_caller_cases().items():
+            with np.errstate(all="ignore"):
+                res = run(NervanaCPU(default_dtype=np.float64, rng_seed=0))
+            for k, arr in res.items():
+                for field, val in summarize(arr).items():
+                    store["%s/%s/%s" % (name, k, field)] = val
+    out = os.path.join(HERE, "neon_callers_golden.npz")
     np.savez_compressed(out, **store)
     print("wrote %s: %d entries, %.1f KiB" % (out, len(store), os.path.getsize(out) / 1024.))
 

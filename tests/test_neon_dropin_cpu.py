@@ -11,11 +11,10 @@ import os
 import numpy as np
 import pytest
 
-# a neon checkout: $NEON_REFERENCE, else a directory named "reference" beside this repository
-REFERENCE = os.environ.get("NEON_REFERENCE") or os.path.join(
-    os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__)))), "reference")
-pytestmark = pytest.mark.skipif(not os.path.isdir(os.path.join(REFERENCE, "neon", "backends")),
-                                reason="no neon checkout on this machine")
+from oracle import neon_ref
+
+REFERENCE = neon_ref.find_reference() or ""
+pytestmark = pytest.mark.skipif(not REFERENCE, reason="no neon source tree on this machine")
 
 
 @pytest.fixture(scope="module")

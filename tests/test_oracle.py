@@ -8,9 +8,9 @@ from oracle.numpy_backend import OracleBackend
 from tests.cases import run_case, standard_cases, summarize
 
 CASES = standard_cases()
-# a neon checkout: $NEON_REFERENCE, else a directory named "reference" beside this repository
-REFERENCE = os.environ.get("NEON_REFERENCE") or os.path.join(
-    os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__)))), "reference")
+from oracle import neon_ref
+
+REFERENCE = neon_ref.find_reference() or ""
 
 
 def _check(fingerprint, golden, prefix):
@@ -36,8 +36,7 @@ def test_oracle_reproduces_reference_golden(case, golden):
             _check(summarize(arr), golden, "%s/%s/%s" % (case.name, np.dtype(dt).name, k))
 
 
-@pytest.mark.skipif(not os.path.isdir(os.path.join(REFERENCE, "neon", "backends")),
-                    reason="no neon checkout on this machine")
+@pytest.mark.skipif(not REFERENCE, reason="no neon source tree on this machine")
 def test_oracle_matches_live_reference_bit_for_bit():
     from tests.golden.make_golden import import_reference_cpu
     NervanaCPU = import_reference_cpu(REFERENCE)
