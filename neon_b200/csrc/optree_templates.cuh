@@ -42,7 +42,9 @@ typedef unsigned char u8;
 namespace b200 {
 
 enum { F32 = 0, F16 = 1, BF16 = 2, I32 = 3, U32 = 4, I16 = 5, U16 = 6, I8 = 7, U8 = 8 };
-enum { OP_SUM = 0, OP_MAX = 1, OP_MIN = 2, OP_ARGMAX = 3, OP_ARGMIN = 4 };
+// OP_MOM_MEAN / OP_MOM_M2 are a PAIR of neighbouring reduction slots (r, r + 1) that together
+// carry the first two moments of one expression: see "moments" below.
+enum { OP_SUM = 0, OP_MAX = 1, OP_MIN = 2, OP_ARGMAX = 3, OP_ARGMIN = 4, OP_MOM_MEAN = 5, OP_MOM_M2 = 6 };
 
 template <int DT> struct dt_size { enum { value = (DT == F32 || DT == I32 || DT == U32) ? 4 : (DT == I8 || DT == U8) ? 1 : 2 }; };
 
@@ -391,7 +393,9 @@ template <int DT> DEV void st_index(u64 base, i64 off, int idx) {
 }
 
 // ------------------------------------------------------------------ reduction algebra
-DEV float red_init(int op) { return op == OP_SUM ? 0.f : (op == OP_MAX || op == OP_ARGMAX) ? -B200_FLT_MAX : B200_FLT_MAX; }
+DEV float red_init(int op) { return (op == OP_SUM || op >= OP_MOM_MEAN) ? 0.f : (op == OP_MAX || op == OP_ARGMAX) ? -B200_FLT_MAX : B200_FLT_MAX; }
+DEV int red_init_idx(int op) { return op >= OP_MOM_MEAN ? 0 : -1; }
+// the slot carries an int next to its value: the index of an arg reduction, the count of a moments pair
 DEV bool red_is_arg(int op) { return op >= OP_ARGMAX; }
 // fold one element in; strict comparison keeps the first index a thread sees
 DEV void red_acc(int op, float& a, int& ai, float v, int vi) {
@@ -414,6 +418,98 @@ DEV void red_merge(int op, float& a, int& ai, float b, int bi) {
     }
 }
 
+// ------------------------------------------------------------------ moments
+// sum(e) and sum((e - m)^2) of one expression e in ONE pass over the data, for statements such
+// as a variance whose second sum is centred on a value m that itself needs the first sum (the
+// reference makes two passes, cuda_templates.py "loop" stage per reduction).  Slots r and r + 1
+// of a pass hold the pair.
+//   while a thread accumulates:  acc[r][i]   sum of (e - K) over the lane's elements
+//                                acc[r+1][i] sum of (e - K)^2
+//                                acci[r][0]  elements seen so far, acci[r+1][0] bits of K,
+//     K = the first element the thread saw (a shift that keeps the squares small);
+//   from the thread level up:    a[r] mean, ai[r] count, a[r+1] sum of squared deviations from
+//     that mean; two such triples merge exactly (Chan, Golub, LeVeque 1979):
+//     mean = mean_a + d * n_b / n,  M2 = M2_a + M2_b + d^2 * n_a * n_b / n,  d = mean_b - mean_a;
+//   before generated code sees them (finish_slots): a[r] = mean * count = sum(e), a[r+1] = M2.
+// Generated code then turns M2 into sum((e - m)^2) = M2 + n (mean - m)^2 for its own m.
+template <int V> DEV void mom_acc_vec(float (&s1)[V], float (&s2)[V], int& cnt, int& kbits, const float (&x)[V]) {
+    if (cnt == 0) kbits = __float_as_int(x[0]);
+    const float K = __int_as_float(kbits);
+#pragma unroll
+    for (int i = 0; i < V; ++i) { const float d = x[i] - K; s1[i] += d; s2[i] = __fmaf_rn(d, d, s2[i]); }
+    cnt += V;
+}
+DEV void mom_acc_one(float& s1, float& s2, int& cnt, int& kbits, float x) {
+    if (cnt == 0) kbits = __float_as_int(x);
+    const float d = x - __int_as_float(kbits);
+    s1 += d; s2 = __fmaf_rn(d, d, s2); cnt += 1;
+}
+DEV void mom_merge(float& mean, int& n, float& m2, float mean_b, int n_b, float m2_b) {
+    if (n_b > 0) {
+        const int na = n, nt = n + n_b;
+        const float f = (float)n_b / (float)nt;
+        const float d = mean_b - mean;
+        m2 = m2 + m2_b + d * d * ((float)na * f);
+        mean = __fmaf_rn(d, f, mean);
+        n = nt;
+    }
+}
+// slot r of a pass and its partner (r + 1, clamped so that dead code stays in bounds)
+#define B200_PARTNER(r, NR) ((r) + 1 < (NR) ? (r) + 1 : (r))
+
+// per-lane accumulators of a thread -> one value per slot
+template <class S, int NR, int V>
+DEV void lanes_to_thread(float (&acc)[NR][V], int (&acci)[NR][V], float* a, int* ai) {
+#pragma unroll
+    for (int r = 0; r < NR; ++r) {
+        if (S::op(r) == OP_MOM_MEAN) {
+            const int r2 = B200_PARTNER(r, NR);
+            float s1 = acc[r][0], s2 = acc[r2][0];
+#pragma unroll
+            for (int i = 1; i < V; ++i) { s1 += acc[r][i]; s2 += acc[r2][i]; }
+            const int n = acci[r][0];
+            float mean = 0.f, m2 = 0.f;
+            if (n > 0) {
+                const float dm = s1 / (float)n;
+                mean = __int_as_float(acci[r2][0]) + dm;
+                m2 = fmaxf(__fmaf_rn(-s1, dm, s2), 0.f);
+            }
+            a[r] = mean; ai[r] = n; a[r2] = m2; ai[r2] = 0;
+        } else if (S::op(r) != OP_MOM_M2) {
+            a[r] = acc[r][0]; ai[r] = acci[r][0];
+#pragma unroll
+            for (int i = 1; i < V; ++i) red_merge(S::op(r), a[r], ai[r], acc[r][i], acci[r][i]);
+        }
+    }
+}
+// a <- a merged with b, slot by slot (pairs jointly)
+template <class S, int NR> DEV void merge_slots(float* a, int* ai, const float* b, const int* bi) {
+#pragma unroll
+    for (int r = 0; r < NR; ++r) {
+        if (S::op(r) == OP_MOM_MEAN) {
+            const int r2 = B200_PARTNER(r, NR);
+            mom_merge(a[r], ai[r], a[r2], b[r], bi[r], b[r2]);
+        } else if (S::op(r) != OP_MOM_M2) {
+            red_merge(S::op(r), a[r], ai[r], b[r], bi[r]);
+        }
+    }
+}
+// merge with the thread `o` lanes away (xor butterfly step)
+template <class S, int NR> DEV void shfl_merge(float* a, int* ai, int o) {
+    float b[NR]; int bi[NR];
+#pragma unroll
+    for (int r = 0; r < NR; ++r) {
+        b[r] = __shfl_xor_sync(0xffffffffu, a[r], o);
+        bi[r] = red_is_arg(S::op(r)) ? __shfl_xor_sync(0xffffffffu, ai[r], o) : -1;
+    }
+    merge_slots<S, NR>(a, ai, b, bi);
+}
+// what generated epilogues read: the mean slot of a moments pair becomes the plain sum
+template <class S, int NR> DEV void finish_slots(float* a, const int* ai) {
+#pragma unroll
+    for (int r = 0; r < NR; ++r) if (S::op(r) == OP_MOM_MEAN) a[r] *= (float)ai[r];
+}
+
 // ================================================================== element-wise
 // MODE 0: 2-d, vector index -> (k, n) by division; grid.x * BLOCK * UNROLL >= K * nvec.
 // MODE 1: flat (K == 1, all operands contiguous), scalar tail of N % V elements.
@@ -431,14 +527,33 @@ template <class S, class P, int NR, int V>
 DEV void accumulate(const P& p, const typename S::H& h, const typename S::L& l, i64 k, i64 n,
                     int idx0, int idx_step, float (&acc)[NR][V], int (&acci)[NR][V]) {
     if constexpr (S::FUSED) {
-        S::accum(p, h, l, k, n, acc);
+        S::accum(p, h, l, k, n, acc, acci);
     } else {
         float out[NR][V];
         S::eval(p, h, l, k, n, out);
 #pragma unroll
-        for (int r = 0; r < NR; ++r)
+        for (int r = 0; r < NR; ++r) {
+            if (S::op(r) == OP_MOM_MEAN) {
+                const int r2 = B200_PARTNER(r, NR);
+                mom_acc_vec<V>(acc[r], acc[r2], acci[r][0], acci[r2][0], out[r]);
+            } else if (S::op(r) != OP_MOM_M2) {
 #pragma unroll
-            for (int i = 0; i < V; ++i) red_acc(S::op(r), acc[r][i], acci[r][i], out[r][i], idx0 + i * idx_step);
+                for (int i = 0; i < V; ++i) red_acc(S::op(r), acc[r][i], acci[r][i], out[r][i], idx0 + i * idx_step);
+            }
+        }
+    }
+}
+// the same for one element of a row's scalar tail (lane 0 of the accumulators)
+template <class S, int NR, int V>
+DEV void accumulate_one(const float (&out)[NR][1], int idx, float (&acc)[NR][V], int (&acci)[NR][V]) {
+#pragma unroll
+    for (int r = 0; r < NR; ++r) {
+        if (S::op(r) == OP_MOM_MEAN) {
+            const int r2 = B200_PARTNER(r, NR);
+            mom_acc_one(acc[r][0], acc[r2][0], acci[r][0], acci[r2][0], out[r][0]);
+        } else if (S::op(r) != OP_MOM_M2) {
+            red_acc(S::op(r), acc[r][0], acci[r][0], out[r][0], idx);
+        }
     }
 }
 
@@ -530,7 +645,7 @@ DEV void red_rows_kernel(const P& p) {
 #pragma unroll
     for (int r = 0; r < NR; ++r)
 #pragma unroll
-        for (int i = 0; i < V; ++i) { acc[r][i] = red_init(S::op(r)); acci[r][i] = -1; }
+        for (int i = 0; i < V; ++i) { acc[r][i] = red_init(S::op(r)); acci[r][i] = red_init_idx(S::op(r)); }
 
     if (live) {
         typename S::H h;
@@ -558,30 +673,18 @@ DEV void red_rows_kernel(const P& p) {
                     S1::load_l(p, k, n, l1);
                     float out[NR][1];
                     S1::eval(p, h1, l1, k, n, out);
-#pragma unroll
-                    for (int r = 0; r < NR; ++r) red_acc(S::op(r), acc[r][0], acci[r][0], out[r][0], (int)n);
+                    accumulate_one<S, NR, V>(out, (int)n, acc, acci);
                 }
             }
         }
     }
     // lanes -> one value per thread
     float a[NR]; int ai[NR];
-#pragma unroll
-    for (int r = 0; r < NR; ++r) {
-        a[r] = acc[r][0]; ai[r] = acci[r][0];
-#pragma unroll
-        for (int i = 1; i < V; ++i) red_merge(S::op(r), a[r], ai[r], acc[r][i], acci[r][i]);
-    }
+    lanes_to_thread<S, NR, V>(acc, acci, a, ai);
     // threads of one index -> one value
     constexpr int W = TPR < 32 ? TPR : 32;
 #pragma unroll
-    for (int r = 0; r < NR; ++r)
-#pragma unroll
-        for (int o = W / 2; o > 0; o >>= 1) {
-            float b = __shfl_xor_sync(0xffffffffu, a[r], o);
-            int bi = __shfl_xor_sync(0xffffffffu, ai[r], o);
-            red_merge(S::op(r), a[r], ai[r], b, bi);
-        }
+    for (int o = W / 2; o > 0; o >>= 1) shfl_merge<S, NR>(a, ai, o);
     if constexpr (TPR > 32) {
         __shared__ float sv[NR][BLOCK / 32];
         __shared__ int si[NR][BLOCK / 32];
@@ -595,22 +698,18 @@ DEV void red_rows_kernel(const P& p) {
 #pragma unroll
             for (int r = 0; r < NR; ++r) {
                 a[r] = lane < BLOCK / 32 ? sv[r][lane] : red_init(S::op(r));
-                ai[r] = lane < BLOCK / 32 ? si[r][lane] : -1;
-#pragma unroll
-                for (int o = (BLOCK / 32) / 2; o > 0; o >>= 1) {
-                    float b = __shfl_xor_sync(0xffffffffu, a[r], o);
-                    int bi = __shfl_xor_sync(0xffffffffu, ai[r], o);
-                    red_merge(S::op(r), a[r], ai[r], b, bi);
-                }
+                ai[r] = lane < BLOCK / 32 ? si[r][lane] : red_init_idx(S::op(r));
             }
+#pragma unroll
+            for (int o = (BLOCK / 32) / 2; o > 0; o >>= 1) shfl_merge<S, NR>(a, ai, o);
         }
     }
     if constexpr (RPC > 1) {
-        if (live && sub == 0) S::epilogue(p, k, a, ai);
+        if (live && sub == 0) { finish_slots<S, NR>(a, ai); S::epilogue(p, k, a, ai); }
         return;
     } else {
         if (p.split == 1) {
-            if (tid == 0) S::epilogue(p, k, a, ai);
+            if (tid == 0) { finish_slots<S, NR>(a, ai); S::epilogue(p, k, a, ai); }
             return;
         }
         // several blocks per index: publish, count arrivals, last one combines in split order
@@ -630,22 +729,20 @@ DEV void red_rows_kernel(const P& p) {
             const float* pv = reinterpret_cast<const float*>(p.part_v);
             const int* pi = reinterpret_cast<const int*>(p.part_i);
 #pragma unroll
-            for (int r = 0; r < NR; ++r) {
-                a[r] = red_init(S::op(r)); ai[r] = -1;
-                const i64 o = ((i64)r * p.K + k) * p.split;
-                for (int s = tid; s < p.split; s += 32) {
-                    float b = __ldcg(pv + o + s);
-                    int bi = red_is_arg(S::op(r)) ? __ldcg(pi + o + s) : -1;
-                    red_merge(S::op(r), a[r], ai[r], b, bi);
-                }
+            for (int r = 0; r < NR; ++r) { a[r] = red_init(S::op(r)); ai[r] = red_init_idx(S::op(r)); }
+            for (int s = tid; s < p.split; s += 32) {
+                float b[NR]; int bi[NR];
 #pragma unroll
-                for (int o2 = 16; o2 > 0; o2 >>= 1) {
-                    float b = __shfl_xor_sync(0xffffffffu, a[r], o2);
-                    int bi = __shfl_xor_sync(0xffffffffu, ai[r], o2);
-                    red_merge(S::op(r), a[r], ai[r], b, bi);
+                for (int r = 0; r < NR; ++r) {
+                    const i64 o = ((i64)r * p.K + k) * p.split;
+                    b[r] = __ldcg(pv + o + s);
+                    bi[r] = red_is_arg(S::op(r)) ? __ldcg(pi + o + s) : -1;
                 }
+                merge_slots<S, NR>(a, ai, b, bi);
             }
-            if (tid == 0) S::epilogue(p, k, a, ai);
+#pragma unroll
+            for (int o2 = 16; o2 > 0; o2 >>= 1) shfl_merge<S, NR>(a, ai, o2);
+            if (tid == 0) { finish_slots<S, NR>(a, ai); S::epilogue(p, k, a, ai); }
         }
     }
 }
@@ -670,7 +767,7 @@ DEV void red_cols_kernel(const P& p) {
 #pragma unroll
     for (int r = 0; r < NR; ++r)
 #pragma unroll
-        for (int i = 0; i < V; ++i) { acc[r][i] = red_init(S::op(r)); acci[r][i] = -1; }
+        for (int i = 0; i < V; ++i) { acc[r][i] = red_init(S::op(r)); acci[r][i] = red_init_idx(S::op(r)); }
 
     if (live) {
         typename S::H h;
@@ -926,7 +1023,7 @@ DEV void rr_pass(const P& q, const P& p, i64 k, i64 knext, RowCtx& cx, unsigned 
 #pragma unroll
     for (int r = 0; r < NR; ++r)
 #pragma unroll
-        for (int i = 0; i < V; ++i) { acc[r][i] = red_init(S::op(r)); acci[r][i] = -1; }
+        for (int i = 0; i < V; ++i) { acc[r][i] = red_init(S::op(r)); acci[r][i] = red_init_idx(S::op(r)); }
     typename S::H h;
     S::load_h(q, k, h);
     const u32 nfull = (cx.v1 - cx.v0) / cx.cv;       // chunks in which every thread has all its vectors
@@ -981,31 +1078,26 @@ DEV void rr_pass(const P& q, const P& p, i64 k, i64 knext, RowCtx& cx, unsigned 
     if constexpr (NR > 0) {
         // lanes of a thread, then the threads of a warp; lane 0 leaves the warp's result in sv/si
         const int warp = tid >> 5, lane = tid & 31;
+        lanes_to_thread<S, NA, V>(acc, acci, a, ai);
 #pragma unroll
-        for (int r = 0; r < NR; ++r) {
-            a[r] = acc[r][0]; ai[r] = acci[r][0];
+        for (int o = 16; o > 0; o >>= 1) shfl_merge<S, NA>(a, ai, o);
+        if (lane == 0) {
 #pragma unroll
-            for (int i = 1; i < V; ++i) red_merge(S::op(r), a[r], ai[r], acc[r][i], acci[r][i]);
-#pragma unroll
-            for (int o = 16; o > 0; o >>= 1) {
-                float b = __shfl_xor_sync(0xffffffffu, a[r], o);
-                int bi = red_is_arg(S::op(r)) ? __shfl_xor_sync(0xffffffffu, ai[r], o) : 0;
-                red_merge(S::op(r), a[r], ai[r], b, bi);
-            }
-            if (lane == 0) { sv[r][warp] = a[r]; if (red_is_arg(S::op(r))) si[r][warp] = ai[r]; }
+            for (int r = 0; r < NR; ++r) { sv[r][warp] = a[r]; if (red_is_arg(S::op(r))) si[r][warp] = ai[r]; }
         }
     }
 }
 
 // Block results of one pass -> row result, left in res[0..NR) (value bits, or the index for arg
-// reductions) for every thread to read, and in a / ai of warp 0.  Warp 0 does the combining,
+// reductions) for every thread to read, and in a / ai of warp 0.  S::fixup (generated) may
+// rewrite the finished values before they are published (the centring term of a moments pair).  Warp 0 does the combining,
 // lane w standing for warp w and then for block w of the cluster, with xor butterflies (a fixed
 // order, so results repeat exactly); the other warps only take part in the barriers.  Blocks
 // PUSH their result into every peer's slots before the cluster barrier, so that after it each
 // block reads only its own shared memory.
-template <template <int> class SV, int V, int C, int THREADS>
-DEV void rr_combine(const RowCtx& cx, float* a, int* ai, float (*sv)[THREADS / 32], int (*si)[THREADS / 32],
-                    u32* slots /* [2 parities][NR][C][2] of this pass */, u32* res) {
+template <template <int> class SV, class P, int V, int C, int THREADS>
+DEV void rr_combine(const P& q, i64 k, const RowCtx& cx, float* a, int* ai, float (*sv)[THREADS / 32],
+                    int (*si)[THREADS / 32], u32* slots /* [2 parities][NR][C][2] of this pass */, u32* res) {
     typedef SV<V> S;
     constexpr int NR = S::NRED;
     constexpr int NW = THREADS / 32;
@@ -1015,15 +1107,14 @@ DEV void rr_combine(const RowCtx& cx, float* a, int* ai, float (*sv)[THREADS / 3
     if (warp == 0) {
 #pragma unroll
         for (int r = 0; r < NR; ++r) {
-            a[r] = lane < NW ? sv[r][lane] : 0.f;
-            ai[r] = (red_is_arg(S::op(r)) && lane < NW) ? si[r][lane] : -1;
+            a[r] = lane < NW ? sv[r][lane] : red_init(S::op(r));
+            ai[r] = (red_is_arg(S::op(r)) && lane < NW) ? si[r][lane] : red_init_idx(S::op(r));
+        }
 #pragma unroll
-            for (int o = NW / 2; o > 0; o >>= 1) {
-                float b = __shfl_xor_sync(0xffffffffu, a[r], o);
-                int bi = red_is_arg(S::op(r)) ? __shfl_xor_sync(0xffffffffu, ai[r], o) : 0;
-                red_merge(S::op(r), a[r], ai[r], b, bi);
-            }
-            if (C > 1 && lane < C) {                  // lane w writes this block's entry at block w
+        for (int o = NW / 2; o > 0; o >>= 1) shfl_merge<S, NR>(a, ai, o);
+        if (C > 1 && lane < C) {                      // lane w writes this block's entry at block w
+#pragma unroll
+            for (int r = 0; r < NR; ++r) {
                 u32* entry = mine + (r * C + (int)cx.rank) * 2;
                 dsmem_st(entry, (u32)lane, __float_as_uint(a[r]));
                 if (red_is_arg(S::op(r))) dsmem_st(entry + 1, (u32)lane, (u32)ai[r]);
@@ -1040,19 +1131,22 @@ DEV void rr_combine(const RowCtx& cx, float* a, int* ai, float (*sv)[THREADS / 3
             const u32* entry = mine + (r * C + (lane < C ? lane : 0)) * 2;
             a[r] = __uint_as_float(entry[0]);
             ai[r] = red_is_arg(S::op(r)) ? (int)entry[1] : -1;
+        }
 #pragma unroll
-            for (int o = C / 2; o > 0; o >>= 1) {
-                float b = __shfl_xor_sync(0xffffffffu, a[r], o);
-                int bi = red_is_arg(S::op(r)) ? __shfl_xor_sync(0xffffffffu, ai[r], o) : 0;
-                red_merge(S::op(r), a[r], ai[r], b, bi);
-            }
-            if (lane == 0) res[r] = red_is_arg(S::op(r)) ? (u32)ai[r] : __float_as_uint(a[r]);
+        for (int o = C / 2; o > 0; o >>= 1) shfl_merge<S, NR>(a, ai, o);
+        finish_slots<S, NR>(a, ai);
+        S::fixup(q, k, a, ai);
+        if (lane == 0) {
+#pragma unroll
+            for (int r = 0; r < NR; ++r) res[r] = (S::op(r) == OP_ARGMAX || S::op(r) == OP_ARGMIN) ? (u32)ai[r] : __float_as_uint(a[r]);
         }
         __syncwarp();
     } else {
         if (threadIdx.x == 0) {
+            finish_slots<S, NR>(a, ai);
+            S::fixup(q, k, a, ai);
 #pragma unroll
-            for (int r = 0; r < NR; ++r) res[r] = red_is_arg(S::op(r)) ? (u32)ai[r] : __float_as_uint(a[r]);
+            for (int r = 0; r < NR; ++r) res[r] = (S::op(r) == OP_ARGMAX || S::op(r) == OP_ARGMIN) ? (u32)ai[r] : __float_as_uint(a[r]);
         }
         __syncthreads();
     }

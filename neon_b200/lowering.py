@@ -506,6 +506,30 @@ class Pass(object):
         self.results = []      # (reduction op, fp32 result address, int32 index address or 0, count)
 
 
+def _red_code(r):
+    """Reduction slot code of node r: its op, or one half of a moments pair."""
+    if r.extra is not None:
+        return "OP_MOM_MEAN" if r.extra[0] == "mean" else "OP_MOM_M2"
+    return RED_CODE[r.op]
+
+
+def _has_index(r):
+    """The slot carries an int beside its value (arg index, or the count of a moments pair)."""
+    return r.op.startswith("arg") or r.extra is not None
+
+
+def _pair_order(rs):
+    """Reductions of one pass with every moments pair in neighbouring slots (mean, then M2)."""
+    out = []
+    for r in rs:
+        if r.extra is not None and r.extra[0] == "m2":
+            continue
+        out.append(r)
+        if r.extra is not None:
+            out.append(r.extra[1])
+    return out
+
+
 def _pow2ceil(x):
     p = 1
     while p < x:
@@ -538,6 +562,7 @@ class Planner(object):
         self.debug_starve_bytes = 0        # tests only: announce this many bytes that never arrive
         self.ew_unroll = 4
         self.ew_min_blocks = None          # None: 5 for instruction-heavy statements, else 4
+        self.fuse_moments = True           # sum(e) and sum(sqr(e - m)) in one pass when m needs sum-level results
 
     # ---- helpers on the frame: K = kept axis, N = loop axis
     def plan(self, st, scratch, rounding=0, fuse_final=True, lin=None):
@@ -550,6 +575,8 @@ class Planner(object):
         ra = st.axis                # reduced / loop axis in tensor coordinates
         ka = 1 - ra
         reds = [n for n in st.nodes if n.kind == "r" and self._reachable(st, n)]
+        if self.fuse_moments and fuse_final:
+            reds = self._pair_moments(st, reds, ka, ra)
         levels = sorted(set(n.level for n in reds))
         passes = []
         res_buf = {}                # reduction nid -> (addr_val, addr_idx or 0)
@@ -561,7 +588,7 @@ class Planner(object):
             if pz is not None:
                 return [pz]
         for lv in levels:
-            rs = [n for n in reds if n.level == lv]
+            rs = _pair_order([n for n in reds if n.level == lv])
             final = fuse_final and (lv == levels[-1]) and root_is_k and out_is_k and st.root.level == lv
             K = full_shape[ka]
             if not final:
@@ -576,6 +603,108 @@ class Planner(object):
                 return passes
         passes.append(self._ew_pass(st, res_buf, ka, ra, rounding))
         return passes
+
+    # ---- moments pairs ---------------------------------------------------------------
+    def _pair_moments(self, st, reds, ka, ra):
+        """Find reductions of the form sum(sqr(e - m)) (or sqr(m - e)) where e varies along the
+        reduced axis and m is a per-row value that needs results of the pass e itself could be
+        reduced in -- the variance pattern, m = sum(e) * c.  Evaluated as written, such a sum
+        waits for another full pass over e.  Instead the pass that can reduce e accumulates the
+        first two moments of e (see "moments" in the kernel header), and sum(sqr(e - m)) is
+        M2 + n * (mean - m)^2 for whatever m turns out to be -- exact for any m, so nothing
+        here depends on the value of a constant.  The reduction moves one level down; levels
+        of everything above it are recomputed.  Only with lanes along the reduced axis (the row
+        kernels).  Returns the reductions to schedule (a sum(e) node is added if the tree has
+        none: it is the pair's mean slot)."""
+        self._frame(st, ka, ra)
+        if self._lanes_on_k(st, ka, ra, self._full_shape(st)[ka]):
+            return reds
+        found = []
+        taken = set()
+        for r2 in reds:
+            if r2.op != "sum" or r2.extra is not None:
+                continue
+            sq = r2.args[0]
+            if sq.kind != "u" or sq.op != "sqr":
+                continue
+            d = sq.args[0]
+            if d.kind != "b" or d.op != "sub":
+                continue
+            for e, m in ((d.args[0], d.args[1]), (d.args[1], d.args[0])):
+                if (e.shape[ra] > 1 and m.shape[ra] == 1 and m.kind != "c" and m.level == e.level + 1
+                        and e.nid not in taken and not self._contains_zero_op(e)):
+                    found.append((r2, e, m))
+                    taken.add(e.nid)
+                    break
+        if not found:
+            return reds
+        reds = list(reds)
+        for r2, e, m in found:
+            r1 = st._reduce("sum", e)
+            if r1.extra is not None:
+                continue
+            r1.extra = ("mean", r2)
+            r2.extra = ("m2", r1, m, e)
+            if r1 not in reds:
+                reds.append(r1)
+        # levels again, bottom up (nodes are in creation order, arguments first); a pair's M2
+        # now sits at the level of the plain reduction of e
+        for n in st.nodes:
+            if n.kind in ("u", "b"):
+                n.level = max(a.level for a in n.args)
+            elif n.kind == "r":
+                if n.extra is not None and n.extra[0] == "m2":
+                    n.level = n.extra[3].level + 1
+                else:
+                    n.level = n.args[0].level + 1
+        return reds
+
+    @staticmethod
+    def _contains_zero_op(node):
+        todo, seen = [node], set()
+        while todo:
+            n = todo.pop()
+            if n.nid in seen:
+                continue
+            seen.add(n.nid)
+            if n.kind == "z":
+                return True
+            if n.kind != "r":
+                todo.extend(n.args)
+        return False
+
+    @staticmethod
+    def _lanes_on_k(st, ka, ra, K):
+        """True when a reduction pass of this statement runs its lanes along the kept axis
+        (the reduced axis is the strided one of its full-size operands)."""
+        def lanes_ok(axis_name):
+            for o in st.operands:
+                sk, sn = o._frame_strides
+                if o.shape[ka] > 1 and o.shape[ra] > 1 and (sn if axis_name == "n" else sk) != 1:
+                    return False
+            return True
+        return (not lanes_ok("n")) and lanes_ok("k") and K > 1
+
+    def _fixup_lines(self, ep, rs, fresh, n_expr):
+        """Code that turns the M2 of every moments pair among ``rs`` into the sum the statement
+        asked for, sum((e - m)^2) = M2 + n (mean - m)^2, with m evaluated by emitter ``ep`` from
+        the finished results r[] of this pass (and earlier ones).  Returns (lines, {nid: name}):
+        the lines to run first and the name under which each corrected sum is available."""
+        lines, names = [], {}
+        for r in rs:
+            if r.extra is None or r.extra[0] != "m2":
+                continue
+            r1, m = r.extra[1], r.extra[2]
+            i1, i2 = fresh[r1.nid], fresh[r.nid]
+            before = len(ep.h_lines)
+            mref = ep.hoist(m)
+            lines.extend(ep.h_lines[before:])
+            del ep.h_lines[before:]
+            name = "m2c%d" % r.nid
+            lines.append("float %s; { const int i = 0; (void)i; const float dm = r[%d] / %s - %s; "
+                         "%s = __fmaf_rn(dm * dm, %s, r[%d]); }" % (name, i1, n_expr, mref, name, n_expr, i2))
+            names[r.nid] = name
+        return lines, names
 
     # ---- row-resident statement: all passes in one cluster kernel -------------------
     def _rowres_pass(self, st, reds, levels, ka, ra, full_shape, rounding, red_out):
@@ -600,11 +729,22 @@ class Planner(object):
         for lv in levels:
             em = self._Emit(st, f, ka, ra, False, res_buf, lv - 1, tables)
             em.no_nc = True
-            rs = [n for n in reds if n.level == lv]
-            outs = [em.elem(r.args[0]) for r in rs]
+            rs = _pair_order([n for n in reds if n.level == lv])
+            outs = [em.elem(self._red_operand(r)) for r in rs]
             ems.append((em, rs, outs))
             lane_ops += em.lane_ops
             staged.update(em.full_inputs)
+        # finished results of each pass are corrected in registers before rr_combine publishes them
+        fixups = []
+        for em, rs, outs in ems:
+            fx = self._Emit(st, f, ka, ra, False, res_buf, rs[0].level - 1, tables)
+            fx.no_nc = True
+            fresh = {r.nid: j for j, r in enumerate(rs)}
+            for r in rs:
+                if r.extra is None or r.extra[0] != "m2":
+                    fx.names[("h", r.nid)] = "(float)ri[%d]" % fresh[r.nid] if r.op.startswith("arg") else "r[%d]" % fresh[r.nid]
+            fix_lines, fixed = self._fixup_lines(fx, rs, fresh, "(float)p.N")
+            fixups.append(fix_lines + ["r[%d] = %s;" % (fresh[nid], name) for nid, name in fixed.items()])
         fin = self._Emit(st, f, ka, ra, False, res_buf, 1 << 30, tables)
         fin.no_nc = True
         if red_out:
@@ -700,11 +840,11 @@ class Planner(object):
 
         parts = ['#include "optree_templates.cuh"', "using namespace b200;", f.decl()]
         for i, (em, rs, outs) in enumerate(ems):
-            ops = " : ".join("r == %d ? %s" % (j, RED_CODE[r.op]) for j, r in enumerate(rs[:-1]))
-            ops = (ops + " : " if ops else "") + RED_CODE[rs[-1].op]
+            ops = " : ".join("r == %d ? %s" % (j, _red_code(r)) for j, r in enumerate(rs[:-1]))
+            ops = (ops + " : " if ops else "") + _red_code(rs[-1])
             tail = ["out[%d][i] = %s;" % (j, e) for j, e in enumerate(outs)]
             parts.append(self._struct("S%d" % i, em, tail, len(rs), ops, None, None,
-                                      acc_tail=self._accum_tail(em, rs, outs)))
+                                      acc_tail=self._accum_tail(em, rs, outs), fix_lines=fixups[i]))
         if red_out:
             parts.append(self._struct("SF", fin, [], 0, "OP_SUM", fin.h_lines + [store], None, epilogue_only=True))
         else:
@@ -751,7 +891,7 @@ class Planner(object):
             body.append("    rr_pass<S%d, ST, P, %d, %d, %d, %s, %s>(q, p, k, knext, cx, %s, %s, a, ai, sv, si);"
                         % (i, V, threads, unroll, "true" if i == 0 else "false", "true" if last else "false",
                            dyn_cur, bars_cur))
-            body.append("    rr_combine<S%d, %d, %d, %d>(cx, a, ai, sv, si, &slots[%d][0][0][0][0], &s_res[%d]);"
+            body.append("    rr_combine<S%d, P, %d, %d, %d>(q, k, cx, a, ai, sv, si, &slots[%d][0][0][0][0], &s_res[%d]);"
                         % (i, V, C, threads, i, slot_of[rs[0].nid]))
         if red_out:
             body.append("    if (threadIdx.x == 0 && cx.rank == 0) SF<%d>::epilogue(q, k, a, ai);" % V)
@@ -789,37 +929,61 @@ class Planner(object):
         return pz
 
     @staticmethod
+    def _red_operand(r):
+        """The expression a reduction slot accumulates: a pair's M2 slot accumulates e itself."""
+        return r.extra[3] if (r.extra is not None and r.extra[0] == "m2") else r.args[0]
+
+    @staticmethod
     def _accum_tail(em, rs, outs):
-        """Lines of S::accum for a pass whose reductions are all sums and where at least one
-        sums a stored 16-bit float tensor as it is (the add then takes the stored value);
-        None when the generic eval + reduction step should be used."""
+        """(per-lane lines, per-vector lines) of S::accum for a pass whose reductions are all sums
+        or moments pairs and where the accumulation can absorb an operand's conversion (a stored
+        16-bit float summed as it is) or is a moments pair; None when the generic eval +
+        reduction step should be used."""
         if any(r.op != "sum" for r in rs):
             return None
-        lines, fused = [], False
+        lines, post, fused = [], [], False
         for j, (r, e) in enumerate(zip(rs, outs)):
-            half = em.half_leaf(r.args[0])
-            if half is not None:
+            if r.extra is not None and r.extra[0] == "m2":
+                continue                                   # written with its mean slot
+            half = em.half_leaf(Planner._red_operand(r))
+            if r.extra is not None:                        # mean slot j, M2 slot j + 1
+                fused = True
+                kexpr = "__int_as_float(acci[%d][0])" % (j + 1)
+                if half is not None:
+                    first = "mx_add<%s, V>(%s, 0, 0.0f)" % (DT_NAMES[half[1]], half[0])
+                    dexpr = "mx_sub<%s, V>(%s, i, %s)" % (DT_NAMES[half[1]], half[0], kexpr)
+                else:
+                    first, dexpr = e, "(%s - %s)" % (e, kexpr)
+                lines.append("if (i == 0 && acci[%d][0] == 0) acci[%d][0] = __float_as_int(%s);" % (j, j + 1, first))
+                lines.append("{ const float d = %s; acc[%d][i] += d; acc[%d][i] = __fmaf_rn(d, d, acc[%d][i]); }"
+                             % (dexpr, j, j + 1, j + 1))
+                post.append("acci[%d][0] += V;" % j)
+            elif half is not None:
                 fused = True
                 lines.append("acc[%d][i] = mx_add<%s, V>(%s, i, acc[%d][i]);" % (j, DT_NAMES[half[1]], half[0], j))
             else:
                 lines.append("acc[%d][i] += %s;" % (j, e))
-        return lines if fused else None
+        return (lines, post) if fused else None
 
     @staticmethod
     def _accum_fn(em, acc_tail, nred, ind):
         if acc_tail is None:
             return ["    enum { FUSED = 0 };"]
+        lines, post = acc_tail
         body = list(em.e_pre)
         body.append("_Pragma(\"unroll\") for (int i = 0; i < V; ++i) {")
         body.extend("    " + x for x in em.e_lines)
-        body.extend("    " + x for x in acc_tail)
+        body.extend("    " + x for x in lines)
         body.append("}")
+        body.extend(post)
         return ["    enum { FUSED = 1 };",
-                "    static DEV void accum(const P& p, const H& h, const L& l, i64 k, i64 n, float (&acc)[%d][V]) {" % nred
+                "    static DEV void accum(const P& p, const H& h, const L& l, i64 k, i64 n, float (&acc)[%d][V], "
+                "int (&acci)[%d][V]) {" % (nred, nred)
                 + ind + ind.join(body) + "\n    }"]
 
     @staticmethod
-    def _struct(name, em, eval_tail, nred, ops, ep_lines, st_lines, epilogue_only=False, acc_tail=None):
+    def _struct(name, em, eval_tail, nred, ops, ep_lines, st_lines, epilogue_only=False, acc_tail=None,
+                fix_lines=None):
         ind = "\n        "
         nout = max(nred, 1)
         parts = ["template <int V> struct %s {" % name]
@@ -845,6 +1009,9 @@ class Planner(object):
         if ep_lines is not None:
             parts.append("    static DEV void epilogue(const P& p, i64 k, const float* r, const int* ri) {"
                          + ind + ind.join(ep_lines) + "\n    }")
+        if fix_lines is not None:
+            parts.append("    static DEV void fixup(const P& p, i64 k, float* r, const int* ri) {"
+                         + ind + ind.join(fix_lines) + "\n    }")
         parts.append("};")
         return "\n".join(parts)
 
@@ -1222,20 +1389,12 @@ class Planner(object):
         K, N = full_shape[ka], full_shape[ra]
         self._frame(st, ka, ra)
         # orientation: lanes along N when the loop axis is the contiguous one
-        def lanes_ok(axis_name):
-            for o in st.operands:
-                sk, sn = o._frame_strides
-                var_k, var_n = o.shape[ka] > 1, o.shape[ra] > 1
-                if var_k and var_n:
-                    if (sn if axis_name == "n" else sk) != 1:
-                        return False
-            return True
-        lanes_on_k = (not lanes_ok("n")) and lanes_ok("k") and K > 1
+        lanes_on_k = self._lanes_on_k(st, ka, ra, K)
         f = _Fields()
         em = self._Emit(st, f, ka, ra, lanes_on_k, res_buf, reds[0].level - 1, (self.unary, self.binary))
         outs = []
         for r in reds:
-            outs.append(em.elem(r.args[0]))
+            outs.append(em.elem(self._red_operand(r)))
         eval_tail = ["out[%d][i] = %s;" % (i, e) for i, e in enumerate(outs)]
         acc_tail = self._accum_tail(em, reds, outs)
 
@@ -1243,9 +1402,15 @@ class Planner(object):
         ep = self._Emit(st, f, ka, ra, False, res_buf, reds[0].level - 1, (self.unary, self.binary))
         ep_lines = []
         fresh = {r.nid: i for i, r in enumerate(reds)}
-        if final:
-            for r in reds:
+        # results of this pass as the epilogue names them; a moments pair's second slot is first
+        # turned into the sum the statement asked for
+        for r in reds:
+            if r.extra is None or r.extra[0] != "m2":
                 ep.names[("h", r.nid)] = "(float)ri[%d]" % fresh[r.nid] if r.op.startswith("arg") else "r[%d]" % fresh[r.nid]
+        fix_lines, fixed = self._fixup_lines(ep, reds, fresh, "(float)p.N")
+        for nid, name in fixed.items():
+            ep.names[("h", nid)] = name
+        if final:
             odt = st.out.dt
             f.u64("o", st.out.ptr)
             f.i64("o_sk", st.out._frame_strides[0])
@@ -1259,12 +1424,16 @@ class Planner(object):
             else:
                 val = ep.hoist(st.root)
                 store = "{ const int i = 0; (void)i; st_one<%s>(p.o, %s, %s); }" % (DT_NAMES[odt], ko, val)
-            ep_lines = ep.h_lines + [store]
+            ep_lines = fix_lines + ep.h_lines + [store]
         else:
+            ep_lines = list(fix_lines)
             for r in reds:
                 av, ai = res_buf[r.nid]
                 i = fresh[r.nid]
-                if r.op.startswith("arg"):
+                if r.nid in fixed:
+                    f.u64("r%dv" % r.nid, av)
+                    ep_lines.append("reinterpret_cast<float*>(p.r%dv)[k] = %s;" % (r.nid, fixed[r.nid]))
+                elif r.op.startswith("arg"):
                     f.u64("r%dv" % r.nid, ai)
                     ep_lines.append("reinterpret_cast<int*>(p.r%dv)[k] = ri[%d];" % (r.nid, i))
                     # the extreme value itself, for callers that merge results of several devices
@@ -1316,7 +1485,7 @@ class Planner(object):
         f.i64("seg", seg)
         f.i32("split", split)
         nr = len(reds)
-        has_arg = any(r.op.startswith("arg") for r in reds)
+        has_arg = any(_has_index(r) for r in reds)
         if split > 1:
             f.u64("part_v", scratch(4 * nr * K * split, False))
             f.u64("part_i", scratch(4 * nr * K * split, False) if has_arg else 0)
@@ -1325,8 +1494,8 @@ class Planner(object):
             f.u64("part_v", 0)
             f.u64("part_i", 0)
             f.u64("counters", 0)
-        ops = " : ".join("r == %d ? %s" % (i, RED_CODE[r.op]) for i, r in enumerate(reds[:-1]))
-        ops = (ops + " : " if ops else "") + RED_CODE[reds[-1].op]
+        ops = " : ".join("r == %d ? %s" % (i, _red_code(r)) for i, r in enumerate(reds[:-1]))
+        ops = (ops + " : " if ops else "") + _red_code(reds[-1])
         src, pz.name = self._source(f, em, eval_tail, nr, ops, ep_lines, None, call, acc_tail=acc_tail)
         pz.source, pz.fields, pz.grid, pz.block = src, f, grid, (BLOCK, 1, 1)
         pz.uses_rng = em.uses_rng

@@ -43,9 +43,37 @@ def test_axis1_statistics_use_row_kernels_and_vector_width_8_for_fp16():
     be = DryRunBackend()
     be.compile = False
     be._planner.rowres = False
+    be._planner.fuse_moments = False
     _run_dry(be, cfg4(256, 401408))
     assert [p.kind for p in be.passes] == ["red_rows", "red_rows", "ew_2d"]
     assert all("V=8" in p.desc for p in be.passes)
+
+
+def test_mean_and_centred_squares_share_one_pass():
+    """var(x) = sum(sqr(x - sum(x) * c)) * c needs sum(x) before its own sum can start; the
+    planner computes both from one pass over x (first two moments) instead of two."""
+    be = DryRunBackend()
+    be.compile = False
+    be._planner.rowres = False
+    _run_dry(be, cfg4(256, 401408))
+    assert [p.kind for p in be.passes] == ["red_rows", "ew_2d"]
+    assert "OP_MOM_MEAN : OP_MOM_M2" in be.passes[0].source
+    # a centre that is not the mean works the same way: sum(sqr(max(x) - x))
+    x, out = be.empty((64, 5000)), be.empty((64, 1))
+    be.passes = []
+    out[:] = be.sum(be.square(be.max(x, axis=1) - x), axis=1)
+    assert [p.kind for p in be.passes] == ["red_rows"]
+    assert "OP_MAX" in be.passes[0].source and "OP_MOM_M2" in be.passes[0].source
+    # a centre that needs nothing from this pass leaves the statement as it is
+    m = be.empty((64, 1))
+    be.passes = []
+    out[:] = be.sum(be.square(x - m), axis=1)
+    assert [p.kind for p in be.passes] == ["red_rows"] and "OP_MOM" not in be.passes[0].source
+    # reductions down the strided axis keep the two-pass form
+    col = be.empty((1, 5000))
+    be.passes = []
+    col[:] = be.var(x, axis=0)
+    assert [p.kind for p in be.passes] == ["red_cols", "red_cols"]
 
 
 def test_rows_that_fit_cluster_shared_memory_become_one_row_resident_kernel():
@@ -57,7 +85,7 @@ def test_rows_that_fit_cluster_shared_memory_become_one_row_resident_kernel():
     assert pz.cluster == 8 and pz.smem == 100352 and pz.block == (512, 1, 1)
     be.passes = []
     _run_dry(be, cfg4(32, 4096))             # short rows: the multi-pass kernels
-    assert [p.kind for p in be.passes] == ["red_rows", "red_rows", "ew_2d"]
+    assert [p.kind for p in be.passes] == ["red_rows", "ew_2d"]
     be.passes = []
     _run_dry(be, cfg4(8, 4000000))           # a row larger than eight blocks can hold
     assert "rowres" not in [p.kind for p in be.passes]

@@ -116,6 +116,63 @@ def test_rows_off_16_byte_boundaries_take_the_multi_pass_kernels(shape, dtype, b
     _compare(case, got, _oracle64(case))
 
 
+def _moment_cases():
+    """Statements whose second sum is centred on a value that needs the first (variance and its
+    relatives): computed from one pass (moments pair).  Sub-warp rows, whole blocks, rows split
+    over blocks, scalar tails, 16-bit storage, a compound operand, a centre that is not the
+    mean, an arg reduction sharing the pass, data far from zero."""
+    def in1(shape, dtype=np.float32, scale=1.0, offset=0.0):
+        return lambda rng: {"x": (offset + scale * rng.standard_normal(shape)).astype(dtype)}
+
+    def var_rows(be, t):
+        t["out"][:] = be.var(t["x"], axis=1)
+
+    def std_rows(be, t):
+        x = t["x"]
+        t["out"][:] = (x - be.mean(x, axis=1)) / (be.std(x, axis=1) + 1e-3)
+
+    def about_max(be, t):
+        x = t["x"]
+        t["out"][:] = be.sum(be.square(be.max(x, axis=1) - x), axis=1)
+
+    def compound(be, t):
+        x = t["x"]
+        t["out"][:] = be.var(x * x + 0.5 * x, axis=1)
+
+    def with_argmax(be, t):
+        x = t["x"]
+        t["out"][:] = be.var(x, axis=1) + be.argmax(x, axis=1)
+
+    out = []
+    for shape in ((300, 40), (37, 1000), (64, 2051), (5, 100003), (3, 1 << 21)):
+        out.append(cases.Case("var_rows_%dx%d" % shape, in1(shape), {"out": ((shape[0], 1), np.float32)}, var_rows))
+    out.append(cases.Case("var_rows_far_from_zero_40x30000", in1((40, 30000), offset=100.0),
+                          {"out": ((40, 1), np.float32)}, var_rows))
+    out.append(cases.Case("var_rows_f16_33x4099", in1((33, 4099), np.float16, 2.0, 1.0),
+                          {"out": ((33, 1), np.float32)}, var_rows))
+    out.append(cases.Case("standardise_rows_f16_20x12345", in1((20, 12345), np.float16, 2.0, 1.0),
+                          {"out": ((20, 12345), np.float16)}, std_rows))
+    out.append(cases.Case("squares_about_max_64x5000", in1((64, 5000)), {"out": ((64, 1), np.float32)}, about_max))
+    out.append(cases.Case("var_of_compound_50x3000", in1((50, 3000)), {"out": ((50, 1), np.float32)}, compound))
+    out.append(cases.Case("var_plus_argmax_48x2500", in1((48, 2500)), {"out": ((48, 1), np.float32)}, with_argmax))
+    return out
+
+
+@pytest.mark.parametrize("case", _moment_cases(), ids=lambda c: c.name)
+def test_single_pass_moments_match_checker(case, b200):
+    got = cases.run_case(b200, case)
+    _compare(case, got, _oracle64(case))
+    # the same statement evaluated as written (one pass per sum) agrees too
+    b200._planner.fuse_moments = False
+    b200._plans.clear()
+    try:
+        plain = cases.run_case(b200, case)
+    finally:
+        b200._planner.fuse_moments = True
+        b200._plans.clear()
+    _compare(case, plain, _oracle64(case))
+
+
 def test_bounded_wait_reports_instead_of_hanging():
     """The one software wait in the kernels (a block waiting for its TMA-staged row slice)
     has a time limit.  Announce 16 bytes that never arrive, give it 20 ms: the kernel must
