@@ -41,7 +41,7 @@ struct FullRed {
             for (int i = 0; i < V; ++i) out[0][i] = ABS ? fabsf(a0[i]) : a0[i];
         }
         // plain sums of 16-bit floats: the add takes the stored value as it is
-        static DEV void accum(const RP&, const H&, const L& l, i64, i64, float (&acc)[1][V]) {
+        static DEV void accum(const RP&, const H&, const L& l, i64, i64, float (&acc)[1][V], int (&)[1][V]) {
             if constexpr (DT != b200::F32) {
 #pragma unroll
                 for (int i = 0; i < V; ++i) acc[0][i] = b200::mx_add<DT, V>(l.a0, i, acc[0][i]);
