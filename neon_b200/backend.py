@@ -275,6 +275,19 @@ class B200Backend(OpTreeBackend):
             return node.reshape(1, size)
         return node
 
+    @staticmethod
+    def _flat_extent(node):
+        """Number of elements the fused whole-tensor reduction(s) under ``node`` run over."""
+        todo = [node]
+        while todo:
+            n = todo.pop()
+            if isinstance(n, OpTreeNode):
+                if n[0]["op"] in OpCollection.reduction_ops:
+                    child = n[1]
+                    return int(child.shape[1]) if hasattr(child, "shape") else 1
+                todo.extend(c for c in n[1:] if c is not None)
+        return None
+
     def _split(self, node, stmts):
         """Returns (expression, tag): tag is None (no reduction inside), 0/1 (reduces
         along that axis) or 'flat' (contains a fused whole-tensor reduction and only
@@ -336,6 +349,10 @@ class B200Backend(OpTreeBackend):
             left = self._finish_dot(left, stmts)
         if type(right) is tuple:
             right = self._finish_dot(right, stmts)
+        if lt == "flat" and rt_ == "flat" and self._flat_extent(left) != self._flat_extent(right):
+            # whole-tensor reductions of tensors of different sizes (the squared-gradient norm
+            # over all layers, optimizers/optimizer.py:72-96): they cannot share a pass
+            left, lt = self._materialise(left, (1, 1), stmts), None
         if lt is not None and rt_ is not None and lt != rt_:
             # two sides reduce differently: evaluate one of them first.  A flat side
             # is a (1,1) value; otherwise the side reducing along axis 0 goes first

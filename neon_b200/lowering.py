@@ -396,6 +396,12 @@ class Statement(object):
         if a.shape[ax] == 1:
             # reducing an extent of one: the value itself, or index 0
             return self._const(0.0, ("k", 0.0)) if op.startswith("arg") else a
+        extent = getattr(self, "_red_extent", None)
+        if extent is None:
+            self._red_extent = a.shape[ax]
+        elif extent != a.shape[ax]:
+            raise ValueError("reductions over %d and %d elements cannot share one kernel"
+                             % (extent, a.shape[ax]))
         shape = list(a.shape)
         shape[ax] = 1
         shape = tuple(shape)

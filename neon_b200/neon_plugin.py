@@ -20,8 +20,9 @@ What ``register`` does besides the registry entry:
 * with ``as_gpu=True`` the backend also answers to the name ``'gpu'`` and, where
   neon's own ``nervanagpu`` module cannot be imported (it needs pycuda), a module
   of that name is provided whose ``NervanaGPU`` / ``GPUTensor`` are this package's
-  classes.  That is how neon's own test files, which ask for ``'gpu'``, are run
-  against this backend.
+  classes, and neon's device queries (``neon.backends.util.check_gpu``, pycuda based) are
+  answered by this package's runtime.  That is how neon's own test files, which ask for
+  ``'gpu'``, are run against this backend.
 """
 
 import sys
@@ -46,7 +47,31 @@ def register(as_gpu=False, backend_cls=None):
             sys.modules["neon.backends.nervanagpu"] = mod
             import neon.backends
             neon.backends.nervanagpu = mod
+        _answer_device_queries()
     return backend_cls
+
+
+def _answer_device_queries():
+    """neon asks pycuda for the device count and compute capability
+    (neon/backends/util/check_gpu.py:20-100; its tests call these before touching a GPU
+    backend).  Without pycuda both answer 0; let them ask this package's runtime instead."""
+    from neon.backends.util import check_gpu
+    from . import runtime as rt
+
+    def get_device_count(verbose=False):
+        return rt.device_count()
+
+    def get_compute_capability(device_id=None, verbose=False):
+        ids = range(rt.device_count()) if device_id is None else \
+            ([device_id] if isinstance(device_id, int) else list(device_id))
+        caps = []
+        for i in ids:
+            props = rt.device_props(i)
+            caps.append(props.cc_major + props.cc_minor / 10.0)
+        return max(caps) if caps else 0
+
+    check_gpu.get_device_count = get_device_count
+    check_gpu.get_compute_capability = get_compute_capability
 
 
 def _adopt_tensor_base():

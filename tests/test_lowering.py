@@ -141,6 +141,29 @@ def test_reference_error_behaviour():
         be.onehot(be.empty((1, 6), np.int32), axis=2)
 
 
+def test_whole_tensor_reductions_of_different_sizes_do_not_share_a_pass():
+    """The squared-gradient norm over all layers (neon/optimizers/optimizer.py:72-96) adds
+    sum(square(g)) over tensors of different sizes: one pass each, then the scalar part."""
+    be = DryRunBackend()
+    be.compile = False
+    be.bsz = 4
+    g0, g1, g2 = be.empty((96, 160)), be.empty((50, 1)), be.empty((96, 160))
+    norm = be.empty((1, 1))
+    norm[:] = be.sqrt(sum(be.sum(be.square(g)) for g in (g0, g1))) / be.bsz
+    assert ["N=15360" in p.desc for p in be.passes] == [True, False]
+    assert "N=50" in be.passes[1].desc
+    be.passes = []
+    norm[:] = be.sqrt(sum(be.sum(be.square(g)) for g in (g0, g2))) / be.bsz       # same size: one pass
+    assert len(be.passes) == 1
+    # and the lowering itself refuses what the splitter must never hand it
+    from neon_b200.lowering import Statement
+    from neon_b200.optree import OpTreeNode
+    a, b = g0.reshape(1, g0.size), g1.reshape(1, g1.size)
+    tree = OpTreeNode({"op": "assign"}, norm, be.sum(a, axis=1) + be.sum(b, axis=1))
+    with pytest.raises(ValueError):
+        Statement(tree.traverse([]))
+
+
 def test_unaligned_views_fall_back_to_narrower_vectors():
     be = DryRunBackend()
     be.compile = False
