@@ -990,10 +990,10 @@ DEV u64 global_ns() { u64 t; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t)
 // the whole block, which then stops staging (its results are meaningless, the
 // host raises on the status) but keeps taking part in every barrier so that its
 // cluster peers are never left waiting.
-DEV void rr_wait_chunk(RowCtx& cx, u64* bar, u64 status, u64 limit_ns) {
-    if (cx.failed || mbar_try_wait(bar, cx.phase)) return;
+DEV void rr_wait_parity(RowCtx& cx, u64* bar, u32 parity, u64 status, u64 limit_ns) {
+    if (cx.failed || mbar_try_wait(bar, parity)) return;
     const u64 t0 = global_ns();
-    while (!mbar_try_wait(bar, cx.phase)) {
+    while (!mbar_try_wait(bar, parity)) {
         if (global_ns() - t0 > limit_ns) {
             cx.failed = true;
             if (status) atomicExch(reinterpret_cast<int*>(status), 1);
@@ -1001,10 +1001,81 @@ DEV void rr_wait_chunk(RowCtx& cx, u64* bar, u64 status, u64 limit_ns) {
         }
     }
 }
+DEV void rr_wait_chunk(RowCtx& cx, u64* bar, u64 status, u64 limit_ns) {
+    rr_wait_parity(cx, bar, cx.phase, status, limit_ns);
+}
 DEV void rr_row_end(RowCtx& cx) {
     cx.failed = __syncthreads_or(cx.failed) != 0;
     cx.phase ^= 1;
     cx.row_parity ^= 1;
+}
+
+// The work of one thread on chunk c of its block's slice: UNROLL vectors, element-wise (NR == 0:
+// evaluate and store) or folded into the accumulators.
+template <class S, class P, int NA, int V, int THREADS, int UNROLL>
+DEV void rr_chunk(const P& q, const typename S::H& h, i64 k, const RowCtx& cx, u32 c, u32 nfull,
+                  float (&acc)[NA][V], int (&acci)[NA][V]) {
+    constexpr int NR = S::NRED;
+    const u32 vb = cx.v0 + c * cx.cv + threadIdx.x;
+    typename S::L l[UNROLL];
+    if (c < nfull) {                                 // every thread has all its vectors: no bounds checks
+#pragma unroll
+        for (int u = 0; u < UNROLL; ++u) S::load_l(q, k, (i64)((vb + u * THREADS) * (u32)V), l[u]);
+#pragma unroll
+        for (int u = 0; u < UNROLL; ++u) {
+            const i64 n = (i64)((vb + u * THREADS) * (u32)V);
+            if constexpr (NR == 0) {
+                float out[1][V];
+                S::eval(q, h, l[u], k, n, out);
+                S::store(q, k, n, out[0]);
+            } else {
+                accumulate<S, P, NA, V>(q, h, l[u], k, n, (int)n, 1, acc, acci);
+            }
+        }
+    } else {
+#pragma unroll
+        for (int u = 0; u < UNROLL; ++u)
+            if (vb + u * THREADS < cx.v1) S::load_l(q, k, (i64)((vb + u * THREADS) * (u32)V), l[u]);
+#pragma unroll
+        for (int u = 0; u < UNROLL; ++u) {
+            if (vb + u * THREADS < cx.v1) {
+                const i64 n = (i64)((vb + u * THREADS) * (u32)V);
+                if constexpr (NR == 0) {
+                    float out[1][V];
+                    S::eval(q, h, l[u], k, n, out);
+                    S::store(q, k, n, out[0]);
+                } else {
+                    accumulate<S, P, NA, V>(q, h, l[u], k, n, (int)n, 1, acc, acci);
+                }
+            }
+        }
+    }
+}
+// every warp reports that it is done with chunk c of the row; thread 0 alone waits for all of
+// them (bounded) and then starts the next row's copies into the chunk, so the other warps run
+// on without a block-wide barrier
+template <class ST, class P>
+DEV void rr_release_chunk(const P& p, RowCtx& cx, i64 knext, u32 c, unsigned char* dyn, u64* bars) {
+    __syncwarp();
+    if ((threadIdx.x & 31) == 0) mbar_arrive(bars + RR_MAX_CHUNKS + c);
+    if (threadIdx.x == 0 && knext < p.K) {
+        rr_wait_chunk(cx, bars + RR_MAX_CHUNKS + c, p.status, p.wait_ns);
+        if (!cx.failed) ST::issue(p, cx, knext, c, dyn, bars);
+    }
+}
+// accumulators of a reduction pass -> one value per warp, left in sv / si by lane 0
+template <class S, int NA, int V, int THREADS>
+DEV void rr_reduce_tail(float (&acc)[NA][V], int (&acci)[NA][V], float* a, int* ai,
+                        float (*sv)[THREADS / 32], int (*si)[THREADS / 32]) {
+    constexpr int NR = S::NRED;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    lanes_to_thread<S, NA, V>(acc, acci, a, ai);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) shfl_merge<S, NA>(a, ai, o);
+    if (lane == 0) {
+#pragma unroll
+        for (int r = 0; r < NR; ++r) { sv[r][warp] = a[r]; if (red_is_arg(S::op(r))) si[r][warp] = ai[r]; }
+    }
 }
 
 // One pass over this block's slice, chunk by chunk (operands already point at shared memory).
@@ -1018,7 +1089,6 @@ DEV void rr_pass(const P& q, const P& p, i64 k, i64 knext, RowCtx& cx, unsigned 
     typedef SV<V> S;
     constexpr int NR = S::NRED;
     constexpr int NA = NR > 0 ? NR : 1;
-    const int tid = threadIdx.x;
     float acc[NA][V]; int acci[NA][V];
 #pragma unroll
     for (int r = 0; r < NR; ++r)
@@ -1029,63 +1099,48 @@ DEV void rr_pass(const P& q, const P& p, i64 k, i64 knext, RowCtx& cx, unsigned 
     const u32 nfull = (cx.v1 - cx.v0) / cx.cv;       // chunks in which every thread has all its vectors
     for (u32 c = 0; c < cx.nc; ++c) {
         if constexpr (WAIT) rr_wait_chunk(cx, bars + c, p.status, p.wait_ns);
-        const u32 vb = cx.v0 + c * cx.cv + tid;
-        typename S::L l[UNROLL];
-        if (c < nfull) {                             // no bounds checks
+        rr_chunk<S, P, NA, V, THREADS, UNROLL>(q, h, k, cx, c, nfull, acc, acci);
+        if constexpr (RELEASE) rr_release_chunk<ST>(p, cx, knext, c, dyn, bars);
+    }
+    if constexpr (NR > 0) rr_reduce_tail<S, NA, V, THREADS>(acc, acci, a, ai, sv, si);
+}
+
+// The last, element-wise pass of row k and the first, reduction pass of row knext in one loop.
+// The element-wise pass hands each chunk it has finished to the copies of the next row; the
+// reduction pass follows LAG chunks behind, so that by the time it asks for a chunk the copy
+// has had LAG chunks' worth of work to land.  Run one after the other, the first pass of a row
+// would spend most of its time waiting for copies that could only be started late in the
+// previous row's last pass.  The first pass of a row reads nothing an earlier pass produced,
+// so its hoisted values come from tensors only (row knext).
+template <template <int> class SVE, template <int> class SV0, class ST, class P, int V, int THREADS, int UNROLL, int LAG>
+DEV void rr_pass_overlap(const P& q, const P& p, i64 k, i64 knext, RowCtx& cx, unsigned char* dyn, u64* bars,
+                         float* a, int* ai, float (*sv)[THREADS / 32], int (*si)[THREADS / 32]) {
+    typedef SVE<V> SE;
+    typedef SV0<V> S0;
+    constexpr int NR = S0::NRED;
+    float acc[NR][V]; int acci[NR][V];
 #pragma unroll
-            for (int u = 0; u < UNROLL; ++u) S::load_l(q, k, (i64)((vb + u * THREADS) * (u32)V), l[u]);
+    for (int r = 0; r < NR; ++r)
 #pragma unroll
-            for (int u = 0; u < UNROLL; ++u) {
-                const i64 n = (i64)((vb + u * THREADS) * (u32)V);
-                if constexpr (NR == 0) {
-                    float out[1][V];
-                    S::eval(q, h, l[u], k, n, out);
-                    S::store(q, k, n, out[0]);
-                } else {
-                    accumulate<S, P, NA, V>(q, h, l[u], k, n, (int)n, 1, acc, acci);
-                }
-            }
-        } else {
-#pragma unroll
-            for (int u = 0; u < UNROLL; ++u)
-                if (vb + u * THREADS < cx.v1) S::load_l(q, k, (i64)((vb + u * THREADS) * (u32)V), l[u]);
-#pragma unroll
-            for (int u = 0; u < UNROLL; ++u) {
-                if (vb + u * THREADS < cx.v1) {
-                    const i64 n = (i64)((vb + u * THREADS) * (u32)V);
-                    if constexpr (NR == 0) {
-                        float out[1][V];
-                        S::eval(q, h, l[u], k, n, out);
-                        S::store(q, k, n, out[0]);
-                    } else {
-                        accumulate<S, P, NA, V>(q, h, l[u], k, n, (int)n, 1, acc, acci);
-                    }
-                }
-            }
+        for (int i = 0; i < V; ++i) { acc[r][i] = red_init(S0::op(r)); acci[r][i] = red_init_idx(S0::op(r)); }
+    float none[1][V]; int nonei[1][V];
+    typename SE::H he;
+    SE::load_h(q, k, he);
+    typename S0::H h0;
+    S0::load_h(q, knext, h0);
+    const u32 nfull = (cx.v1 - cx.v0) / cx.cv;
+    const u32 next_parity = cx.phase ^ 1u;
+    for (u32 c = 0; c < cx.nc + LAG; ++c) {
+        if (c < cx.nc) {
+            rr_chunk<SE, P, 1, V, THREADS, UNROLL>(q, he, k, cx, c, nfull, none, nonei);
+            rr_release_chunk<ST>(p, cx, knext, c, dyn, bars);
         }
-        if constexpr (RELEASE) {
-            // each warp reports that it is done with chunk c; thread 0 alone waits for all of
-            // them (bounded) and then starts the next row's copies into the chunk, so the
-            // other warps run on into the next chunk without a block-wide barrier
-            __syncwarp();
-            if ((tid & 31) == 0) mbar_arrive(bars + RR_MAX_CHUNKS + c);
-            if (tid == 0 && knext < p.K) {
-                rr_wait_chunk(cx, bars + RR_MAX_CHUNKS + c, p.status, p.wait_ns);
-                if (!cx.failed) ST::issue(p, cx, knext, c, dyn, bars);
-            }
+        if (c >= LAG) {
+            rr_wait_parity(cx, bars + (c - LAG), next_parity, p.status, p.wait_ns);
+            rr_chunk<S0, P, NR, V, THREADS, UNROLL>(q, h0, knext, cx, c - LAG, nfull, acc, acci);
         }
     }
-    if constexpr (NR > 0) {
-        // lanes of a thread, then the threads of a warp; lane 0 leaves the warp's result in sv/si
-        const int warp = tid >> 5, lane = tid & 31;
-        lanes_to_thread<S, NA, V>(acc, acci, a, ai);
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) shfl_merge<S, NA>(a, ai, o);
-        if (lane == 0) {
-#pragma unroll
-            for (int r = 0; r < NR; ++r) { sv[r][warp] = a[r]; if (red_is_arg(S::op(r))) si[r][warp] = ai[r]; }
-        }
-    }
+    rr_reduce_tail<S0, NR, V, THREADS>(acc, acci, a, ai, sv, si);
 }
 
 // Block results of one pass -> row result, left in res[0..NR) (value bits, or the index for arg

@@ -562,6 +562,8 @@ class Planner(object):
         self.smem_cap = 200 * 1024         # dynamic shared memory a row-resident block may ask for
         self.rowres_slice_cap = 100 * 1024 # preferred largest slice of a row per block (two blocks per SM)
         self.rowres_unroll = 2             # vectors per thread and chunk in the row-resident kernel
+        self.rowres_overlap = True         # first pass of the next row rides along with the last pass of this one
+        self.rowres_lag = 2                # ... this many chunks behind
         self.rowres_threads = None         # cap on its block size (None: as many as the registers allow)
         self.status_ptr = 0                # device int the kernels set when a bounded wait gives up
         self.wait_limit_ns = 2000000000    # how long a block waits for its staged row slice
@@ -888,19 +890,32 @@ class Planner(object):
         for r in reds:
             if ("r%d" % r.nid) in f.values:
                 body.append("q.r%d = (u64)&s_res[%d]; q.r%d_sk = 0; q.r%d_sn = 0;" % (r.nid, slot_of[r.nid], r.nid, r.nid))
+        # The first pass of a row needs nothing but the row itself, so when the last pass is
+        # element-wise the two share a loop (rr_pass_overlap): the last pass of row k hands its
+        # finished chunks to the copies of row k + 1 and the first pass of row k + 1 follows a
+        # few chunks behind.  Only the very first row of a cluster runs its first pass alone.
+        overlap = bool(self.rowres_overlap) and not red_out
+        body.append("float a[%d]; int ai[%d];" % (nrmax, nrmax))
+        if overlap:
+            body.append("bool first_done = false;")
         body.append("for (i64 k = kfirst; k < p.K; k += kstep) {")
         body.append("    const i64 knext = k + kstep;")
-        body.append("    float a[%d]; int ai[%d];" % (nrmax, nrmax))
         dyn_cur, bars_cur = "dyn", "bars"
         for i, (em, rs, outs) in enumerate(ems):
             last = red_out and i == len(ems) - 1
-            body.append("    rr_pass<S%d, ST, P, %d, %d, %d, %s, %s>(q, p, k, knext, cx, %s, %s, a, ai, sv, si);"
-                        % (i, V, threads, unroll, "true" if i == 0 else "false", "true" if last else "false",
-                           dyn_cur, bars_cur))
+            call = ("rr_pass<S%d, ST, P, %d, %d, %d, %s, %s>(q, p, k, knext, cx, %s, %s, a, ai, sv, si);"
+                    % (i, V, threads, unroll, "true" if i == 0 else "false", "true" if last else "false",
+                       dyn_cur, bars_cur))
+            body.append("    " + ("if (!first_done) " if (overlap and i == 0) else "") + call)
             body.append("    rr_combine<S%d, P, %d, %d, %d>(q, k, cx, a, ai, sv, si, &slots[%d][0][0][0][0], &s_res[%d]);"
                         % (i, V, C, threads, i, slot_of[rs[0].nid]))
         if red_out:
             body.append("    if (threadIdx.x == 0 && cx.rank == 0) SF<%d>::epilogue(q, k, a, ai);" % V)
+        elif overlap:
+            body.append("    if (knext < p.K) { rr_pass_overlap<SE, S0, ST, P, %d, %d, %d, %d>(q, p, k, knext, cx, dyn, bars, "
+                        "a, ai, sv, si); first_done = true; }" % (V, threads, unroll, int(self.rowres_lag)))
+            body.append("    else rr_pass<SE, ST, P, %d, %d, %d, false, true>(q, p, k, knext, cx, dyn, bars, a, ai, sv, si);"
+                        % (V, threads, unroll))
         else:
             body.append("    rr_pass<SE, ST, P, %d, %d, %d, false, true>(q, p, k, knext, cx, %s, %s, a, ai, sv, si);"
                         % (V, threads, unroll, dyn_cur, bars_cur))
@@ -947,12 +962,14 @@ class Planner(object):
         reduction step should be used."""
         if any(r.op != "sum" for r in rs):
             return None
-        lines, post, fused = [], [], False
+        pre, lines, post, fused = [], [], [], False
         for j, (r, e) in enumerate(zip(rs, outs)):
             if r.extra is not None and r.extra[0] == "m2":
                 continue                                   # written with its mean slot
             half = em.half_leaf(Planner._red_operand(r))
             if r.extra is not None:                        # mean slot j, M2 slot j + 1
+                # a vector's deviations are summed in two registers and added to lane 0 of the
+                # accumulators: the pair costs two live accumulators, not 2 V
                 fused = True
                 kexpr = "__int_as_float(acci[%d][0])" % (j + 1)
                 if half is not None:
@@ -960,23 +977,23 @@ class Planner(object):
                     dexpr = "mx_sub<%s, V>(%s, i, %s)" % (DT_NAMES[half[1]], half[0], kexpr)
                 else:
                     first, dexpr = e, "(%s - %s)" % (e, kexpr)
+                pre.append("float s1v%d = 0.0f, s2v%d = 0.0f;" % (j, j))
                 lines.append("if (i == 0 && acci[%d][0] == 0) acci[%d][0] = __float_as_int(%s);" % (j, j + 1, first))
-                lines.append("{ const float d = %s; acc[%d][i] += d; acc[%d][i] = __fmaf_rn(d, d, acc[%d][i]); }"
-                             % (dexpr, j, j + 1, j + 1))
-                post.append("acci[%d][0] += V;" % j)
+                lines.append("{ const float d = %s; s1v%d += d; s2v%d = __fmaf_rn(d, d, s2v%d); }" % (dexpr, j, j, j))
+                post.append("acc[%d][0] += s1v%d; acc[%d][0] += s2v%d; acci[%d][0] += V;" % (j, j, j + 1, j, j))
             elif half is not None:
                 fused = True
                 lines.append("acc[%d][i] = mx_add<%s, V>(%s, i, acc[%d][i]);" % (j, DT_NAMES[half[1]], half[0], j))
             else:
                 lines.append("acc[%d][i] += %s;" % (j, e))
-        return (lines, post) if fused else None
+        return (pre, lines, post) if fused else None
 
     @staticmethod
     def _accum_fn(em, acc_tail, nred, ind):
         if acc_tail is None:
             return ["    enum { FUSED = 0 };"]
-        lines, post = acc_tail
-        body = list(em.e_pre)
+        pre, lines, post = acc_tail
+        body = list(em.e_pre) + list(pre)
         body.append("_Pragma(\"unroll\") for (int i = 0; i < V; ++i) {")
         body.extend("    " + x for x in em.e_lines)
         body.extend("    " + x for x in lines)
