@@ -447,7 +447,7 @@ DEV void mom_acc_one(float& s1, float& s2, int& cnt, int& kbits, float x) {
 DEV void mom_merge(float& mean, int& n, float& m2, float mean_b, int n_b, float m2_b) {
     if (n_b > 0) {
         const int na = n, nt = n + n_b;
-        const float f = (float)n_b / (float)nt;
+        const float f = (float)n_b * rcp_approx((float)nt);     // a weight: one ulp of it is far below the result's
         const float d = mean_b - mean;
         m2 = m2 + m2_b + d * d * ((float)na * f);
         mean = __fmaf_rn(d, f, mean);
@@ -470,7 +470,7 @@ DEV void lanes_to_thread(float (&acc)[NR][V], int (&acci)[NR][V], float* a, int*
             const int n = acci[r][0];
             float mean = 0.f, m2 = 0.f;
             if (n > 0) {
-                const float dm = s1 / (float)n;
+                const float dm = s1 * rcp_approx((float)n);
                 mean = __int_as_float(acci[r2][0]) + dm;
                 m2 = fmaxf(__fmaf_rn(-s1, dm, s2), 0.f);
             }
@@ -557,19 +557,20 @@ DEV void accumulate_one(const float (&out)[NR][1], int idx, float (&acc)[NR][V],
     }
 }
 
+// The work of one block: `bx` is the block's index along x, `row` its row (MODE 2 only).
 template <template <int> class SV, class P, int V, int BLOCK, int UNROLL, int MODE, bool IDX32 = false>
-DEV void ew_kernel(const P& p) {
+DEV void ew_body(const P& p, u32 bx, i64 row) {
     typedef SV<V> S;
     constexpr bool FLAT = MODE == 1 || MODE == 3;
     const i64 nvec = p.nvec;                     // vectors per row (FLAT: all vectors)
     const i64 total = MODE == 0 ? p.K * nvec : nvec;
-    const i64 base = IDX32 ? (i64)(blockIdx.x * (u32)(BLOCK * UNROLL) + threadIdx.x)
-                           : (i64)blockIdx.x * (BLOCK * UNROLL) + threadIdx.x;
+    const i64 base = IDX32 ? (i64)(bx * (u32)(BLOCK * UNROLL) + threadIdx.x)
+                           : (i64)bx * (BLOCK * UNROLL) + threadIdx.x;
     i64 krow = 0;
-    if constexpr (MODE == 2) krow = (i64)blockIdx.y + (i64)blockIdx.z * gridDim.y;
+    if constexpr (MODE == 2) krow = row;
     // MODE 3: k carries, instead of the row r itself, the amount to add to a flat index of row r to
     // get the element index in the enclosing tensor: lin_0 + r * lin_r
-    if constexpr (MODE == 3) krow = p.lin_0 + (i64)(blockIdx.x / (u32)p.flat_bpr) * p.lin_r;
+    if constexpr (MODE == 3) krow = p.lin_0 + (i64)(bx / (u32)p.flat_bpr) * p.lin_r;
     if (MODE == 2 && krow >= p.K) return;
     typename S::L l[UNROLL];
     typename S::H h[UNROLL];
@@ -598,8 +599,8 @@ DEV void ew_kernel(const P& p) {
     }
     if constexpr (FLAT && V > 1) {               // scalar tail: N % V elements
         typedef SV<1> S1;
-        const i64 t = nvec * V + (i64)blockIdx.x * BLOCK + threadIdx.x;
-        if (blockIdx.x == 0 && t < p.N) {
+        const i64 t = nvec * V + (i64)bx * BLOCK + threadIdx.x;
+        if (bx == 0 && t < p.N) {
             typename S1::L l1; typename S1::H h1;
             S1::load_l(p, 0, t, l1); S1::load_h(p, 0, h1);
             float out[1][1];
@@ -607,6 +608,11 @@ DEV void ew_kernel(const P& p) {
             S1::store(p, 0, t, out[0]);
         }
     }
+}
+
+template <template <int> class SV, class P, int V, int BLOCK, int UNROLL, int MODE, bool IDX32 = false>
+DEV void ew_kernel(const P& p) {
+    ew_body<SV, P, V, BLOCK, UNROLL, MODE, IDX32>(p, blockIdx.x, MODE == 2 ? (i64)blockIdx.y + (i64)blockIdx.z * gridDim.y : 0);
 }
 
 // ================================================================== split-reduction finish
@@ -626,16 +632,18 @@ DEV void write_partial(const P& p, i64 k, int j, i64 pj, i64 pk, const float* a,
 // ================================================================== reduce along lanes (rows)
 // TPR threads cooperate on one kept index; BLOCK/TPR indices per block.
 // TPR == BLOCK: one index per block and the row may be split over p.split blocks.
+// The work of block number `bid` of the pass.  Returns the kept index whose epilogue this block
+// has just run (its thread 0; the results of that index are complete), or -1.
 template <template <int> class SV, class P, int V, int BLOCK, int TPR, int UNROLL>
-DEV void red_rows_kernel(const P& p) {
+DEV i64 red_rows_body(const P& p, i64 bid) {
     typedef SV<V> S;
     constexpr int NR = S::NRED;
     constexpr int RPC = BLOCK / TPR;
     const int tid = threadIdx.x;
     const int sub = tid % TPR;
     i64 k; int j;
-    if constexpr (RPC == 1) { k = (i64)blockIdx.x / p.split; j = (int)((i64)blockIdx.x - k * p.split); }
-    else { k = (i64)blockIdx.x * RPC + tid / TPR; j = 0; }
+    if constexpr (RPC == 1) { k = bid / p.split; j = (int)(bid - k * p.split); }
+    else { k = bid * RPC + tid / TPR; j = 0; }
     const bool live = k < p.K;
     const i64 nvec = p.nvec;
     i64 v0 = 0, v1 = nvec;
@@ -706,11 +714,11 @@ DEV void red_rows_kernel(const P& p) {
     }
     if constexpr (RPC > 1) {
         if (live && sub == 0) { finish_slots<S, NR>(a, ai); S::epilogue(p, k, a, ai); }
-        return;
+        return -1;
     } else {
         if (p.split == 1) {
             if (tid == 0) { finish_slots<S, NR>(a, ai); S::epilogue(p, k, a, ai); }
-            return;
+            return k;
         }
         // several blocks per index: publish, count arrivals, last one combines in split order
         __shared__ int s_last;
@@ -723,7 +731,7 @@ DEV void red_rows_kernel(const P& p) {
             if (s_last) *cnt = 0;                      // leave the counter clean for the next launch
         }
         __syncthreads();
-        if (!s_last) return;
+        if (!s_last) return -1;
         __threadfence();
         if (tid < 32) {
             const float* pv = reinterpret_cast<const float*>(p.part_v);
@@ -744,7 +752,12 @@ DEV void red_rows_kernel(const P& p) {
             for (int o2 = 16; o2 > 0; o2 >>= 1) shfl_merge<S, NR>(a, ai, o2);
             if (tid == 0) { finish_slots<S, NR>(a, ai); S::epilogue(p, k, a, ai); }
         }
+        return k;
     }
+}
+template <template <int> class SV, class P, int V, int BLOCK, int TPR, int UNROLL>
+DEV void red_rows_kernel(const P& p) {
+    red_rows_body<SV, P, V, BLOCK, TPR, UNROLL>(p, (i64)blockIdx.x);
 }
 
 // ================================================================== reduce across lanes (cols)
@@ -871,6 +884,93 @@ DEV void red_cols_kernel(const P& p) {
 }
 
 
+// ================================================================== row-pipelined statements
+// A statement of two passes over the same rows -- a reduction along the rows (statistics), then
+// an element-wise pass that needs its results -- as ONE persistent kernel that keeps both passes
+// of neighbouring rows in flight: rows are taken in groups small enough for L2; while the
+// element-wise pass works on group g (its operands still in L2 from the reduction pass, so HBM
+// sees each operand once), the reduction pass already streams group g + 1 from HBM.  Blocks draw
+// work items from a ticket counter in an order in which every item's prerequisites have smaller
+// tickets:   red(group 0), red(group 1), ew(group 0), red(group 2), ew(group 1), ... ew(last).
+// A reduction item is one segment of one row (red_rows_body: the last segment to finish
+// combines the row, runs the epilogue and then publishes ready[row] = epoch); an element-wise
+// item is `tiles` neighbouring tiles of one row (ew_body, MODE 2) and first waits for ready[row].
+// That wait is the only one; whoever it waits for holds a smaller ticket, i.e. is already
+// running, and it is bounded in time all the same (status word, like the staging waits below).
+// Both passes keep their own parameter struct and generated S; PP carries the schedule.
+DEV u32 ld_acquire_u32(const u32* p) { u32 v; asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory"); return v; }
+DEV void st_release_u32(u32* p, u32 v) { asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory"); }
+DEV u64 rp_global_ns() { u64 t; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t)); return t; }
+
+template <template <int> class SA, class PA, int VA, int UA, template <int> class SB, class PB, int VB, int UB,
+          bool IDX32, class PP, int BLOCK>
+DEV void rowpipe_kernel(const PP& p) {
+    __shared__ u32 s_ticket[2];
+    const u32 K = (u32)p.a.K, R = p.group_rows;
+    const u32 SAn = (u32)p.a.split, SBn = p.items_b;          // items per row in each pass
+    const u32 G = (K + R - 1) / R;
+    const u32 total = K * SAn + K * SBn;
+    u32* ticket = reinterpret_cast<u32*>(p.ticket);
+    u32* ready = reinterpret_cast<u32*>(p.ready);
+    if (threadIdx.x == 0) s_ticket[0] = atomicAdd(ticket, 1u);
+    __syncthreads();
+    u32 t = s_ticket[0];
+    u32 par = 0;
+    while (t < total) {
+        // the next ticket is drawn while this item runs
+        if (threadIdx.x == 0) s_ticket[par ^ 1] = atomicAdd(ticket, 1u);
+        // ticket -> (pass, group, index within the group's items)
+        u32 rest = t, g = 0, phase = 0;
+        {
+            const u32 r0 = K < R ? K : R;
+            if (rest < r0 * SAn) { g = 0; phase = 0; }
+            else {
+                rest -= r0 * SAn;
+                for (g = 0; g < G; ++g) {                     // step g: red(group g + 1), then ew(group g)
+                    const u32 lo1 = (g + 1) * R, hi1 = lo1 + R < K ? lo1 + R : K;
+                    const u32 nred = lo1 < K ? (hi1 - lo1) * SAn : 0u;
+                    if (rest < nred) { g = g + 1; phase = 0; break; }
+                    rest -= nred;
+                    const u32 lo0 = g * R, hi0 = lo0 + R < K ? lo0 + R : K;
+                    const u32 new_ = (hi0 - lo0) * SBn;
+                    if (rest < new_) { phase = 1; break; }
+                    rest -= new_;
+                }
+            }
+        }
+        if (phase == 0) {
+            const i64 bid = (i64)(g * R) * SAn + rest;           // row-major (row, segment), as the plain kernel numbers its blocks
+            const i64 done = red_rows_body<SA, PA, VA, BLOCK, BLOCK, UA>(p.a, bid);
+            if (done >= 0 && threadIdx.x == 0) {
+                __threadfence();
+                st_release_u32(ready + done, p.epoch);
+            }
+        } else {
+            const u32 row = g * R + rest / SBn, first = (rest % SBn) * p.tiles_per_item;
+            if (threadIdx.x == 0) {
+                if (ld_acquire_u32(ready + row) != p.epoch) {
+                    const u64 t0 = rp_global_ns();
+                    while (ld_acquire_u32(ready + row) != p.epoch) {
+                        if (rp_global_ns() - t0 > p.wait_ns) {
+                            if (p.status) atomicExch(reinterpret_cast<int*>(p.status), 2);
+                            break;
+                        }
+                    }
+                }
+            }
+            __syncthreads();
+            for (u32 i = 0; i < p.tiles_per_item; ++i)
+                if (first + i < p.tiles_b) ew_body<SB, PB, VB, BLOCK, UB, 2, IDX32>(p.b, first + i, (i64)row);
+        }
+        __syncthreads();                                      // shared scratch of the bodies and s_ticket are free again
+        par ^= 1;
+        t = s_ticket[par];
+    }
+    // every block draws exactly one ticket >= total; the block that draws the last of them
+    // (nobody can draw after it) leaves the counter at zero for the next launch
+    if (threadIdx.x == 0 && t == total + gridDim.x - 1) *ticket = 0u;
+}
+
 // ================================================================== row-resident statements
 // A statement with several passes over the same rows (mean -> variance ->
 // normalise, row softmax ...) normally re-reads its operands from HBM once per
@@ -927,16 +1027,25 @@ DEV void mbar_expect_tx(u64* bar, u32 bytes) {
 DEV void mbar_arrive(u64* bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
+// One try: the thread may be suspended by the hardware until the phase completes or, at the
+// latest, for about RR_WAIT_HINT_NS -- so a waiting warp issues a handful of instructions per
+// hint period instead of spinning (and taking issue slots from the block it shares the SM with).
+#define RR_WAIT_HINT_NS 20000
 DEV bool mbar_try_wait(u64* bar, u32 parity) {
     u32 ok;
-    asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
-                 : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+    asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                 : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity), "r"(RR_WAIT_HINT_NS) : "memory");
     return ok != 0;
 }
 // global -> this block's shared memory, 16-byte aligned on both sides, bytes % 16 == 0
 DEV void bulk_g2s(void* dst, const void* src, u32 bytes, u64* bar) {
     asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
                  ::"r"(smem_u32(dst)), "l"(src), "r"(bytes), "r"(smem_u32(bar)) : "memory");
+}
+
+// ask L2 to fetch `bytes` (a multiple of 16, from a 16-byte aligned address) ahead of the copies
+DEV void bulk_prefetch_l2(const void* src, u32 bytes) {
+    asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(src), "r"(bytes) : "memory");
 }
 
 enum { RR_MAX_CHUNKS = 32 };
@@ -983,6 +1092,18 @@ template <class ST, class P>
 DEV void rr_issue_row(const P& p, const RowCtx& cx, i64 k, unsigned char* dyn, u64* bars) {
     if (threadIdx.x == 0 && !cx.failed)
         for (u32 c = 0; c < cx.nc; ++c) ST::issue(p, cx, k, c, dyn, bars);
+}
+// Row k's slice of one operand on its way into L2 while the block still works on the row
+// before: the staging copies, which can only start as chunks of shared memory come free late in
+// that row's last pass, then find their data in L2, and HBM has a whole row time to deliver it.
+// Warp 0 splits the slice into 8 KB pieces.
+DEV void rr_prefetch(u64 src, u32 bytes) {
+    if (threadIdx.x < 32) {
+        for (u32 off = threadIdx.x * 8192u; off < bytes; off += 32u * 8192u) {
+            const u32 n = bytes - off < 8192u ? bytes - off : 8192u;
+            bulk_prefetch_l2(reinterpret_cast<const char*>(src) + off, n);
+        }
+    }
 }
 DEV u64 global_ns() { u64 t; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t)); return t; }
 // Wait for one chunk, for at most limit_ns.  When the time runs out the thread
