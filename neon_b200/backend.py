@@ -107,14 +107,6 @@ class B200Backend(OpTreeBackend):
         self._status = rt.malloc(256)          # kernels set it when a bounded wait gives up
         rt.memset(self._status, 0, 1, 256)
         self._planner.status_ptr = self._status
-        # per-row "results are ready" words of the row-pipelined kernels: each launch publishes
-        # its own launch number, so the array never needs clearing between launches
-        self._ready_rows = 1 << 16
-        self._ready = rt.malloc(4 * self._ready_rows)
-        rt.memset(self._ready, 0, 1, 4 * self._ready_rows)
-        self._planner.ready_ptr, self._planner.ready_rows = self._ready, self._ready_rows
-        self._epoch = 0
-        self._planner.smem_cap = min(200 * 1024, props.max_smem_per_block - 24 * 1024)
         self._kernels = {}
         self._plans = {}                   # program_key -> BoundPlan
         self._temps = {}
@@ -409,12 +401,6 @@ class B200Backend(OpTreeBackend):
             pz.kernel = kernel
             if pz.setup is not None:
                 pz.setup(rt, kernel, pz)
-        if pz.uses_epoch:
-            self._epoch += 1
-            if self._epoch >= 0xFFFFFFF0:           # the launch number is about to wrap: start over
-                rt.memset(self._ready, 0, 1, 4 * self._ready_rows, self.stream)
-                self._epoch = 1
-            pz.fields.values["epoch"] = self._epoch
         if pz.uses_rng:
             k0, k1 = rt.rng_next_key()
             pz.fields.values["rk0"] = k0

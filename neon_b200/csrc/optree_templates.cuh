@@ -614,7 +614,6 @@ template <template <int> class SV, class P, int V, int BLOCK, int UNROLL, int MO
 DEV void ew_kernel(const P& p) {
     ew_body<SV, P, V, BLOCK, UNROLL, MODE, IDX32>(p, blockIdx.x, MODE == 2 ? (i64)blockIdx.y + (i64)blockIdx.z * gridDim.y : 0);
 }
-
 // ================================================================== split-reduction finish
 // Partials of reduction r, kept index k, split j live at r*K*SPLIT + j*pj + k*pk.
 template <class S, class P>
@@ -759,7 +758,6 @@ template <template <int> class SV, class P, int V, int BLOCK, int TPR, int UNROL
 DEV void red_rows_kernel(const P& p) {
     red_rows_body<SV, P, V, BLOCK, TPR, UNROLL>(p, (i64)blockIdx.x);
 }
-
 // ================================================================== reduce across lanes (cols)
 // Block = CW x RH threads (CW*RH == BLOCK).  threadIdx % CW picks V neighbouring
 // kept indices, threadIdx / CW a residue class of the reduced axis.
@@ -884,93 +882,6 @@ DEV void red_cols_kernel(const P& p) {
 }
 
 
-// ================================================================== row-pipelined statements
-// A statement of two passes over the same rows -- a reduction along the rows (statistics), then
-// an element-wise pass that needs its results -- as ONE persistent kernel that keeps both passes
-// of neighbouring rows in flight: rows are taken in groups small enough for L2; while the
-// element-wise pass works on group g (its operands still in L2 from the reduction pass, so HBM
-// sees each operand once), the reduction pass already streams group g + 1 from HBM.  Blocks draw
-// work items from a ticket counter in an order in which every item's prerequisites have smaller
-// tickets:   red(group 0), red(group 1), ew(group 0), red(group 2), ew(group 1), ... ew(last).
-// A reduction item is one segment of one row (red_rows_body: the last segment to finish
-// combines the row, runs the epilogue and then publishes ready[row] = epoch); an element-wise
-// item is `tiles` neighbouring tiles of one row (ew_body, MODE 2) and first waits for ready[row].
-// That wait is the only one; whoever it waits for holds a smaller ticket, i.e. is already
-// running, and it is bounded in time all the same (status word, like the staging waits below).
-// Both passes keep their own parameter struct and generated S; PP carries the schedule.
-DEV u32 ld_acquire_u32(const u32* p) { u32 v; asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory"); return v; }
-DEV void st_release_u32(u32* p, u32 v) { asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory"); }
-DEV u64 rp_global_ns() { u64 t; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t)); return t; }
-
-template <template <int> class SA, class PA, int VA, int UA, template <int> class SB, class PB, int VB, int UB,
-          bool IDX32, class PP, int BLOCK>
-DEV void rowpipe_kernel(const PP& p) {
-    __shared__ u32 s_ticket[2];
-    const u32 K = (u32)p.a.K, R = p.group_rows;
-    const u32 SAn = (u32)p.a.split, SBn = p.items_b;          // items per row in each pass
-    const u32 G = (K + R - 1) / R;
-    const u32 total = K * SAn + K * SBn;
-    u32* ticket = reinterpret_cast<u32*>(p.ticket);
-    u32* ready = reinterpret_cast<u32*>(p.ready);
-    if (threadIdx.x == 0) s_ticket[0] = atomicAdd(ticket, 1u);
-    __syncthreads();
-    u32 t = s_ticket[0];
-    u32 par = 0;
-    while (t < total) {
-        // the next ticket is drawn while this item runs
-        if (threadIdx.x == 0) s_ticket[par ^ 1] = atomicAdd(ticket, 1u);
-        // ticket -> (pass, group, index within the group's items)
-        u32 rest = t, g = 0, phase = 0;
-        {
-            const u32 r0 = K < R ? K : R;
-            if (rest < r0 * SAn) { g = 0; phase = 0; }
-            else {
-                rest -= r0 * SAn;
-                for (g = 0; g < G; ++g) {                     // step g: red(group g + 1), then ew(group g)
-                    const u32 lo1 = (g + 1) * R, hi1 = lo1 + R < K ? lo1 + R : K;
-                    const u32 nred = lo1 < K ? (hi1 - lo1) * SAn : 0u;
-                    if (rest < nred) { g = g + 1; phase = 0; break; }
-                    rest -= nred;
-                    const u32 lo0 = g * R, hi0 = lo0 + R < K ? lo0 + R : K;
-                    const u32 new_ = (hi0 - lo0) * SBn;
-                    if (rest < new_) { phase = 1; break; }
-                    rest -= new_;
-                }
-            }
-        }
-        if (phase == 0) {
-            const i64 bid = (i64)(g * R) * SAn + rest;           // row-major (row, segment), as the plain kernel numbers its blocks
-            const i64 done = red_rows_body<SA, PA, VA, BLOCK, BLOCK, UA>(p.a, bid);
-            if (done >= 0 && threadIdx.x == 0) {
-                __threadfence();
-                st_release_u32(ready + done, p.epoch);
-            }
-        } else {
-            const u32 row = g * R + rest / SBn, first = (rest % SBn) * p.tiles_per_item;
-            if (threadIdx.x == 0) {
-                if (ld_acquire_u32(ready + row) != p.epoch) {
-                    const u64 t0 = rp_global_ns();
-                    while (ld_acquire_u32(ready + row) != p.epoch) {
-                        if (rp_global_ns() - t0 > p.wait_ns) {
-                            if (p.status) atomicExch(reinterpret_cast<int*>(p.status), 2);
-                            break;
-                        }
-                    }
-                }
-            }
-            __syncthreads();
-            for (u32 i = 0; i < p.tiles_per_item; ++i)
-                if (first + i < p.tiles_b) ew_body<SB, PB, VB, BLOCK, UB, 2, IDX32>(p.b, first + i, (i64)row);
-        }
-        __syncthreads();                                      // shared scratch of the bodies and s_ticket are free again
-        par ^= 1;
-        t = s_ticket[par];
-    }
-    // every block draws exactly one ticket >= total; the block that draws the last of them
-    // (nobody can draw after it) leaves the counter at zero for the next launch
-    if (threadIdx.x == 0 && t == total + gridDim.x - 1) *ticket = 0u;
-}
-
 // ================================================================== row-resident statements
 // A statement with several passes over the same rows (mean -> variance ->
 // normalise, row softmax ...) normally re-reads its operands from HBM once per
@@ -1043,11 +954,6 @@ DEV void bulk_g2s(void* dst, const void* src, u32 bytes, u64* bar) {
                  ::"r"(smem_u32(dst)), "l"(src), "r"(bytes), "r"(smem_u32(bar)) : "memory");
 }
 
-// ask L2 to fetch `bytes` (a multiple of 16, from a 16-byte aligned address) ahead of the copies
-DEV void bulk_prefetch_l2(const void* src, u32 bytes) {
-    asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(src), "r"(bytes) : "memory");
-}
-
 enum { RR_MAX_CHUNKS = 32 };
 
 struct RowCtx {
@@ -1092,18 +998,6 @@ template <class ST, class P>
 DEV void rr_issue_row(const P& p, const RowCtx& cx, i64 k, unsigned char* dyn, u64* bars) {
     if (threadIdx.x == 0 && !cx.failed)
         for (u32 c = 0; c < cx.nc; ++c) ST::issue(p, cx, k, c, dyn, bars);
-}
-// Row k's slice of one operand on its way into L2 while the block still works on the row
-// before: the staging copies, which can only start as chunks of shared memory come free late in
-// that row's last pass, then find their data in L2, and HBM has a whole row time to deliver it.
-// Warp 0 splits the slice into 8 KB pieces.
-DEV void rr_prefetch(u64 src, u32 bytes) {
-    if (threadIdx.x < 32) {
-        for (u32 off = threadIdx.x * 8192u; off < bytes; off += 32u * 8192u) {
-            const u32 n = bytes - off < 8192u ? bytes - off : 8192u;
-            bulk_prefetch_l2(reinterpret_cast<const char*>(src) + off, n);
-        }
-    }
 }
 DEV u64 global_ns() { u64 t; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t)); return t; }
 // Wait for one chunk, for at most limit_ns.  When the time runs out the thread
@@ -1224,44 +1118,6 @@ DEV void rr_pass(const P& q, const P& p, i64 k, i64 knext, RowCtx& cx, unsigned 
         if constexpr (RELEASE) rr_release_chunk<ST>(p, cx, knext, c, dyn, bars);
     }
     if constexpr (NR > 0) rr_reduce_tail<S, NA, V, THREADS>(acc, acci, a, ai, sv, si);
-}
-
-// The last, element-wise pass of row k and the first, reduction pass of row knext in one loop.
-// The element-wise pass hands each chunk it has finished to the copies of the next row; the
-// reduction pass follows LAG chunks behind, so that by the time it asks for a chunk the copy
-// has had LAG chunks' worth of work to land.  Run one after the other, the first pass of a row
-// would spend most of its time waiting for copies that could only be started late in the
-// previous row's last pass.  The first pass of a row reads nothing an earlier pass produced,
-// so its hoisted values come from tensors only (row knext).
-template <template <int> class SVE, template <int> class SV0, class ST, class P, int V, int THREADS, int UNROLL, int LAG>
-DEV void rr_pass_overlap(const P& q, const P& p, i64 k, i64 knext, RowCtx& cx, unsigned char* dyn, u64* bars,
-                         float* a, int* ai, float (*sv)[THREADS / 32], int (*si)[THREADS / 32]) {
-    typedef SVE<V> SE;
-    typedef SV0<V> S0;
-    constexpr int NR = S0::NRED;
-    float acc[NR][V]; int acci[NR][V];
-#pragma unroll
-    for (int r = 0; r < NR; ++r)
-#pragma unroll
-        for (int i = 0; i < V; ++i) { acc[r][i] = red_init(S0::op(r)); acci[r][i] = red_init_idx(S0::op(r)); }
-    float none[1][V]; int nonei[1][V];
-    typename SE::H he;
-    SE::load_h(q, k, he);
-    typename S0::H h0;
-    S0::load_h(q, knext, h0);
-    const u32 nfull = (cx.v1 - cx.v0) / cx.cv;
-    const u32 next_parity = cx.phase ^ 1u;
-    for (u32 c = 0; c < cx.nc + LAG; ++c) {
-        if (c < cx.nc) {
-            rr_chunk<SE, P, 1, V, THREADS, UNROLL>(q, he, k, cx, c, nfull, none, nonei);
-            rr_release_chunk<ST>(p, cx, knext, c, dyn, bars);
-        }
-        if (c >= LAG) {
-            rr_wait_parity(cx, bars + (c - LAG), next_parity, p.status, p.wait_ns);
-            rr_chunk<S0, P, NR, V, THREADS, UNROLL>(q, h0, knext, cx, c - LAG, nfull, acc, acci);
-        }
-    }
-    rr_reduce_tail<S0, NR, V, THREADS>(acc, acci, a, ai, sv, si);
 }
 
 // Block results of one pass -> row result, left in res[0..NR) (value bits, or the index for arg

@@ -498,56 +498,10 @@ class _Fields(object):
         return packer.pack(*vals)
 
 
-class _Fanout(object):
-    """Dictionary view over several parameter-value dictionaries: reads come from the first that
-    has the key, writes go to every one that has it."""
-
-    def __init__(self, dicts):
-        self.dicts = dicts
-
-    def __contains__(self, key):
-        return any(key in d for d in self.dicts)
-
-    def __getitem__(self, key):
-        for d in self.dicts:
-            if key in d:
-                return d[key]
-        raise KeyError(key)
-
-    def __setitem__(self, key, value):
-        hit = False
-        for d in self.dicts:
-            if key in d:
-                d[key] = value
-                hit = True
-        if not hit:
-            raise KeyError(key)
-
-
-class _PipeFields(object):
-    """Parameter block of a kernel made of two passes: the two passes' blocks, then the schedule."""
-
-    def __init__(self, fa, fb, sched):
-        self.parts = (fa, fb, sched)
-        self.values = _Fanout([fa.values, fb.values, sched.values])
-
-    def names(self):
-        seen, out = set(), []
-        for f in self.parts:
-            for n in f.names():
-                if n not in seen:
-                    seen.add(n)
-                    out.append(n)
-        return out
-
-    def pack(self):
-        return b"".join(f.pack() for f in self.parts)
-
-
 class Pass(object):
     """One kernel launch of a statement."""
     __slots__ = ("source", "name", "grid", "block", "fields", "kernel", "uses_rng", "desc",
-                 "results", "kind", "smem", "cluster", "setup", "tparams", "uses_epoch")
+                 "results", "kind", "smem", "cluster", "setup")
 
     def __init__(self):
         self.kernel = None
@@ -556,8 +510,6 @@ class Pass(object):
         self.cluster = 1       # thread blocks per cluster
         self.setup = None      # callable(runtime, kernel, pass) run once after compilation
         self.results = []      # (reduction op, fp32 result address, int32 index address or 0, count)
-        self.tparams = None    # template arguments of the skeleton call (for passes merged into one kernel)
-        self.uses_epoch = False   # the launcher supplies a fresh launch number in field "epoch"
 
 
 def _red_code(r):
@@ -610,25 +562,13 @@ class Planner(object):
         self.smem_cap = 200 * 1024         # dynamic shared memory a row-resident block may ask for
         self.rowres_slice_cap = 100 * 1024 # preferred largest slice of a row per block (two blocks per SM)
         self.rowres_unroll = 2             # vectors per thread and chunk in the row-resident kernel
-        self.rowres_overlap = False        # first pass of the next row rides along with the last pass of this one
-        self.rowres_lag = 2                # ... this many chunks behind
-        self.rowres_prefetch = False       # next row's slice prefetched into L2 at the start of a row
         self.rowres_threads = None         # cap on its block size (None: as many as the registers allow)
         self.status_ptr = 0                # device int the kernels set when a bounded wait gives up
-        self.ready_rows = 0                # entries of the per-row ready array
         self.wait_limit_ns = 2000000000    # how long a block waits for its staged row slice
         self.debug_starve_bytes = 0        # tests only: announce this many bytes that never arrive
         self.ew_unroll = 4
         self.ew_min_blocks = None          # None: 5 for instruction-heavy statements, else 4
         self.fuse_moments = True           # sum(e) and sum(sqr(e - m)) in one pass when m needs sum-level results
-        self.rowpipe = True                # reduction pass + element-wise pass as one persistent, L2-pipelined kernel
-        self.rowpipe_first = True          # ... preferred to the row-resident cluster kernel where both apply
-        self.rowpipe_min_bytes = 48 << 20  # ... for statements whose full-size inputs exceed this (smaller ones sit in L2 anyway)
-        self.rowpipe_group_bytes = 12 << 20   # input bytes of the rows between a row's two passes
-        self.rowpipe_seg_bytes = 96 << 10  # input bytes per reduction work item
-        self.rowpipe_tiles = 4             # element-wise tiles per work item
-        self.rowpipe_blocks = 4            # resident blocks per SM
-        self.ready_ptr = 0                 # device array of per-row launch numbers (set by the backend)
 
     # ---- helpers on the frame: K = kept axis, N = loop axis
     def plan(self, st, scratch, rounding=0, fuse_final=True, lin=None):
@@ -649,15 +589,8 @@ class Planner(object):
         full_shape = self._full_shape(st)
         root_is_k = st.root.shape[ra] == 1
         out_is_k = st.out_shape[ra] == 1
-        def try_rowres():
-            if fuse_final and levels and self.rowres:
-                return self._rowres_pass(st, reds, levels, ka, ra, full_shape, rounding, root_is_k and out_is_k)
-
-        def try_rowpipe():
-            if fuse_final and self.rowpipe and len(levels) == 1 and not (root_is_k and out_is_k) and self._lin is None:
-                return self._rowpipe_pass(st, _pair_order(reds), ka, ra, full_shape, scratch, rounding)
-        for attempt in ((try_rowpipe, try_rowres) if self.rowpipe_first else (try_rowres, try_rowpipe)):
-            pz = attempt()
+        if fuse_final and levels and self.rowres:
+            pz = self._rowres_pass(st, reds, levels, ka, ra, full_shape, rounding, root_is_k and out_is_k)
             if pz is not None:
                 return [pz]
         for lv in levels:
@@ -778,75 +711,6 @@ class Planner(object):
                          "%s = __fmaf_rn(dm * dm, %s, r[%d]); }" % (name, i1, n_expr, mref, name, n_expr, i2))
             names[r.nid] = name
         return lines, names
-
-    # ---- row-pipelined statement: reduction pass + element-wise pass in one kernel ----
-    def _rowpipe_pass(self, st, reds, ka, ra, full_shape, scratch, rounding):
-        """One persistent kernel for [a reduction pass along long rows, an element-wise pass that
-        uses its results] (rowpipe_kernel in the header): both passes are planned as usual and
-        their generated structs placed side by side; work items are segments of rows.  Returns
-        None when the statement is not of that shape, is small enough to live in L2 anyway, or
-        has no room for the per-row ready flags."""
-        K, N = full_shape[ka], full_shape[ra]
-        if not self.ready_ptr or K > self.ready_rows or K < 2:
-            return None
-        in_bytes = sum(DT_SIZE[o.dt] for o in st.operands if o.shape[ka] > 1 and o.shape[ra] > 1)
-        if in_bytes * K * N < self.rowpipe_min_bytes:
-            return None
-        res_buf = {}
-        for r in reds:
-            res_buf[r.nid] = (scratch(4 * K, False), scratch(4 * K, False) if r.op.startswith("arg") else 0)
-        pa = self._reduction_pass(st, reds, res_buf, ka, ra, full_shape, scratch, False,
-                                  seg_bytes=self.rowpipe_seg_bytes)
-        if pa.kind != "red_rows" or pa.tparams["tpr"] != BLOCK:
-            return None
-        pb = self._ew_pass(st, res_buf, ka, ra, rounding)
-        tb = pb.tparams
-        if pb.kind != "ew_2d" or tb["mode"] != 2 or tb["K"] != K:
-            return None
-        ta = pa.tparams
-
-        def body_of(src):
-            lines = src.split("\n")
-            assert lines[0].startswith("#include") and lines[1].startswith("using namespace")
-            end = max(i for i, ln in enumerate(lines) if ln.startswith('extern "C"'))
-            return "\n".join(lines[2:end])
-        tiles_b = (tb["nvec"] + BLOCK * tb["unroll"] - 1) // (BLOCK * tb["unroll"])
-        per_item = max(1, min(int(self.rowpipe_tiles), tiles_b))
-        items_b = (tiles_b + per_item - 1) // per_item
-        row_bytes = in_bytes * N
-        group = int(max(1, min(K, self.rowpipe_group_bytes // max(row_bytes, 1))))
-        fs = _Fields()
-        fs.u64("ticket", scratch(4, True))
-        fs.u64("ready", self.ready_ptr)
-        fs.u64("status", self.status_ptr)
-        fs.u64("wait_ns", int(self.wait_limit_ns))
-        fs.u32("epoch", 0)
-        fs.u32("group_rows", group)
-        fs.u32("items_b", items_b)
-        fs.u32("tiles_b", tiles_b)
-        fs.u32("tiles_per_item", per_item)
-        members = "\n".join("    %s %s;" % (c, n) for c, _, n in fs.f8 + fs.f4) + ("\n    int pad_;" if len(fs.f4) % 2 else "")
-        text = ('#include "optree_templates.cuh"\nusing namespace b200;\n'
-                "namespace pa {\n%s\n}\nnamespace pb {\n%s\n}\n"
-                "struct PP {\n    pa::P a;\n    pb::P b;\n%s\n};\n" % (body_of(pa.source), body_of(pb.source), members))
-        import zlib
-        name = "ot_rowpipe_kernel_%08x" % (zlib.crc32(text.encode()) & 0xFFFFFFFF)
-        nblk = int(self.rowpipe_blocks)
-        text += ('extern "C" __global__ void __launch_bounds__(%d, %d) %s(const __grid_constant__ PP p) { '
-                 "rowpipe_kernel<pa::S, pa::P, %d, %d, pb::S, pb::P, %d, %d, %s, PP, %d>(p); }\n"
-                 % (BLOCK, nblk, name, ta["V"], ta["unroll"], tb["V"], tb["unroll"],
-                    "true" if tb["idx32"] else "false", BLOCK))
-        pz = Pass()
-        pz.kind = "rowpipe"
-        pz.name, pz.source = name, text
-        pz.fields = _PipeFields(pa.fields, pb.fields, fs)
-        pz.block = (BLOCK, 1, 1)
-        pz.grid = (self.sm_count * nblk, 1, 1)
-        pz.uses_rng = pb.uses_rng
-        pz.uses_epoch = True
-        pz.desc = "rowpipe K=%d N=%d group=%d red[V=%d split=%d] ew[V=%d tiles=%d x%d] grid=%s" % (
-            K, N, group, ta["V"], ta["split"], tb["V"], tiles_b, per_item, pz.grid)
-        return pz
 
     # ---- row-resident statement: all passes in one cluster kernel -------------------
     def _rowres_pass(self, st, reds, levels, ka, ra, full_shape, rounding, red_out):
@@ -1005,14 +869,8 @@ class Planner(object):
             isz = DT_SIZE[o.dt]
             issue.append("rr_copy(dyn + p.off_%s + e0 * %du, p.%s + (u64)((k * p.%s_sk + n0) * %d), ne * %du, bars + c);"
                          % (pre, isz, pre, pre, isz, isz))
-        pref = ["const u32 seg = (cx.v1 - cx.v0) * %du;" % V, "const i64 n0 = (i64)cx.v0 * %d;" % V]
-        for pre, o in sorted(staged.items()):
-            isz = DT_SIZE[o.dt]
-            pref.append("rr_prefetch(p.%s + (u64)((k * p.%s_sk + n0) * %d), seg * %du);" % (pre, pre, isz, isz))
         parts.append("struct ST {\n    static DEV void issue(const P& p, const RowCtx& cx, i64 k, u32 c, "
-                     "unsigned char* dyn, u64* bars) {\n        " + "\n        ".join(issue) + "\n    }\n"
-                     "    static DEV void prefetch(const P& p, const RowCtx& cx, i64 k) {\n        "
-                     + "\n        ".join(pref) + "\n    }\n};")
+                     "unsigned char* dyn, u64* bars) {\n        " + "\n        ".join(issue) + "\n    }\n};")
 
         body = []
         body.append("extern __shared__ __align__(128) unsigned char dyn[];")
@@ -1030,34 +888,19 @@ class Planner(object):
         for r in reds:
             if ("r%d" % r.nid) in f.values:
                 body.append("q.r%d = (u64)&s_res[%d]; q.r%d_sk = 0; q.r%d_sn = 0;" % (r.nid, slot_of[r.nid], r.nid, r.nid))
-        # The first pass of a row needs nothing but the row itself, so when the last pass is
-        # element-wise the two share a loop (rr_pass_overlap): the last pass of row k hands its
-        # finished chunks to the copies of row k + 1 and the first pass of row k + 1 follows a
-        # few chunks behind.  Only the very first row of a cluster runs its first pass alone.
-        overlap = bool(self.rowres_overlap) and not red_out
-        body.append("float a[%d]; int ai[%d];" % (nrmax, nrmax))
-        if overlap:
-            body.append("bool first_done = false;")
         body.append("for (i64 k = kfirst; k < p.K; k += kstep) {")
         body.append("    const i64 knext = k + kstep;")
-        if self.rowres_prefetch:
-            body.append("    if (knext < p.K) ST::prefetch(p, cx, knext);")
+        body.append("    float a[%d]; int ai[%d];" % (nrmax, nrmax))
         dyn_cur, bars_cur = "dyn", "bars"
         for i, (em, rs, outs) in enumerate(ems):
             last = red_out and i == len(ems) - 1
-            call = ("rr_pass<S%d, ST, P, %d, %d, %d, %s, %s>(q, p, k, knext, cx, %s, %s, a, ai, sv, si);"
-                    % (i, V, threads, unroll, "true" if i == 0 else "false", "true" if last else "false",
-                       dyn_cur, bars_cur))
-            body.append("    " + ("if (!first_done) " if (overlap and i == 0) else "") + call)
+            body.append("    rr_pass<S%d, ST, P, %d, %d, %d, %s, %s>(q, p, k, knext, cx, %s, %s, a, ai, sv, si);"
+                        % (i, V, threads, unroll, "true" if i == 0 else "false", "true" if last else "false",
+                           dyn_cur, bars_cur))
             body.append("    rr_combine<S%d, P, %d, %d, %d>(q, k, cx, a, ai, sv, si, &slots[%d][0][0][0][0], &s_res[%d]);"
                         % (i, V, C, threads, i, slot_of[rs[0].nid]))
         if red_out:
             body.append("    if (threadIdx.x == 0 && cx.rank == 0) SF<%d>::epilogue(q, k, a, ai);" % V)
-        elif overlap:
-            body.append("    if (knext < p.K) { rr_pass_overlap<SE, S0, ST, P, %d, %d, %d, %d>(q, p, k, knext, cx, dyn, bars, "
-                        "a, ai, sv, si); first_done = true; }" % (V, threads, unroll, int(self.rowres_lag)))
-            body.append("    else rr_pass<SE, ST, P, %d, %d, %d, false, true>(q, p, k, knext, cx, dyn, bars, a, ai, sv, si);"
-                        % (V, threads, unroll))
         else:
             body.append("    rr_pass<SE, ST, P, %d, %d, %d, false, true>(q, p, k, knext, cx, %s, %s, a, ai, sv, si);"
                         % (V, threads, unroll, dyn_cur, bars_cur))
@@ -1550,7 +1393,7 @@ class Planner(object):
             o._frame_strides = (sk, sn)
 
     # ---- passes -----------------------------------------------------------------
-    def _reduction_pass(self, st, reds, res_buf, ka, ra, full_shape, scratch, final, seg_bytes=None):
+    def _reduction_pass(self, st, reds, res_buf, ka, ra, full_shape, scratch, final):
         K, N = full_shape[ka], full_shape[ra]
         self._frame(st, ka, ra)
         # orientation: lanes along N when the loop axis is the contiguous one
@@ -1631,11 +1474,7 @@ class Planner(object):
             nvec = N // V
             if nvec >= 2 * BLOCK or (K * 8 <= self.target and nvec > 32):
                 TPR = BLOCK
-                if seg_bytes:                      # caller wants work items of about this many input bytes
-                    row_bytes = N * sum(DT_SIZE[o.dt] for o, _ in em.lane_ops)
-                    split = max(1, min(nvec // (BLOCK * 4), (row_bytes + seg_bytes - 1) // seg_bytes))
-                else:
-                    split = self._pick_split(K, nvec // (BLOCK * 4))
+                split = self._pick_split(K, nvec // (BLOCK * 4))
                 seg = (nvec + split - 1) // split
                 split = max(1, (nvec + seg - 1) // seg)
                 grid = (K * split, 1, 1)
@@ -1669,8 +1508,6 @@ class Planner(object):
         pz.source, pz.fields, pz.grid, pz.block = src, f, grid, (BLOCK, 1, 1)
         pz.uses_rng = em.uses_rng
         pz.desc = "%s V=%d K=%d N=%d split=%d grid=%s" % (pz.kind, V, K, N, split, grid)
-        pz.tparams = {"V": V, "unroll": unroll, "split": split, "K": K,
-                      "tpr": None if lanes_on_k else TPR}
         return pz
 
     def _ew_pass(self, st, res_buf, ka0, ra0, rounding):
@@ -1780,7 +1617,6 @@ class Planner(object):
         pz.source, pz.fields, pz.grid, pz.block = src, f, grid, (BLOCK, 1, 1)
         pz.uses_rng = em.uses_rng
         pz.desc = "%s V=%d K=%d N=%d grid=%s" % (pz.kind, V, K, N, grid)
-        pz.tparams = {"V": V, "unroll": unroll, "mode": mode, "idx32": idx32, "nvec": nvec, "K": K}
         if "lin_r" in f.values:
             # linear element index = row * ncols + col of the output tensor
             f.values["lin_r"] = st.out_shape[1] if not st.flat else 0

@@ -46,8 +46,6 @@ class DryRunBackend(B200Backend):
         self.bench = False
         self.trace = []
         self._next = 0x7F0000000000
-        self._planner.ready_ptr, self._planner.ready_rows = 0x7E0000000000, 1 << 16
-        self._planner.status_ptr = 0x7E0000100000
         self.launches = 0
         self.passes = []            # every Pass planned so far
         self.sources = {}           # source -> image size

@@ -76,22 +76,9 @@ def test_mean_and_centred_squares_share_one_pass():
     assert [p.kind for p in be.passes] == ["red_cols", "red_cols"]
 
 
-def test_large_two_pass_row_statements_become_one_pipelined_kernel():
-    be = DryRunBackend()
-    _run_dry(be, cfg4(256, 401408))          # 205 MB of input: reduction + element-wise pass in one kernel
-    assert [p.kind for p in be.passes] == ["rowpipe"]
-    pz = be.passes[0]
-    assert pz.uses_epoch and "rowpipe_kernel<pa::S, pa::P" in pz.source
-    assert len(pz.fields.pack()) % 8 == 0
-    be.passes = []
-    _run_dry(be, cfg4(64, 100352))           # 12.8 MB: stays in L2 between two launches anyway
-    assert "rowpipe" not in [p.kind for p in be.passes]
-
-
 def test_rows_that_fit_cluster_shared_memory_become_one_row_resident_kernel():
     be = DryRunBackend()
     be.compile = False
-    be._planner.rowpipe = False
     _run_dry(be, cfg4(256, 401408))          # 802,816-byte rows: eight blocks of 100,352 bytes, two per SM
     assert [p.kind for p in be.passes] == ["rowres"]
     pz = be.passes[0]

@@ -91,76 +91,11 @@ def test_row_resident_cluster_kernel_matches_checker(case, b200):
     """Statements whose rows fit in cluster shared memory run as one kernel (TMA-staged
     rows, reductions exchanged through distributed shared memory)."""
     b200.launch_log = []
-    b200._planner.rowpipe = False
-    b200._plans.clear()
-    try:
-        got = cases.run_case(b200, case)
-    finally:
-        b200._planner.rowpipe = True
-        b200._plans.clear()
+    got = cases.run_case(b200, case)
     kinds = [k for k, _ in b200.launch_log]
     b200.launch_log = None
     assert kinds == ["rowres"], kinds
     b200.check_status()
-    _compare(case, got, _oracle64(case))
-
-
-def _rowpipe_cases():
-    def in1(shape, dtype=np.float32, scale=1.0):
-        return lambda rng: {"x": (scale * rng.uniform(-1, 1, shape)).astype(dtype)}
-
-    def std_rows(be, t):
-        x = t["x"]
-        t["out"][:] = (x - be.mean(x, axis=1)) / (be.std(x, axis=1) + 1e-3)
-
-    def norm_rows(be, t):
-        x = t["x"]
-        t["out"][:] = x / be.sum(be.absolute(x), axis=1)
-
-    def center_argmax(be, t):
-        x = t["x"]
-        t["out"][:] = (x - be.max(x, axis=1)) * be.argmax(x, axis=1)
-
-    return [cases.cfg4(256, 56 * 56 * 128), cases.cfg4(37, 1000000),
-            cases.Case("standardise_rows_f32_1000x20000", in1((1000, 20000)), {"out": ((1000, 20000), np.float32)}, std_rows),
-            cases.Case("l1_normalise_rows_f16_3x9000008", in1((3, 9000008), np.float16), {"out": ((3, 9000008), np.float16)}, norm_rows),
-            cases.Case("shift_by_max_times_argmax_64x300000", in1((64, 300000)), {"out": ((64, 300000), np.float32)}, center_argmax)]
-
-
-@pytest.mark.parametrize("case", _rowpipe_cases(), ids=lambda c: c.name)
-def test_row_pipelined_kernel_matches_checker(case, b200):
-    """Large statements of one reduction pass along the rows plus an element-wise pass run as
-    one persistent kernel (row groups pipelined through L2, per-row ready flags)."""
-    b200.launch_log = []
-    got = cases.run_case(b200, case)
-    kinds = [k for k, _ in b200.launch_log]
-    b200.launch_log = None
-    assert kinds == ["rowpipe"], kinds
-    b200.check_status()
-    _compare(case, got, _oracle64(case))
-    # twice more: the ticket counter must be back at zero and the ready flags must not carry over
-    for _ in range(2):
-        again = cases.run_case(b200, case)
-        for k in case.outputs:
-            assert np.array_equal(again[k], got[k]), k
-
-
-@pytest.mark.parametrize("shape,dtype", [((128, 4098), np.float32), ((128, 8196), np.float16),
-                                         ((128, 1026), np.float32), ((128, 2052), np.float16)])
-def test_rows_off_16_byte_boundaries_take_the_multi_pass_kernels(shape, dtype, b200):
-    """Row lengths that would put staged rows on 8-byte boundaries (bulk copies need 16) must
-    not reach the row-resident kernel, and must still give the right answer."""
-    def run(be, t):
-        x = t["x"]
-        t["out"][:] = (x - be.mean(x, axis=1)) / (be.std(x, axis=1) + 1e-3)
-    case = cases.Case("standardise_rows_%dx%d_%s" % (shape + (np.dtype(dtype).name,)),
-                      lambda rng: {"x": rng.uniform(-1, 1, shape).astype(dtype)},
-                      {"out": (shape, np.float32)}, run)
-    b200.launch_log = []
-    got = cases.run_case(b200, case)
-    kinds = [k for k, _ in b200.launch_log]
-    b200.launch_log = None
-    assert "rowres" not in kinds, kinds
     _compare(case, got, _oracle64(case))
 
 
