@@ -250,6 +250,17 @@ b200_status b200_allreduce(uint64_t comm, uint64_t send, uint64_t recv, uint64_t
 b200_status b200_allgather(uint64_t comm, uint64_t send, uint64_t recv, uint64_t send_bytes,
                            uint64_t stream);
 
+/* ---- exchange areas: peer-mapped device memory for reductions that finish across GPUs
+ * inside the reduction kernel (no counterpart in the reference tree, as above).  Collective
+ * over `comm`: every rank allocates `bytes` (zeroed) on its device, the CUDA IPC handles
+ * travel over the communicator, every rank maps the others' areas.  *local is this rank's
+ * area; *table is a device array of n_ranks addresses, entry r = rank r's area as this device
+ * addresses it.  Kernels write partial results and a launch number into the peers' areas with
+ * plain stores over NVLink and read only their own area; they never wait without a time limit. */
+b200_status b200_xchg_create(uint64_t comm, int32_t n_ranks, int32_t rank, uint64_t bytes,
+                             uint64_t *local, uint64_t *table);
+b200_status b200_xchg_destroy(uint64_t local);
+
 #ifdef __cplusplus
 }
 #endif

@@ -12,7 +12,7 @@ lookup tables) raise ``NotImplementedError``.
 import numpy as np
 
 from . import runtime as rt
-from .lowering import BoundPlan, Planner, Statement, dtype_code, program_key
+from .lowering import BoundPlan, MixedExtents, Planner, Statement, dtype_code, program_key
 from .optree import OpCollection, OpTreeBackend, OpTreeNode, Tensor
 from .tensor import B200Tensor
 
@@ -116,6 +116,7 @@ class B200Backend(OpTreeBackend):
         self.launch_log = None             # set to a list to record (kind, desc) per launch
         self.trace = []                    # with bench=True: one record per launch (name, geometry, ms)
         self._trace_events = None
+        self._timeline, self._timeline_pool = None, []
         self.hist_bins, self.hist_offset = None, None
         self.set_hist_buffers(hist_bins, hist_offset)
         super(B200Backend, self).__init__(rng_seed, default_dtype, compat_mode=compat_mode,
@@ -201,8 +202,11 @@ class B200Backend(OpTreeBackend):
                     simple = False
                     break
         if simple:
-            self._run_stack(out, stack)
-            return out
+            try:
+                self._run_stack(out, stack)
+                return out
+            except MixedExtents:
+                pass                            # same axis, different lengths: split below
         stmts = []
         self._temps_used = {}
         expr, tag = self._split(rhs, stmts)
@@ -287,6 +291,19 @@ class B200Backend(OpTreeBackend):
                 todo.extend(c for c in n[1:] if c is not None)
         return None
 
+    @staticmethod
+    def _red_extent(node, axis):
+        """Elements per result of the outermost reduction(s) along ``axis`` under ``node``."""
+        todo = [node]
+        while todo:
+            n = todo.pop()
+            if isinstance(n, OpTreeNode):
+                if n[0]["op"] in OpCollection.reduction_ops and n[0].get("axis") == axis:
+                    child = n[1]
+                    return int(child.shape[axis]) if hasattr(child, "shape") else 1
+                todo.extend(c for c in n[1:] if c is not None)
+        return None
+
     def _split(self, node, stmts):
         """Returns (expression, tag): tag is None (no reduction inside), 0/1 (reduces
         along that axis) or 'flat' (contains a fused whole-tensor reduction and only
@@ -352,6 +369,9 @@ class B200Backend(OpTreeBackend):
             # whole-tensor reductions of tensors of different sizes (the squared-gradient norm
             # over all layers, optimizers/optimizer.py:72-96): they cannot share a pass
             left, lt = self._materialise(left, (1, 1), stmts), None
+        if lt in (0, 1) and rt_ == lt and self._red_extent(left, lt) != self._red_extent(right, lt):
+            # both sides reduce along the same axis but over different numbers of elements
+            left, lt = self._materialise(left, left.shape, stmts), None
         if lt is not None and rt_ is not None and lt != rt_:
             # two sides reduce differently: evaluate one of them first.  A flat side
             # is a (1,1) value; otherwise the side reducing along axis 0 goes first
@@ -409,8 +429,11 @@ class B200Backend(OpTreeBackend):
             if self._trace_events is None:
                 self._trace_events = (rt.event_create(), rt.event_create())
             rt.event_record(self._trace_events[0], self.stream)
+        mark = self._timeline_begin("kernel", pz.name) if self._timeline is not None else None
         rt.launch(kernel, pz.grid, pz.block, pz.fields.pack(), smem=pz.smem, stream=self.stream,
                   cluster=pz.cluster)
+        if mark is not None:
+            rt.event_record(mark, self.stream)
         if self.bench:
             # per-launch timing, as be.bench does in the reference (float_ew.py:917-938); the
             # records stay in self.trace (newest last, bounded) and dump_trace() writes them out
@@ -635,6 +658,30 @@ class B200Backend(OpTreeBackend):
     def get_time(self, start, end):
         return rt.event_elapsed_ms(start, end)
 
+    # a timeline is lighter than bench=True: events around every launch (and, in the sharded
+    # backend, every collective), read back only when it is stopped
+    def start_timeline(self):
+        self._timeline = []
+
+    def _timeline_begin(self, kind, name):
+        """Record the start event of an interval; returns the event to record at its end."""
+        pool = self._timeline_pool
+        ev0 = pool.pop() if pool else rt.event_create()
+        ev1 = pool.pop() if pool else rt.event_create()
+        rt.event_record(ev0, self.stream)
+        self._timeline.append((kind, name, ev0, ev1))
+        return ev1
+
+    def stop_timeline(self):
+        """[(kind, name, ms)] of everything issued since start_timeline()."""
+        self.synchronize()
+        out = []
+        for kind, name, ev0, ev1 in self._timeline:
+            out.append((kind, name, rt.event_elapsed_ms(ev0, ev1)))
+            self._timeline_pool.extend((ev0, ev1))
+        self._timeline = None
+        return out
+
     def dump_trace(self, path):
         """Write the per-launch records collected with ``bench=True`` as JSON."""
         import json
@@ -651,7 +698,9 @@ class B200Backend(OpTreeBackend):
         rt.memcpy_d2h(flag.ctypes.data, self._status, 4, self.stream, sync=True)
         if flag[0]:
             rt.memset(self._status, 0, 1, 4, self.stream)
-            raise rt.B200Error(-6, "a kernel gave up waiting for its shared-memory staging copy")
+            what = [msg for bit, msg in ((1, "its shared-memory staging copy"),
+                                         (4, "the results of another GPU (exchange area)")) if flag[0] & bit]
+            raise rt.B200Error(-6, "a kernel gave up waiting for " + " and ".join(what or ["(unknown)"]))
 
     # ------------------------------------------------------------------ not on the op-tree path
     def _off_path(self, *a, **k):

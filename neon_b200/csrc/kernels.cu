@@ -28,7 +28,7 @@ template <int DT, int OP, bool ABS>
 struct FullRed {
     template <int V>
     struct S {
-        enum { NRED = 1, FUSED = (OP == b200::OP_SUM && !ABS && DT != b200::F32) ? 1 : 0 };
+        enum { NRED = 1, FUSED = (OP == b200::OP_SUM && !ABS && DT != b200::F32) ? 1 : 0, XCHG = 0 };
         static DEV constexpr int op(int) { return OP; }
         struct H { int unused_; };
         struct L { u32 a0[(b200::dt_size<DT>::value * V + 3) / 4]; };

@@ -628,6 +628,85 @@ DEV void write_partial(const P& p, i64 k, int j, i64 pj, i64 pk, const float* a,
     }
 }
 
+// ================================================================== finishing a reduction across GPUs
+// One process per GPU, tensors sharded by columns: a reduction along the rows of a shard ends
+// with the other GPUs' results for the same rows.  Instead of leaving that to a collective
+// launched after the kernel, the thread that holds a row's final local result exchanges it
+// itself: it stores the result into the exchange area of EVERY rank (peer-mapped memory, plain
+// stores over NVLink), then stores the launch number into a flag word next to it with release
+// semantics, waits until its own area shows the launch number of every rank for that row, and
+// merges the W results in rank order -- the same order on every GPU, so all of them end up with
+// the same bits.  Nothing is read from a peer, and the wait is bounded in time: a rank that
+// never arrives sets bit 2 of the status word and the kernel carries on to its end.
+// Area layout (both halves alike; a launch uses half `epoch & 1`, so a rank that is one launch
+// ahead never overwrites what a slower rank still reads): data[W][cap] pairs of 32-bit words
+// (value bits, index or count), then flags[W][rows] launch numbers.
+//   P fields: x_table (device array of W area addresses), x_epoch, x_rank, x_world, x_cap,
+//   x_rows, x_col0 (first global column of the shard, added to arg-reduction indices).
+//   S::XCHG enables it; S::xc(r) says whether slot r spans the shards (a reduction of a
+//   replicated operand does not: every rank already holds the full result).
+DEV void st_sys_v2(u32* p, u32 a, u32 b) { asm volatile("st.relaxed.sys.global.v2.u32 [%0], {%1, %2};" ::"l"(p), "r"(a), "r"(b) : "memory"); }
+DEV void ld_sys_v2(const u32* p, u32& a, u32& b) { asm volatile("ld.relaxed.sys.global.v2.u32 {%0, %1}, [%2];" : "=r"(a), "=r"(b) : "l"(p) : "memory"); }
+DEV void st_release_sys(u32* p, u32 v) { asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory"); }
+DEV u32 ld_acquire_sys(const u32* p) { u32 v; asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory"); return v; }
+DEV u64 xchg_ns() { u64 t; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t)); return t; }
+
+template <class S, class P, int NR>
+DEV void xchg_rows(const P& p, i64 k, float* a, int* ai) {
+    const u32 W = p.x_world, me = p.x_rank, epoch = p.x_epoch;
+    const u64* table = reinterpret_cast<const u64*>(p.x_table);
+    const u64 data_bytes = (u64)W * p.x_cap * 8u;
+    const u64 half = (u64)(epoch & 1u) * (data_bytes + (u64)W * p.x_rows * 4u);
+#pragma unroll
+    for (int r = 0; r < NR; ++r)
+        if (S::op(r) == OP_ARGMAX || S::op(r) == OP_ARGMIN) ai[r] += p.x_col0;
+    for (u32 q = 0; q < W; ++q) {
+        u32* data = reinterpret_cast<u32*>(__ldg(table + q) + half) + (u64)me * p.x_cap * 2u;
+#pragma unroll
+        for (int r = 0; r < NR; ++r)
+            if (S::xc(r)) st_sys_v2(data + ((u64)r * p.K + k) * 2u, __float_as_uint(a[r]), (u32)ai[r]);
+    }
+    for (u32 q = 0; q < W; ++q) {
+        u32* flags = reinterpret_cast<u32*>(__ldg(table + q) + half + data_bytes);
+        st_release_sys(flags + (u64)me * p.x_rows + k, epoch);
+    }
+    const u64 mine = __ldg(table + me) + half;
+    const u32* myflags = reinterpret_cast<const u32*>(mine + data_bytes);
+    u64 t0 = 0;
+    bool gave_up = false;
+    for (u32 q = 0; q < W && !gave_up; ++q) {
+        while (ld_acquire_sys(myflags + (u64)q * p.x_rows + k) != epoch) {
+            if (t0 == 0) t0 = xchg_ns();
+            else if (xchg_ns() - t0 > p.wait_ns) {
+                if (p.status) atomicOr(reinterpret_cast<int*>(p.status), 4);
+                gave_up = true;
+                break;
+            }
+        }
+    }
+    float own[NR]; int owni[NR];
+#pragma unroll
+    for (int r = 0; r < NR; ++r) { own[r] = a[r]; owni[r] = ai[r]; }
+    for (u32 q = 0; q < W; ++q) {
+        const u32* data = reinterpret_cast<const u32*>(mine) + (u64)q * p.x_cap * 2u;
+        float b[NR]; int bi[NR];
+#pragma unroll
+        for (int r = 0; r < NR; ++r) {
+            u32 v = 0, i = 0;
+            if (S::xc(r)) ld_sys_v2(data + ((u64)r * p.K + k) * 2u, v, i);
+            b[r] = __uint_as_float(v); bi[r] = (int)i;
+        }
+        if (q == 0) {
+#pragma unroll
+            for (int r = 0; r < NR; ++r) { a[r] = b[r]; ai[r] = bi[r]; }
+        } else {
+            merge_slots<S, NR>(a, ai, b, bi);
+        }
+    }
+#pragma unroll
+    for (int r = 0; r < NR; ++r) if (!S::xc(r)) { a[r] = own[r]; ai[r] = owni[r]; }
+}
+
 // ================================================================== reduce along lanes (rows)
 // TPR threads cooperate on one kept index; BLOCK/TPR indices per block.
 // TPR == BLOCK: one index per block and the row may be split over p.split blocks.
@@ -712,11 +791,17 @@ DEV i64 red_rows_body(const P& p, i64 bid) {
         }
     }
     if constexpr (RPC > 1) {
-        if (live && sub == 0) { finish_slots<S, NR>(a, ai); S::epilogue(p, k, a, ai); }
+        if (live && sub == 0) {
+            if constexpr (S::XCHG) xchg_rows<S, P, NR>(p, k, a, ai);
+            finish_slots<S, NR>(a, ai); S::epilogue(p, k, a, ai);
+        }
         return -1;
     } else {
         if (p.split == 1) {
-            if (tid == 0) { finish_slots<S, NR>(a, ai); S::epilogue(p, k, a, ai); }
+            if (tid == 0) {
+                if constexpr (S::XCHG) xchg_rows<S, P, NR>(p, k, a, ai);
+                finish_slots<S, NR>(a, ai); S::epilogue(p, k, a, ai);
+            }
             return k;
         }
         // several blocks per index: publish, count arrivals, last one combines in split order
@@ -749,7 +834,10 @@ DEV i64 red_rows_body(const P& p, i64 bid) {
             }
 #pragma unroll
             for (int o2 = 16; o2 > 0; o2 >>= 1) shfl_merge<S, NR>(a, ai, o2);
-            if (tid == 0) { finish_slots<S, NR>(a, ai); S::epilogue(p, k, a, ai); }
+            if (tid == 0) {
+                if constexpr (S::XCHG) xchg_rows<S, P, NR>(p, k, a, ai);
+                finish_slots<S, NR>(a, ai); S::epilogue(p, k, a, ai);
+            }
         }
         return k;
     }

@@ -65,6 +65,7 @@ struct State {
 };
 State g;
 std::mutex g_mu;
+std::recursive_mutex g_arena_mu;       // arena entry points may be called from any host thread (tensor finalisers)
 
 uint64_t round_block(uint64_t bytes) {
     if (bytes == 0) bytes = 1;
@@ -236,6 +237,7 @@ b200_status b200_mem_info(uint64_t *free_bytes, uint64_t *total_bytes) {
 b200_status b200_malloc(uint64_t bytes, uint64_t *dptr) {
     if (!dptr) return fail(B200_ERR_INVALID, "dptr is null");
     if (g.device < 0) return fail(B200_ERR_INVALID, "b200_init has not been called");
+    std::lock_guard<std::recursive_mutex> lock(g_arena_mu);
     uint64_t sz = round_block(bytes);
     auto it = g.free_blocks.lower_bound(sz);
     void *p = nullptr;
@@ -267,6 +269,7 @@ b200_status b200_malloc(uint64_t bytes, uint64_t *dptr) {
 
 b200_status b200_free(uint64_t dptr) {
     if (!dptr) return B200_OK;
+    std::lock_guard<std::recursive_mutex> lock(g_arena_mu);
     void *p = reinterpret_cast<void *>(dptr);
     auto it = g.live.find(p);
     if (it == g.live.end()) return fail(B200_ERR_INVALID, "b200_free: %p is not a live block", p);
@@ -279,6 +282,7 @@ b200_status b200_free(uint64_t dptr) {
 }
 
 b200_status b200_mem_trim(void) {
+    std::lock_guard<std::recursive_mutex> lock(g_arena_mu);
     if (g.free_blocks.empty()) return B200_OK;
     cudaDeviceSynchronize();
     for (auto &kv : g.free_blocks) cudaFree(kv.second);
@@ -288,6 +292,7 @@ b200_status b200_mem_trim(void) {
 }
 
 b200_status b200_mem_stats(uint64_t *in_use, uint64_t *cached, uint64_t *peak, uint64_t *allocs) {
+    std::lock_guard<std::recursive_mutex> lock(g_arena_mu);
     if (in_use) *in_use = g.in_use;
     if (cached) *cached = g.cached;
     if (peak) *peak = g.peak;
@@ -731,6 +736,73 @@ b200_status b200_allgather(uint64_t comm, uint64_t send, uint64_t recv, uint64_t
     int r = nccl.AllGather(reinterpret_cast<const void *>(send), reinterpret_cast<void *>(recv), send_bytes, 0 /* ncclInt8 */,
                            reinterpret_cast<void *>(comm), as_stream(stream));
     if (r) return fail(B200_ERR_NCCL, "ncclAllGather: %s", nccl.GetErrorString(r));
+    return B200_OK;
+}
+
+// ---------------------------------------------------------------- exchange areas (peer memory)
+struct Xchg {
+    void *local = nullptr;
+    void *table = nullptr;
+    std::vector<void *> opened;
+};
+static std::unordered_map<uint64_t, Xchg> g_xchg;
+
+b200_status b200_xchg_create(uint64_t comm, int32_t n_ranks, int32_t rank, uint64_t bytes,
+                             uint64_t *local, uint64_t *table) {
+    if (!comm || n_ranks < 1 || rank < 0 || rank >= n_ranks || !local || !table || !bytes)
+        return fail(B200_ERR_INVALID, "b200_xchg_create: bad arguments");
+    if (g.device < 0) return fail(B200_ERR_INVALID, "b200_init has not been called");
+    Xchg x;
+    CU(cudaMalloc(&x.local, bytes));
+    CU(cudaMemset(x.local, 0, bytes));
+    CU(cudaDeviceSynchronize());
+    cudaIpcMemHandle_t mine;
+    CU(cudaIpcGetMemHandle(&mine, x.local));
+    // the handles travel over the communicator: staged in device memory, gathered, read back
+    const size_t hb = sizeof(cudaIpcMemHandle_t);
+    void *stage = nullptr;
+    CU(cudaMalloc(&stage, hb * (size_t)(n_ranks + 1)));
+    CU(cudaMemcpy(stage, &mine, hb, cudaMemcpyHostToDevice));
+    b200_status st = b200_allgather(comm, reinterpret_cast<uint64_t>(stage),
+                                    reinterpret_cast<uint64_t>(static_cast<char *>(stage) + hb), hb,
+                                    reinterpret_cast<uint64_t>(g.stream));
+    if (st != B200_OK) { cudaFree(stage); cudaFree(x.local); return st; }
+    CU(cudaStreamSynchronize(g.stream));
+    std::vector<cudaIpcMemHandle_t> all(n_ranks);
+    CU(cudaMemcpy(all.data(), static_cast<char *>(stage) + hb, hb * (size_t)n_ranks, cudaMemcpyDeviceToHost));
+    CU(cudaFree(stage));
+    std::vector<uint64_t> bases(n_ranks);
+    for (int r = 0; r < n_ranks; ++r) {
+        if (r == rank) { bases[r] = reinterpret_cast<uint64_t>(x.local); continue; }
+        void *p = nullptr;
+        cudaError_t e = cudaIpcOpenMemHandle(&p, all[r], cudaIpcMemLazyEnablePeerAccess);
+        if (e != cudaSuccess) {
+            cudaGetLastError();
+            for (void *q : x.opened) cudaIpcCloseMemHandle(q);
+            cudaFree(x.local);
+            return fail(B200_ERR_CUDA, "cudaIpcOpenMemHandle(rank %d): %s", r, cudaGetErrorString(e));
+        }
+        x.opened.push_back(p);
+        bases[r] = reinterpret_cast<uint64_t>(p);
+    }
+    CU(cudaMalloc(&x.table, sizeof(uint64_t) * (size_t)n_ranks));
+    CU(cudaMemcpy(x.table, bases.data(), sizeof(uint64_t) * (size_t)n_ranks, cudaMemcpyHostToDevice));
+    *local = reinterpret_cast<uint64_t>(x.local);
+    *table = reinterpret_cast<uint64_t>(x.table);
+    std::lock_guard<std::mutex> lock(g_mu);
+    g_xchg[*local] = x;
+    return B200_OK;
+}
+
+b200_status b200_xchg_destroy(uint64_t local) {
+    std::lock_guard<std::mutex> lock(g_mu);
+    auto it = g_xchg.find(local);
+    if (it == g_xchg.end()) return fail(B200_ERR_INVALID, "b200_xchg_destroy: unknown exchange area");
+    cudaDeviceSynchronize();
+    for (void *q : it->second.opened) cudaIpcCloseMemHandle(q);
+    cudaFree(it->second.table);
+    cudaFree(it->second.local);
+    g_xchg.erase(it);
     return B200_OK;
 }
 

@@ -400,8 +400,8 @@ class Statement(object):
         if extent is None:
             self._red_extent = a.shape[ax]
         elif extent != a.shape[ax]:
-            raise ValueError("reductions over %d and %d elements cannot share one kernel"
-                             % (extent, a.shape[ax]))
+            raise MixedExtents("reductions over %d and %d elements cannot share one kernel"
+                               % (extent, a.shape[ax]))
         shape = list(a.shape)
         shape[ax] = 1
         shape = tuple(shape)
@@ -501,7 +501,7 @@ class _Fields(object):
 class Pass(object):
     """One kernel launch of a statement."""
     __slots__ = ("source", "name", "grid", "block", "fields", "kernel", "uses_rng", "desc",
-                 "results", "kind", "smem", "cluster", "setup")
+                 "results", "kind", "smem", "cluster", "setup", "uses_xchg")
 
     def __init__(self):
         self.kernel = None
@@ -510,6 +510,17 @@ class Pass(object):
         self.cluster = 1       # thread blocks per cluster
         self.setup = None      # callable(runtime, kernel, pass) run once after compilation
         self.results = []      # (reduction op, fp32 result address, int32 index address or 0, count)
+        self.uses_xchg = False    # the launcher supplies the exchange launch number in field "x_epoch"
+
+
+class MixedExtents(ValueError):
+    """Reductions over different numbers of elements in one statement: the backend evaluates
+    them as separate statements."""
+
+
+class XchgUnsupported(Exception):
+    """The statement cannot finish its reductions through the exchange area (too many results,
+    or a kernel shape without that path): the caller falls back to collectives between passes."""
 
 
 def _red_code(r):
@@ -571,13 +582,18 @@ class Planner(object):
         self.fuse_moments = True           # sum(e) and sum(sqr(e - m)) in one pass when m needs sum-level results
 
     # ---- helpers on the frame: K = kept axis, N = loop axis
-    def plan(self, st, scratch, rounding=0, fuse_final=True, lin=None):
+    def plan(self, st, scratch, rounding=0, fuse_final=True, lin=None, xchg=None, sharded=None):
         """Return the list of Pass objects for Statement ``st``.  ``fuse_final=False``
         keeps every reduction result in scratch (for a caller that combines results
         of several devices between passes); ``lin=(ncols, col0, local cols)`` makes
         element indices for random numbers those of a wider tensor this one is a
-        column slice of."""
+        column slice of; ``sharded`` names the operands (by index) that are column shards, and
+        ``xchg`` (a dict: table, rank, world, cap, rows, col0) makes every reduction that spans
+        them finish across the GPUs inside its kernel.
+        Raises XchgUnsupported when the statement cannot use the exchange area."""
         self._lin = lin
+        self._xchg = xchg           # reductions finish across GPUs inside the kernel (see _reduction_pass)
+        self._sharded = sharded     # indices of the operands that are column shards of wider tensors
         ra = st.axis                # reduced / loop axis in tensor coordinates
         ka = 1 - ra
         reds = [n for n in st.nodes if n.kind == "r" and self._reachable(st, n)]
@@ -589,7 +605,7 @@ class Planner(object):
         full_shape = self._full_shape(st)
         root_is_k = st.root.shape[ra] == 1
         out_is_k = st.out_shape[ra] == 1
-        if fuse_final and levels and self.rowres:
+        if fuse_final and levels and self.rowres and xchg is None:
             pz = self._rowres_pass(st, reds, levels, ka, ra, full_shape, rounding, root_is_k and out_is_k)
             if pz is not None:
                 return [pz]
@@ -603,7 +619,11 @@ class Planner(object):
                                       scratch(4 * K, False) if r.op.startswith("arg") else 0)
             pz = self._reduction_pass(st, rs, res_buf, ka, ra, full_shape, scratch, final)
             if not final:
-                pz.results = [(r.op,) + res_buf[r.nid] + (K,) for r in rs]
+                # for a caller that combines results of several devices between the passes: the
+                # reductions that span the column shards (all of them when it did not say which
+                # operands are shards)
+                pz.results = [(r.op,) + res_buf[r.nid] + (K,) for r in rs
+                              if self._sharded is None or self._spans_shards(st, r, self._sharded)]
             passes.append(pz)
             if final:
                 return passes
@@ -666,6 +686,23 @@ class Planner(object):
         return reds
 
     @staticmethod
+    def _spans_shards(st, red, sharded):
+        """True when reduction ``red`` reduces something computed from a column-sharded tensor
+        (``sharded``: operand indices), directly or through an earlier such reduction."""
+        todo, seen = [Planner._red_operand(red)], set()
+        while todo:
+            n = todo.pop()
+            if n.nid in seen:
+                continue
+            seen.add(n.nid)
+            if n.kind == "t" and n.tix in sharded:
+                return True
+            if n.kind == "z" and n.op == "onehot" and n.tix in sharded:
+                return True
+            todo.extend(n.args)
+        return False
+
+    @staticmethod
     def _contains_zero_op(node):
         todo, seen = [node], set()
         while todo:
@@ -691,7 +728,7 @@ class Planner(object):
             return True
         return (not lanes_ok("n")) and lanes_ok("k") and K > 1
 
-    def _fixup_lines(self, ep, rs, fresh, n_expr):
+    def _fixup_lines(self, ep, rs, fresh):
         """Code that turns the M2 of every moments pair among ``rs`` into the sum the statement
         asked for, sum((e - m)^2) = M2 + n (mean - m)^2, with m evaluated by emitter ``ep`` from
         the finished results r[] of this pass (and earlier ones).  Returns (lines, {nid: name}):
@@ -707,8 +744,9 @@ class Planner(object):
             lines.extend(ep.h_lines[before:])
             del ep.h_lines[before:]
             name = "m2c%d" % r.nid
+            cnt = "(float)ri[%d]" % i1                       # elements the pair has seen (all shards)
             lines.append("float %s; { const int i = 0; (void)i; const float dm = r[%d] / %s - %s; "
-                         "%s = __fmaf_rn(dm * dm, %s, r[%d]); }" % (name, i1, n_expr, mref, name, n_expr, i2))
+                         "%s = __fmaf_rn(dm * dm, %s, r[%d]); }" % (name, i1, cnt, mref, name, cnt, i2))
             names[r.nid] = name
         return lines, names
 
@@ -749,7 +787,7 @@ class Planner(object):
             for r in rs:
                 if r.extra is None or r.extra[0] != "m2":
                     fx.names[("h", r.nid)] = "(float)ri[%d]" % fresh[r.nid] if r.op.startswith("arg") else "r[%d]" % fresh[r.nid]
-            fix_lines, fixed = self._fixup_lines(fx, rs, fresh, "(float)p.N")
+            fix_lines, fixed = self._fixup_lines(fx, rs, fresh)
             fixups.append(fix_lines + ["r[%d] = %s;" % (fresh[nid], name) for nid, name in fixed.items()])
         fin = self._Emit(st, f, ka, ra, False, res_buf, 1 << 30, tables)
         fin.no_nc = True
@@ -1398,6 +1436,12 @@ class Planner(object):
         self._frame(st, ka, ra)
         # orientation: lanes along N when the loop axis is the contiguous one
         lanes_on_k = self._lanes_on_k(st, ka, ra, K)
+        xchg = self._xchg
+        crossing = [bool(xchg) and self._spans_shards(st, r, self._sharded or ()) for r in reds]
+        if not any(crossing):
+            xchg = None
+        elif lanes_on_k or K > xchg["rows"] or len(reds) * K > xchg["cap"]:
+            raise XchgUnsupported("reduction of %d x %d results does not fit the exchange area" % (len(reds), K))
         f = _Fields()
         em = self._Emit(st, f, ka, ra, lanes_on_k, res_buf, reds[0].level - 1, (self.unary, self.binary))
         outs = []
@@ -1415,7 +1459,7 @@ class Planner(object):
         for r in reds:
             if r.extra is None or r.extra[0] != "m2":
                 ep.names[("h", r.nid)] = "(float)ri[%d]" % fresh[r.nid] if r.op.startswith("arg") else "r[%d]" % fresh[r.nid]
-        fix_lines, fixed = self._fixup_lines(ep, reds, fresh, "(float)p.N")
+        fix_lines, fixed = self._fixup_lines(ep, reds, fresh)
         for nid, name in fixed.items():
             ep.names[("h", nid)] = name
         if final:
@@ -1504,7 +1548,20 @@ class Planner(object):
             f.u64("counters", 0)
         ops = " : ".join("r == %d ? %s" % (i, _red_code(r)) for i, r in enumerate(reds[:-1]))
         ops = (ops + " : " if ops else "") + _red_code(reds[-1])
-        src, pz.name = self._source(f, em, eval_tail, nr, ops, ep_lines, None, call, acc_tail=acc_tail)
+        xc = None
+        if xchg:
+            f.u64("x_table", xchg["table"])
+            f.u64("status", self.status_ptr)
+            f.u64("wait_ns", int(self.wait_limit_ns))
+            f.u32("x_epoch", 0)
+            f.u32("x_rank", xchg["rank"])
+            f.u32("x_world", xchg["world"])
+            f.u32("x_cap", xchg["cap"])
+            f.u32("x_rows", xchg["rows"])
+            f.i32("x_col0", xchg["col0"])
+            xc = " || ".join("r == %d" % i for i, c in enumerate(crossing) if c)
+        src, pz.name = self._source(f, em, eval_tail, nr, ops, ep_lines, None, call, acc_tail=acc_tail, xc=xc)
+        pz.uses_xchg = bool(xchg)
         pz.source, pz.fields, pz.grid, pz.block = src, f, grid, (BLOCK, 1, 1)
         pz.uses_rng = em.uses_rng
         pz.desc = "%s V=%d K=%d N=%d split=%d grid=%s" % (pz.kind, V, K, N, split, grid)
@@ -1628,12 +1685,14 @@ class Planner(object):
         return pz
 
     @staticmethod
-    def _source(f, em, eval_tail, nred, ops, ep_lines, st_lines, call, min_blocks=1, acc_tail=None):
+    def _source(f, em, eval_tail, nred, ops, ep_lines, st_lines, call, min_blocks=1, acc_tail=None, xc=None):
         ind = "\n        "
         nout = max(nred, 1)
         parts = ['#include "optree_templates.cuh"', "using namespace b200;", f.decl(), "template <int V> struct S {"]
-        parts.append("    enum { NRED = %d };" % nred)
+        parts.append("    enum { NRED = %d, XCHG = %d };" % (nred, 1 if xc else 0))
         parts.append("    static DEV constexpr int op(int r) { return %s; }" % ops)
+        if xc:
+            parts.append("    static DEV constexpr bool xc(int r) { return %s; }" % xc)
         parts.append("    struct H { %s int unused_; };" % " ".join(em.h_decl))
         parts.append("    struct L { %s int unused_; };" % " ".join(em.l_decl))
         parts.append("    static DEV void load_h(const P& p, i64 k, H& h) {" + ind + ind.join(em.h_lines) + "\n    }")

@@ -87,6 +87,8 @@ SIGNATURES = {
     "b200_comm_destroy": (i32, [u64]),
     "b200_allreduce": (i32, [u64, u64, u64, u64, i32, i32, u64]),
     "b200_allgather": (i32, [u64, u64, u64, u64, u64]),
+    "b200_xchg_create": (i32, [u64, i32, i32, u64, P(u64), P(u64)]),
+    "b200_xchg_destroy": (i32, [u64]),
 }
 
 _lib = None
@@ -390,3 +392,14 @@ def allreduce(comm, send, recv, count, dtype=F32, op=SUM, stream=0):
 
 def allgather(comm, send, recv, send_bytes, stream=0):
     check(lib().b200_allgather(comm, send, recv, send_bytes, stream))
+
+
+def xchg_create(comm, n_ranks, rank, nbytes):
+    """Collective: (this rank's exchange area, device table of every rank's area)."""
+    local, table = u64(0), u64(0)
+    check(lib().b200_xchg_create(comm, n_ranks, rank, nbytes, C.byref(local), C.byref(table)))
+    return local.value, table.value
+
+
+def xchg_destroy(local):
+    check(lib().b200_xchg_destroy(local))

@@ -13,23 +13,27 @@ module gives ``parallel=True`` a meaning:
   the global count) and stores columns ``[c0, c1)`` on this rank.  Tensors made
   without the keyword are replicated.
 * element-wise statements and reductions along axis 0 are shard-local;
-* ``sum`` / ``max`` / ``min`` along axis 1 (and over a whole tensor) reduce the
-  local shard, then the per-row fp32 results are all-reduced over NCCL before
-  the next pass reads them (so a variance needs two all-reduces, of the sum and
-  of the centred squares);
+* reductions along axis 1 (and over a whole tensor) reduce the local shard and
+  finish across the GPUs inside the reduction kernel: the thread that holds a
+  row's local result stores it into every rank's peer-mapped exchange area over
+  NVLink, waits (time-bounded) for the other ranks' results and merges them in
+  rank order (``xchg_rows`` in the kernel header), so a statement is planned as
+  on one GPU and no collective is launched between its passes.  Statements the
+  exchange area cannot carry (more than 4096 rows, reductions down a transposed
+  view) reduce locally and all-reduce the per-row results over NCCL instead;
 * random numbers and stochastic rounding use the element index in the global
   tensor, so stored values do not depend on how many GPUs share the work.
 
-Host plumbing (rank discovery, the NCCL unique id, barriers, max-over-ranks of
-timings) rides on a gloo ``torch.distributed`` group; no torch tensor touches
-the data path.
+Host plumbing (the NCCL unique id, barriers, max-over-ranks of timings) goes
+over a small TCP star (``HostGroup``); ranks are told who they are by whatever
+launched them (``RANK`` / ``WORLD_SIZE`` / ``MASTER_ADDR`` / ``MASTER_PORT``).
 """
 
 import numpy as np
 
 from . import runtime as rt
 from .backend import B200Backend
-from .lowering import BoundPlan, Statement, program_key
+from .lowering import BoundPlan, Statement, XchgUnsupported, program_key
 from .optree import OpTreeNode, Tensor
 
 _none_slice = slice(None, None, None)
@@ -119,12 +123,20 @@ class ShardedTensor(Tensor):
 class ShardedBackend(B200Backend):
     """B200Backend of one rank of a column-sharded job."""
 
-    def __init__(self, rank, world_size, comm, host_barrier=None, host_max=None, **kw):
+    def __init__(self, rank, world_size, comm, host_barrier=None, host_max=None, use_exchange=True, **kw):
         super(ShardedBackend, self).__init__(**kw)
         self.rank, self.world_size, self.comm = rank, world_size, comm
         self.host_barrier = host_barrier or (lambda: None)
         self.host_max = host_max or (lambda v: v)
         self.collectives = 0                 # all-reduces issued so far
+        self.exchanges = 0                   # reduction kernels that finished across the GPUs by themselves
+        # peer-mapped exchange area: rows x reductions it can carry per launch
+        self._xchg, self._xchg_local, self._xepoch = None, 0, 0
+        if world_size > 1 and comm and use_exchange:
+            rows, cap = 4096, 16384
+            nbytes = 2 * (world_size * cap * 8 + world_size * rows * 4)
+            self._xchg_local, table = rt.xchg_create(comm, world_size, rank, nbytes)
+            self._xchg = {"table": table, "rank": rank, "world": world_size, "cap": cap, "rows": rows}
 
     # ---- factories: parallel=True -> column shard
     def _make(self, factory, shape, dtype, name, parallel, fill=None):
@@ -204,13 +216,36 @@ class ShardedBackend(B200Backend):
             row_ok = lin is not None and out.flat_of is None and lin[2] % 8192 == 0
             st = Statement(local_stack, allow_flat=(not uses_rng) or row_ok)
             crosses = st.has_red and st.axis == 1
-            self._scratch.reset()
-            passes = self._planner.plan(st, self._scratch, rounding=rounding, fuse_final=not crosses, lin=lin)
+            local_ids = set(id(s.local) for s in sharded)
+            shard_ops = set(i for i, o in enumerate(st.operands) if id(o.tensor) in local_ids)
+            passes = None
+            if crosses and self._xchg is not None:
+                # reductions along the sharded axis finish across the GPUs inside their kernels
+                flat = sharded[0].flat_of is not None
+                has_arg = any(type(s) is dict and s["op"] in ("argmax", "argmin") for s in stack)
+                if not (flat and has_arg):
+                    xchg = dict(self._xchg, col0=0 if flat else sharded[0].c0)
+                    try:
+                        self._scratch.reset()
+                        passes = self._planner.plan(st, self._scratch, rounding=rounding, lin=lin,
+                                                    xchg=xchg, sharded=shard_ops)
+                        crosses = False              # nothing left to do between the passes
+                    except XchgUnsupported:
+                        passes = None
+                        st = Statement(local_stack, allow_flat=(not uses_rng) or row_ok)
+            if passes is None:
+                self._scratch.reset()
+                passes = self._planner.plan(st, self._scratch, rounding=rounding, fuse_final=not crosses,
+                                            lin=lin, sharded=shard_ops)
             cached = self._plans[key] = (BoundPlan(st, passes), crosses)
         else:
             cached[0].rebind(local_stack)
         plan, crosses = cached
         for pz in plan.passes:
+            if pz.uses_xchg:
+                self._xepoch += 1
+                pz.fields.values["x_epoch"] = self._xepoch & 0xFFFFFFFF
+                self.exchanges += 1
             self._launch(pz)
             if crosses:
                 for op, addr_v, addr_i, count in pz.results:
@@ -239,7 +274,10 @@ class ShardedBackend(B200Backend):
         idx[:] = self.sum(self.onehot(winner, axis=0) * idxs, axis=0)
 
     def _allreduce(self, addr, count, op):
+        mark = self._timeline_begin("collective", "allreduce") if self._timeline is not None else None
         rt.allreduce(self.comm, addr, addr, count, rt.F32, op, self.stream)
+        if mark is not None:
+            rt.event_record(mark, self.stream)
         self.collectives += 1
 
     def allreduce_tensor(self, tensor, op="sum"):
@@ -248,30 +286,105 @@ class ShardedBackend(B200Backend):
         self._allreduce(tensor.ptr, tensor.size, _NCCL_OP[op])
 
 
-def bootstrap(rank, world_size, make_id=None, init_comm=None):
-    """Host-side rendezvous over a gloo process group: rank 0 creates the NCCL
-    unique id, everybody receives it and joins the communicator.  Returns
-    (comm, barrier, max_over_ranks).  The two callables default to the library's
-    NCCL bridge; tests pass stand-ins."""
-    import torch
-    import torch.distributed as dist
-    if not dist.is_initialized():
-        dist.init_process_group(backend="gloo", rank=rank, world_size=world_size)
+class HostGroup(object):
+    """The few host-side collectives the job needs -- hand out the communicator id, a barrier,
+    a maximum over ranks (for timings) -- over plain TCP: rank 0 listens on ``MASTER_ADDR`` at
+    ``MASTER_PORT + 1`` (the port itself belongs to whatever launched the ranks) and is the hub
+    of a star.  Messages are fixed-size; nothing here touches tensor data."""
+
+    def __init__(self, rank, world_size, addr=None, port=None, timeout=120.0):
+        import os
+        import socket
+        import time
+        self.rank, self.world_size = rank, world_size
+        self.peers, self.hub = [], None
+        if world_size == 1:
+            return
+        addr = addr or os.environ.get("MASTER_ADDR", "127.0.0.1")
+        port = int(port or int(os.environ.get("MASTER_PORT", "29500")) + 1)
+        if rank == 0:
+            srv = socket.socket(socket.AF_INET, socket.SOCK_STREAM)
+            srv.setsockopt(socket.SOL_SOCKET, socket.SO_REUSEADDR, 1)
+            srv.bind((addr, port))
+            srv.listen(world_size)
+            srv.settimeout(timeout)
+            by_rank = {}
+            while len(by_rank) < world_size - 1:
+                conn, _ = srv.accept()
+                conn.setsockopt(socket.IPPROTO_TCP, socket.TCP_NODELAY, 1)
+                conn.settimeout(timeout)
+                by_rank[int.from_bytes(self._recv(conn, 4), "little")] = conn
+            srv.close()
+            self.peers = [by_rank[r] for r in range(1, world_size)]
+        else:
+            deadline = time.time() + timeout
+            while True:
+                try:
+                    self.hub = socket.create_connection((addr, port), timeout=timeout)
+                    break
+                except OSError:
+                    if time.time() > deadline:
+                        raise
+                    time.sleep(0.05)
+            self.hub.setsockopt(socket.IPPROTO_TCP, socket.TCP_NODELAY, 1)
+            self.hub.sendall(int(rank).to_bytes(4, "little"))
+
+    @staticmethod
+    def _recv(conn, n):
+        buf = b""
+        while len(buf) < n:
+            part = conn.recv(n - len(buf))
+            if not part:
+                raise ConnectionError("peer closed the rendezvous connection")
+            buf += part
+        return buf
+
+    def broadcast(self, payload, nbytes):
+        """``payload`` (bytes of length nbytes) of rank 0, on every rank."""
+        if self.world_size == 1:
+            return payload
+        if self.rank == 0:
+            for c in self.peers:
+                c.sendall(payload)
+            return payload
+        return self._recv(self.hub, nbytes)
+
+    def max(self, value):
+        import struct
+        if self.world_size == 1:
+            return float(value)
+        if self.rank == 0:
+            vals = [float(value)] + [struct.unpack("<d", self._recv(c, 8))[0] for c in self.peers]
+            out = max(vals)
+            for c in self.peers:
+                c.sendall(struct.pack("<d", out))
+            return out
+        self.hub.sendall(struct.pack("<d", float(value)))
+        return struct.unpack("<d", self._recv(self.hub, 8))[0]
+
+    def barrier(self):
+        self.max(0.0)
+
+    def close(self):
+        for c in self.peers + ([self.hub] if self.hub else []):
+            try:
+                c.close()
+            except OSError:
+                pass
+        self.peers, self.hub = [], None
+
+
+def bootstrap(rank, world_size, make_id=None, init_comm=None, addr=None, port=None):
+    """Host-side rendezvous: rank 0 creates the NCCL unique id, everybody receives it and joins
+    the communicator.  Returns (comm, barrier, max_over_ranks).  The two callables default to
+    the library's NCCL bridge; tests pass stand-ins."""
     make_id = make_id or rt.comm_unique_id
     init_comm = init_comm or rt.comm_init
-    box = [make_id() if rank == 0 else None]
-    dist.broadcast_object_list(box, src=0)
-    comm = init_comm(box[0], world_size, rank)
-
-    def barrier():
-        dist.barrier()
-
-    def max_over_ranks(value):
-        t = torch.tensor([float(value)], dtype=torch.float64)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        return float(t[0])
-
-    return comm, barrier, max_over_ranks
+    group = HostGroup(rank, world_size, addr, port)
+    uid = bytes(make_id()) if rank == 0 else None
+    uid = group.broadcast(uid, 128)
+    comm = init_comm(uid, world_size, rank)
+    return comm, group.barrier, group.max
 
 
 def gen_sharded_backend(rank, world_size, device_id=0, rng_seed=None, datatype=np.float32, **kw):

@@ -15,7 +15,11 @@ def main():
     from oracle.numpy_backend import OracleBackend
     from tests.parity import check_output
     rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
-    be = gen_sharded_backend(rank, world, device_id=int(os.environ.get("LOCAL_RANK", rank)), rng_seed=0)
+    exchange = os.environ.get("B200_SHARDED_EXCHANGE", "1") == "1"
+    be = gen_sharded_backend(rank, world, device_id=int(os.environ.get("LOCAL_RANK", rank)), rng_seed=0,
+                             use_exchange=exchange)
+    if os.environ.get("B200_SHARDED_MODE") == "expiry":
+        return expiry(be, rank, world)
     ob = OracleBackend(default_dtype=np.float64)
     rng = np.random.RandomState(0)
 
@@ -27,9 +31,12 @@ def main():
     x = be.array(xh, dtype=np.float16, parallel=True)
     y = be.empty((rows, cols), dtype=np.float16, parallel=True)
     g, b = be.array(gh), be.array(bh)
-    before = be.collectives
+    before, before_x, launches = be.collectives, be.exchanges, be.launches
     y[:] = (x - be.mean(x, axis=1)) / be.sqrt(be.var(x, axis=1) + 1e-5) * g + b
-    assert be.collectives - before == 2
+    if exchange:        # statistics in one kernel that finishes across the GPUs, then the element-wise pass
+        assert (be.collectives - before, be.exchanges - before_x, be.launches - launches) == (0, 1, 2)
+    else:
+        assert be.collectives - before == 2
     ox, og, obt = ob.array(xh, dtype=np.float64), ob.array(gh, dtype=np.float64), ob.array(bh, dtype=np.float64)
     oy = ob.zeros((rows, cols), dtype=np.float64)
     oy[:] = (ox - ob.mean(ox, axis=1)) / ob.sqrt(ob.var(ox, axis=1) + 1e-5) * og + obt
@@ -98,9 +105,45 @@ def main():
             continue                                   # minima of differences are ill-conditioned in fp32
         check_output("sharded fuzz seed %d" % seed, g, w, g.dtype)
     assert ran > 40, ran
+    be.synchronize()
     be.host_barrier()
     if rank == 0:
-        print("SHARDED-OK world=%d collectives=%d" % (world, be.collectives))
+        print("SHARDED-OK world=%d collectives=%d exchanges=%d" % (world, be.collectives, be.exchanges))
+
+
+def expiry(be, rank, world):
+    """A rank that leaves a statement out: the others' kernels wait for its results, give up
+    after the time limit, report through the status word -- and the job carries on."""
+    from neon_b200 import runtime as rt
+    rng = np.random.RandomState(1)
+    rows, cols = 48, 4096 * world
+    xh = rng.randn(rows, cols).astype(np.float32)
+    x = be.array(xh, parallel=True)
+    m = be.empty((rows, 1))
+    m[:] = be.max(x, axis=1)
+    be.synchronize()
+    assert np.array_equal(m.get(), xh.max(1, keepdims=True))
+    be._planner.wait_limit_ns = 30 * 1000 * 1000
+    be._plans.clear()
+    be.host_barrier()
+    if rank != world - 1:
+        m[:] = be.max(x, axis=1)
+        try:
+            be.synchronize()
+            raise AssertionError("the wait for the missing rank did not run out")
+        except rt.B200Error as e:
+            assert e.status == -6 and "another GPU" in str(e), str(e)
+    else:
+        be._xepoch += 1          # the launch number of the statement this rank leaves out
+    be.host_barrier()
+    be._planner.wait_limit_ns = 2000000000
+    be._plans.clear()
+    m[:] = be.min(x, axis=1)
+    be.synchronize()
+    assert np.array_equal(m.get(), xh.min(1, keepdims=True))
+    be.host_barrier()
+    if rank == 0:
+        print("SHARDED-OK expiry world=%d" % world)
 
 
 if __name__ == "__main__":

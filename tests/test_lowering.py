@@ -162,6 +162,11 @@ def test_whole_tensor_reductions_of_different_sizes_do_not_share_a_pass():
     tree = OpTreeNode({"op": "assign"}, norm, be.sum(a, axis=1) + be.sum(b, axis=1))
     with pytest.raises(ValueError):
         Statement(tree.traverse([]))
+    # the same for reductions along an axis: rows of 100 and of 300 elements
+    s1, s2, col = be.empty((64, 100)), be.empty((64, 300)), be.empty((64, 1))
+    be.passes = []
+    col[:] = be.sum(s1, axis=1) + be.max(s2, axis=1)
+    assert ["N=100" in p.desc for p in be.passes] == [True, False] and "N=300" in be.passes[1].desc
 
 
 def test_unaligned_views_fall_back_to_narrower_vectors():

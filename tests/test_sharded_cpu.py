@@ -1,9 +1,11 @@
 """
-CPU tests of the multi-GPU layer's host logic with two gloo ranks: the
-rendezvous that distributes the communicator id, the column partition, and the
-collective schedule each rank derives for sharded statements (un-fused final
-pass, one all-reduce per cross-shard reduction, global element indices for the
-random words).  Devices and NCCL are replaced by recording stand-ins.
+CPU tests of the multi-GPU layer's host logic with two and four ranks: the
+rendezvous that distributes the communicator id (the package's own TCP star),
+the column partition, and what each rank plans for sharded statements -- with an
+exchange area (reductions finish inside their kernels) and without (un-fused
+final pass, one all-reduce per cross-shard reduction) -- plus global element
+indices for the random words.  Devices and NCCL are replaced by recording
+stand-ins; the test compares the ranks' plans over a gloo group of its own.
 """
 import os
 import socket
@@ -24,6 +26,7 @@ def _free_port():
 def _worker(rank, world, port, out):
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
     import torch.distributed as dist
+    dist.init_process_group(backend="gloo", rank=rank, world_size=world)     # the test's own gathers
     from neon_b200 import sharded
     from neon_b200.sharded import ShardedBackend, ShardedTensor, bootstrap, shard_columns
     from tests.dryrun import DryRunBackend, DryTensor
@@ -40,7 +43,8 @@ def _worker(rank, world, port, out):
             DryRunBackend.__init__(self)
             self.compile = False
             self.rank, self.world_size, self.comm = rank, world, comm
-            self.collectives = 0
+            self.collectives = self.exchanges = 0
+            self._xchg, self._xepoch = None, 0          # no exchange area: collectives between the passes
             self.calls = []
             self.plans = []
 
@@ -112,6 +116,48 @@ def _worker(rank, world, port, out):
     gathered = [None] * world
     dist.all_gather_object(gathered, [(p.kind, p.grid) for p in be.plans] + be.calls)
     assert all(g == gathered[0] for g in gathered)
+
+    # a reduction of a replicated operand next to one of a sharded operand: only the latter is combined
+    be.plans, be.calls = [], []
+    rep = be.empty((rows, cols // world))           # replicated, as wide as a shard
+    m[:] = be.sum(rep, axis=1) + be.sum(x, axis=1)
+    assert be.calls == [(0, rows)], be.calls
+
+    # ---- with an exchange area the reductions finish across the GPUs inside their kernels:
+    #      statements are planned as on one GPU (moments in one pass, fused final epilogue),
+    #      nothing is issued between the passes, every exchange pass gets its own launch number
+    be._xchg = {"table": 0x7D0000000000, "rank": rank, "world": world, "cap": 16384, "rows": 4096}
+    be._plans.clear()
+    be.plans, be.calls = [], []
+    y[:] = (x - be.mean(x, axis=1)) / be.sqrt(be.var(x, axis=1) + 1e-5) * gamma + beta
+    assert [p.kind for p in be.plans] == ["red_rows", "ew_2d"] and be.calls == []
+    red = be.plans[0]
+    assert red.uses_xchg and "XCHG = 1" in red.source and "OP_MOM_MEAN" in red.source
+    assert red.fields.values["x_epoch"] == 1 and red.fields.values["x_rank"] == rank
+    assert red.fields.values["x_col0"] == c0
+    be.plans = []
+    m[:] = be.max(x, axis=1)                       # replicated output: the epilogue of the one pass stores it
+    total[:] = be.sum(z)
+    assert [p.kind for p in be.plans] == ["red_rows", "red_rows"] and be.calls == []
+    assert [p.fields.values["x_epoch"] for p in be.plans] == [2, 3] and be.exchanges == 3
+    be.plans = []
+    m[:] = be.sum(rep, axis=1) + be.sum(x, axis=1)
+    assert "xc(int r) { return r == 1; }" in be.plans[0].source or "xc(int r) { return r == 0; }" in be.plans[0].source
+    be.plans = []
+    idx = be.empty((rows, 1), np.int32)
+    idx[:] = be.argmax(x, axis=1)                  # indices become global columns before they are exchanged
+    assert be.plans[0].uses_xchg and be.calls == []
+    # more rows than the area has flags for: back to collectives between the passes
+    tall = be.empty((8192, 64 * world), parallel=True)
+    tm = be.empty((8192, 1))
+    be.plans, be.calls = [], []
+    tm[:] = be.max(tall, axis=1)
+    assert not any(p.uses_xchg for p in be.plans) and be.calls == [(1, 8192)]
+    gathered = [None] * world
+    dist.all_gather_object(gathered, be._xepoch)
+    assert all(g == gathered[0] for g in gathered)
+    be._xchg = None
+    be._plans.clear()
 
     # seeded random statements over sharded tensors plan on every rank (the GPU run checks values)
     from tests import fuzz

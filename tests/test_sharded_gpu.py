@@ -12,13 +12,40 @@ pytestmark = pytest.mark.gpu
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 
-@pytest.mark.parametrize("world", [2, 4])
-def test_sharded_execution_matches_checker(world):
-    if rt.device_count() < world:
-        pytest.skip("needs %d GPUs" % world)
+def _run(world, port, **env):
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", str(world),
-           "--master-addr", "127.0.0.1", "--master-port", str(29500 + world),
+           "--master-addr", "127.0.0.1", "--master-port", str(port),
            os.path.join(ROOT, "tests", "sharded_worker.py")]
-    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0", **env)
     res = subprocess.run(cmd, cwd=ROOT, env=env, capture_output=True, text=True, timeout=600)
     assert res.returncode == 0 and "SHARDED-OK" in res.stdout, res.stdout[-3000:] + res.stderr[-3000:]
+    return res.stdout
+
+
+@pytest.mark.parametrize("world", [2, 4])
+def test_sharded_execution_matches_checker(world):
+    """Reductions along the sharded axis finish across the GPUs inside their kernels
+    (peer-mapped exchange area): no collective launched between passes."""
+    if rt.device_count() < world:
+        pytest.skip("needs %d GPUs" % world)
+    out = _run(world, 29500 + world, B200_SHARDED_EXCHANGE="1")
+    assert "exchanges=0" not in out, out[-500:]
+
+
+@pytest.mark.parametrize("world", [2])
+def test_sharded_execution_with_collectives_between_passes(world):
+    """The same checks with the exchange area switched off: local reductions, then NCCL."""
+    if rt.device_count() < world:
+        pytest.skip("needs %d GPUs" % world)
+    out = _run(world, 29520 + world, B200_SHARDED_EXCHANGE="0")
+    assert "exchanges=0" in out, out[-500:]
+
+
+def test_a_missing_rank_makes_the_others_time_out_not_hang():
+    """Failure on the host side: one rank leaves a statement out.  The other ranks' reduction
+    kernels wait for its results at most the configured time, set the status word, return; the
+    host raises, and the next statement runs normally on all ranks.  (No GPU is made to fault;
+    plain peer stores, NVLS off.)"""
+    if rt.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    _run(2, 29541, B200_SHARDED_EXCHANGE="1", B200_SHARDED_MODE="expiry")
