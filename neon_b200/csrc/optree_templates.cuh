@@ -633,68 +633,74 @@ DEV void write_partial(const P& p, i64 k, int j, i64 pj, i64 pk, const float* a,
 // with the other GPUs' results for the same rows.  Instead of leaving that to a collective
 // launched after the kernel, the thread that holds a row's final local result exchanges it
 // itself: it stores the result into the exchange area of EVERY rank (peer-mapped memory, plain
-// stores over NVLink), then stores the launch number into a flag word next to it with release
-// semantics, waits until its own area shows the launch number of every rank for that row, and
+// stores over NVLink), waits until its own area holds every rank's result for that row, and
 // merges the W results in rank order -- the same order on every GPU, so all of them end up with
-// the same bits.  Nothing is read from a peer, and the wait is bounded in time: a rank that
-// never arrives sets bit 2 of the status word and the kernel carries on to its end.
-// Area layout (both halves alike; a launch uses half `epoch & 1`, so a rank that is one launch
-// ahead never overwrites what a slower rank still reads): data[W][cap] pairs of 32-bit words
-// (value bits, index or count), then flags[W][rows] launch numbers.
-//   P fields: x_table (device array of W area addresses), x_epoch, x_rank, x_world, x_cap,
-//   x_rows, x_col0 (first global column of the shard, added to arg-reduction indices).
+// the same bits.  Nothing is read from a peer.
+// Every 32-bit word travels in an aligned 64-bit store together with the launch number
+// (payload in the low half, launch number in the high half): such a store arrives whole or not
+// at all, so a word is valid exactly when its high half shows the current launch number, and
+// no fence is needed between "data" and "flag" -- a system-scope fence in the tail of a
+// bandwidth-bound kernel costs several microseconds, two of them cost more than the exchange.
+// A launch uses half `epoch & 1` of the area, so a rank that is one launch ahead never
+// overwrites what a slower rank still reads (it cannot get two ahead: it needs this rank's
+// results first).  The wait is bounded in time: a rank that never arrives sets bit 2 of the
+// status word and the kernel carries on to its end.
+// Area layout, both halves alike: entry[W][cap] of two 64-bit words (value, index or count).
+//   P fields: x_table (device array of W area addresses), x_epoch (never 0), x_rank, x_world,
+//   x_cap, x_col0 (first global column of the shard, added to arg-reduction indices).
 //   S::XCHG enables it; S::xc(r) says whether slot r spans the shards (a reduction of a
 //   replicated operand does not: every rank already holds the full result).
-DEV void st_sys_v2(u32* p, u32 a, u32 b) { asm volatile("st.relaxed.sys.global.v2.u32 [%0], {%1, %2};" ::"l"(p), "r"(a), "r"(b) : "memory"); }
-DEV void ld_sys_v2(const u32* p, u32& a, u32& b) { asm volatile("ld.relaxed.sys.global.v2.u32 {%0, %1}, [%2];" : "=r"(a), "=r"(b) : "l"(p) : "memory"); }
-DEV void st_release_sys(u32* p, u32 v) { asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory"); }
-DEV u32 ld_acquire_sys(const u32* p) { u32 v; asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory"); return v; }
+DEV void st_sys_u64(u64* p, u64 v) { asm volatile("st.relaxed.sys.global.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory"); }
+DEV u64 ld_sys_u64(const u64* p) { u64 v; asm volatile("ld.relaxed.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory"); return v; }
 DEV u64 xchg_ns() { u64 t; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t)); return t; }
 
 template <class S, class P, int NR>
 DEV void xchg_rows(const P& p, i64 k, float* a, int* ai) {
-    const u32 W = p.x_world, me = p.x_rank, epoch = p.x_epoch;
+    const u32 W = p.x_world, me = p.x_rank;
+    const u64 tag = (u64)p.x_epoch << 32;
     const u64* table = reinterpret_cast<const u64*>(p.x_table);
-    const u64 data_bytes = (u64)W * p.x_cap * 8u;
-    const u64 half = (u64)(epoch & 1u) * (data_bytes + (u64)W * p.x_rows * 4u);
+    const u64 half = (u64)(p.x_epoch & 1u) * ((u64)W * p.x_cap * 16u);
 #pragma unroll
     for (int r = 0; r < NR; ++r)
         if (S::op(r) == OP_ARGMAX || S::op(r) == OP_ARGMIN) ai[r] += p.x_col0;
     for (u32 q = 0; q < W; ++q) {
-        u32* data = reinterpret_cast<u32*>(__ldg(table + q) + half) + (u64)me * p.x_cap * 2u;
+        u64* entry = reinterpret_cast<u64*>(__ldg(table + q) + half) + (u64)me * p.x_cap * 2u;
 #pragma unroll
-        for (int r = 0; r < NR; ++r)
-            if (S::xc(r)) st_sys_v2(data + ((u64)r * p.K + k) * 2u, __float_as_uint(a[r]), (u32)ai[r]);
-    }
-    for (u32 q = 0; q < W; ++q) {
-        u32* flags = reinterpret_cast<u32*>(__ldg(table + q) + half + data_bytes);
-        st_release_sys(flags + (u64)me * p.x_rows + k, epoch);
-    }
-    const u64 mine = __ldg(table + me) + half;
-    const u32* myflags = reinterpret_cast<const u32*>(mine + data_bytes);
-    u64 t0 = 0;
-    bool gave_up = false;
-    for (u32 q = 0; q < W && !gave_up; ++q) {
-        while (ld_acquire_sys(myflags + (u64)q * p.x_rows + k) != epoch) {
-            if (t0 == 0) t0 = xchg_ns();
-            else if (xchg_ns() - t0 > p.wait_ns) {
-                if (p.status) atomicOr(reinterpret_cast<int*>(p.status), 4);
-                gave_up = true;
-                break;
-            }
+        for (int r = 0; r < NR; ++r) {
+            if (!S::xc(r)) continue;
+            u64* e = entry + ((u64)r * p.K + k) * 2u;
+            st_sys_u64(e, tag | __float_as_uint(a[r]));
+            if (red_is_arg(S::op(r))) st_sys_u64(e + 1, tag | (u32)ai[r]);
         }
     }
     float own[NR]; int owni[NR];
 #pragma unroll
     for (int r = 0; r < NR; ++r) { own[r] = a[r]; owni[r] = ai[r]; }
+    const u64* mine = reinterpret_cast<const u64*>(__ldg(table + me) + half);
+    u64 t0 = 0;
+    bool gave_up = false;
     for (u32 q = 0; q < W; ++q) {
-        const u32* data = reinterpret_cast<const u32*>(mine) + (u64)q * p.x_cap * 2u;
+        const u64* entry = mine + (u64)q * p.x_cap * 2u;
         float b[NR]; int bi[NR];
 #pragma unroll
         for (int r = 0; r < NR; ++r) {
-            u32 v = 0, i = 0;
-            if (S::xc(r)) ld_sys_v2(data + ((u64)r * p.K + k) * 2u, v, i);
-            b[r] = __uint_as_float(v); bi[r] = (int)i;
+            b[r] = red_init(S::op(r)); bi[r] = red_init_idx(S::op(r));
+            if (!S::xc(r)) continue;
+            const u64* e = entry + ((u64)r * p.K + k) * 2u;
+#pragma unroll
+            for (int w = 0; w < 2; ++w) {
+                if (w == 1 && !red_is_arg(S::op(r))) continue;
+                u64 v = ld_sys_u64(e + w);
+                while ((v >> 32) != (tag >> 32) && !gave_up) {
+                    if (t0 == 0) t0 = xchg_ns();
+                    else if (xchg_ns() - t0 > p.wait_ns) {
+                        if (p.status) atomicOr(reinterpret_cast<int*>(p.status), 4);
+                        gave_up = true;
+                    }
+                    v = ld_sys_u64(e + w);
+                }
+                if (w == 0) b[r] = __uint_as_float((u32)v); else bi[r] = (int)(u32)v;
+            }
         }
         if (q == 0) {
 #pragma unroll

@@ -588,7 +588,7 @@ class Planner(object):
         of several devices between passes); ``lin=(ncols, col0, local cols)`` makes
         element indices for random numbers those of a wider tensor this one is a
         column slice of; ``sharded`` names the operands (by index) that are column shards, and
-        ``xchg`` (a dict: table, rank, world, cap, rows, col0) makes every reduction that spans
+        ``xchg`` (a dict: table, rank, world, cap, col0) makes every reduction that spans
         them finish across the GPUs inside its kernel.
         Raises XchgUnsupported when the statement cannot use the exchange area."""
         self._lin = lin
@@ -1440,7 +1440,7 @@ class Planner(object):
         crossing = [bool(xchg) and self._spans_shards(st, r, self._sharded or ()) for r in reds]
         if not any(crossing):
             xchg = None
-        elif lanes_on_k or K > xchg["rows"] or len(reds) * K > xchg["cap"]:
+        elif lanes_on_k or len(reds) * K > xchg["cap"]:
             raise XchgUnsupported("reduction of %d x %d results does not fit the exchange area" % (len(reds), K))
         f = _Fields()
         em = self._Emit(st, f, ka, ra, lanes_on_k, res_buf, reds[0].level - 1, (self.unary, self.binary))
@@ -1557,7 +1557,6 @@ class Planner(object):
             f.u32("x_rank", xchg["rank"])
             f.u32("x_world", xchg["world"])
             f.u32("x_cap", xchg["cap"])
-            f.u32("x_rows", xchg["rows"])
             f.i32("x_col0", xchg["col0"])
             xc = " || ".join("r == %d" % i for i, c in enumerate(crossing) if c)
         src, pz.name = self._source(f, em, eval_tail, nr, ops, ep_lines, None, call, acc_tail=acc_tail, xc=xc)

@@ -19,7 +19,7 @@ module gives ``parallel=True`` a meaning:
   NVLink, waits (time-bounded) for the other ranks' results and merges them in
   rank order (``xchg_rows`` in the kernel header), so a statement is planned as
   on one GPU and no collective is launched between its passes.  Statements the
-  exchange area cannot carry (more than 4096 rows, reductions down a transposed
+  exchange area cannot carry (more than 16384 results, reductions down a transposed
   view) reduce locally and all-reduce the per-row results over NCCL instead;
 * random numbers and stochastic rounding use the element index in the global
   tensor, so stored values do not depend on how many GPUs share the work.
@@ -130,13 +130,13 @@ class ShardedBackend(B200Backend):
         self.host_max = host_max or (lambda v: v)
         self.collectives = 0                 # all-reduces issued so far
         self.exchanges = 0                   # reduction kernels that finished across the GPUs by themselves
-        # peer-mapped exchange area: rows x reductions it can carry per launch
+        # peer-mapped exchange area
         self._xchg, self._xchg_local, self._xepoch = None, 0, 0
         if world_size > 1 and comm and use_exchange:
-            rows, cap = 4096, 16384
-            nbytes = 2 * (world_size * cap * 8 + world_size * rows * 4)
+            cap = 16384                      # (rows x reductions) one launch can exchange
+            nbytes = 2 * world_size * cap * 16
             self._xchg_local, table = rt.xchg_create(comm, world_size, rank, nbytes)
-            self._xchg = {"table": table, "rank": rank, "world": world_size, "cap": cap, "rows": rows}
+            self._xchg = {"table": table, "rank": rank, "world": world_size, "cap": cap}
 
     # ---- factories: parallel=True -> column shard
     def _make(self, factory, shape, dtype, name, parallel, fill=None):

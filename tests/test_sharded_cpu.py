@@ -126,7 +126,7 @@ def _worker(rank, world, port, out):
     # ---- with an exchange area the reductions finish across the GPUs inside their kernels:
     #      statements are planned as on one GPU (moments in one pass, fused final epilogue),
     #      nothing is issued between the passes, every exchange pass gets its own launch number
-    be._xchg = {"table": 0x7D0000000000, "rank": rank, "world": world, "cap": 16384, "rows": 4096}
+    be._xchg = {"table": 0x7D0000000000, "rank": rank, "world": world, "cap": 16384}
     be._plans.clear()
     be.plans, be.calls = [], []
     y[:] = (x - be.mean(x, axis=1)) / be.sqrt(be.var(x, axis=1) + 1e-5) * gamma + beta
@@ -147,12 +147,12 @@ def _worker(rank, world, port, out):
     idx = be.empty((rows, 1), np.int32)
     idx[:] = be.argmax(x, axis=1)                  # indices become global columns before they are exchanged
     assert be.plans[0].uses_xchg and be.calls == []
-    # more rows than the area has flags for: back to collectives between the passes
-    tall = be.empty((8192, 64 * world), parallel=True)
-    tm = be.empty((8192, 1))
+    # more results than the area has room for: back to collectives between the passes
+    tall = be.empty((32768, 64 * world), parallel=True)
+    tm = be.empty((32768, 1))
     be.plans, be.calls = [], []
     tm[:] = be.max(tall, axis=1)
-    assert not any(p.uses_xchg for p in be.plans) and be.calls == [(1, 8192)]
+    assert not any(p.uses_xchg for p in be.plans) and be.calls == [(1, 32768)]
     gathered = [None] * world
     dist.all_gather_object(gathered, be._xepoch)
     assert all(g == gathered[0] for g in gathered)
