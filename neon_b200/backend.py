@@ -58,6 +58,34 @@ class _Scratch(object):
                 pass
 
 
+class _PlanCache(object):
+    """Least-recently-used cache of statement plans.  Keys hold shapes, strides and
+    alignments, so a workload that keeps cutting new views would otherwise grow it
+    without bound (every entry keeps its generated source alive)."""
+
+    def __init__(self, capacity=4096):
+        import collections
+        self.capacity = capacity
+        self._d = collections.OrderedDict()
+
+    def get(self, key):
+        plan = self._d.get(key)
+        if plan is not None:
+            self._d.move_to_end(key)
+        return plan
+
+    def __setitem__(self, key, plan):
+        self._d[key] = plan
+        if len(self._d) > self.capacity:
+            self._d.popitem(last=False)
+
+    def __len__(self):
+        return len(self._d)
+
+    def clear(self):
+        self._d.clear()
+
+
 class CapturedGraph(object):
     """A recorded statement sequence (see ``B200Backend.capture``)."""
 
@@ -85,8 +113,10 @@ class B200Backend(OpTreeBackend):
                  deterministic_update=False, deterministic=None, device_id=0, bench=False,
                  scratch_size=0, hist_bins=64, hist_offset=-48, compat_mode=None,
                  enable_winograd=True, cache_dir=None, num_devices=None, max_devices=None,
-                 precise_math=False):
+                 precise_math=False, check_bounds=None):
         self.enable_winograd = enable_winograd        # read by neon's fixtures; no convolutions here
+        import os
+        self.check_bounds = bool(int(os.environ.get("B200EW_CHECK", "0"))) if check_bounds is None else bool(check_bounds)
         if default_dtype not in (np.float16, np.float32) and np.dtype(default_dtype).name != "bfloat16":
             raise ValueError("Default data type for the b200 backend must be float16 or 32")
         if rt.device_count() <= int(device_id):
@@ -108,7 +138,7 @@ class B200Backend(OpTreeBackend):
         rt.memset(self._status, 0, 1, 256)
         self._planner.status_ptr = self._status
         self._kernels = {}
-        self._plans = {}                   # program_key -> BoundPlan
+        self._plans = _PlanCache()         # program_key -> BoundPlan
         self._temps = {}
         self._temps_used = {}
         self._marks = []
@@ -399,7 +429,52 @@ class B200Backend(OpTreeBackend):
     def _run(self, out, expr):
         self._run_stack(out, OpTreeNode({"op": "assign"}, out, expr).traverse([]))
 
+    # ------------------------------------------------------------------ checked mode
+    def check_operands(self, stack):
+        """Checked mode (``check_bounds=True`` or B200EW_CHECK=1): before a statement is launched,
+        every tensor's addressed span -- lowest to highest element its shape and strides reach --
+        must lie inside the allocation it views, and every index vector of a fancy-indexed
+        operand is read back and must stay inside the indexed axis.  A violation raises
+        B200Error(B200_ERR_INVALID) and nothing is launched.  Costs a host loop per statement and
+        a device-to-host copy per index vector, so it is a debugging aid, off by default."""
+        for s in stack:
+            if type(s) is dict:
+                s = s.get("idx")
+            if not isinstance(s, B200Tensor):
+                continue
+            block = s._block
+            taken = s.take_array[1] if s.take_array else None
+            if block is not None:
+                lo = hi = 0
+                for axis, (d, st) in enumerate(zip(s.shape, s.strides)):
+                    if axis == taken:
+                        continue                     # addressed through the index vector, checked below
+                    if d == 0:
+                        lo = hi = None
+                        break
+                    if st >= 0:
+                        hi += (d - 1) * st
+                    else:
+                        lo += (d - 1) * st
+                if lo is not None:
+                    isz = s.dtype.itemsize
+                    first, last = s.gpudata + lo * isz, s.gpudata + (hi + 1) * isz
+                    if first < block.ptr or last > block.ptr + block.nbytes:
+                        raise rt.B200Error(-1, "tensor %s (shape %s, strides %s) reaches bytes [%d, %d) of an "
+                                           "allocation of %d bytes" % (s.name, s.shape, s.strides,
+                                                                       first - block.ptr, last - block.ptr, block.nbytes))
+            if s.take_array:
+                vec, axis = s.take_array
+                base = s.base if s.base is not None else s
+                extent = base.shape[axis] if axis < len(base.shape) else 0
+                idx = vec.get().reshape(-1)
+                if idx.size and (int(idx.min()) < 0 or int(idx.max()) >= extent):
+                    raise rt.B200Error(-1, "index vector of %s holds %d..%d for an axis of %d entries"
+                                       % (s.name, int(idx.min()), int(idx.max()), extent))
+
     def _run_stack(self, out, stack):
+        if self.check_bounds:
+            self.check_operands(stack)
         rounding = self._rounding_bits(out)
         key = (program_key(stack), rounding)
         plan = self._plans.get(key)

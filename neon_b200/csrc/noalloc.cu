@@ -20,6 +20,7 @@
 #include <cuda_runtime.h>
 
 #include <cstdio>
+#include <mutex>
 
 extern "C" int b200_detail_reduce_full(uint64_t in, int32_t dtype, uint64_t count, int32_t op, int32_t absolute,
                                        uint64_t out, uint64_t scratch, int sm_count, void* stream);
@@ -41,6 +42,7 @@ struct PerDevice {
     int sm_count = 0;
 };
 PerDevice g_dev[kMaxDevices];
+std::mutex g_dev_mu;
 
 }  // namespace
 
@@ -68,6 +70,7 @@ extern "C" b200_status b200_reduce_full_noalloc(uint64_t in, int32_t dtype, uint
     if (dev < 0 || dev >= kMaxDevices) return b200_detail_fail(B200_ERR_UNSUPPORTED, "device ordinal out of range");
 
     PerDevice& d = g_dev[dev];
+    std::lock_guard<std::mutex> lock(g_dev_mu);      // two host threads may make the first call together
     if (!d.scratch) {
         // first call on this device (it is the current one): resolve the array's device address
         void* p = nullptr;

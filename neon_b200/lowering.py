@@ -185,20 +185,31 @@ def program_key(stack):
     allocation, ops and axes -- and nothing that is a run-time argument
     (addresses, values of python numbers)."""
     out = stack[0]
+    out_block = getattr(out, "_block", None)
     seen = {}
     key = []
+    add = key.append
     for s in stack:
-        if isinstance(s, Tensor):
+        t = type(s)
+        if t is dict:
+            idx = s.get("idx")
+            add((s["op"], s.get("axis"), None if idx is None else seen.setdefault(id(idx), len(seen))))
+        elif t is float or t is int:
+            add(None)
+        elif isinstance(s, Tensor):
             ix = seen.setdefault(id(s), len(seen))
             pk = getattr(s, "_plan_key", None)
             if pk is None:
                 pk = (s.dtype.str, s.shape, s.strides, s.ptr & 15, s.take_array[1] if s.take_array else None)
-            key.append((ix, pk, s is not out and shares_memory(s, out)))
-        elif type(s) is dict:
-            idx = s.get("idx")
-            key.append((s["op"], s.get("axis"), None if idx is None else seen.setdefault(id(idx), len(seen))))
+            if s is out:
+                alias = False
+            elif out_block is not None and getattr(s, "_block", None) is not None:
+                alias = s._block is out_block
+            else:
+                alias = shares_memory(s, out)
+            add((ix, pk, alias))
         else:
-            key.append(None)
+            add(None)
     return tuple(key)
 
 

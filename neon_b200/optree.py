@@ -36,6 +36,9 @@ class OpCollection(object):
     ew_ops = float_ops - {"dot", "transpose"}
 
 
+_EW_NOT_ASSIGN = frozenset(OpCollection.ew_ops - {"assign"})
+
+
 def _binary(op, swap=False):
     if swap:
         def f(self, other):
@@ -133,15 +136,25 @@ class Tensor(_Operators):
         return self.set(a)
 
 
+_ONE, _NONE = (1, 1), (0, 0)
+
+
 def _shape2(x):
     """2-d shape used for inference: tensors/nodes their own, numbers (1,1),
-    None (0,0) (backend.py:1793-1812)."""
-    if isinstance(x, (OpTreeNode, Tensor)):
-        s = tuple(x.shape)
-        return s + (1,) if len(s) == 1 else s
+    None (0,0) (backend.py:1793-1812); False for anything that cannot be an operand."""
+    t = type(x)
+    if t is OpTreeNode:
+        return x[0]["shape"]
+    if t is float or t is int:
+        return _ONE
+    if x is None:
+        return _NONE
+    if isinstance(x, Tensor):
+        s = x.shape
+        return s if len(s) == 2 else (tuple(s) + (1,) if len(s) == 1 else tuple(s))
     if isinstance(x, (int, float)):
-        return (1, 1)
-    return (0, 0)
+        return _ONE
+    return False
 
 
 class OpTreeNode(_Operators, tuple):
@@ -174,12 +187,16 @@ class OpTreeNode(_Operators, tuple):
         (or a non-None ``out``) executes the tree at once through the backend
         of the destination tensor (backend.py:1776-1850).
         """
-        for arg in (a, b):
-            if not isinstance(arg, (int, float, Tensor, OpTreeNode, type(None))):
-                return NotImplemented
         sa, sb = _shape2(a), _shape2(b)
-        if op in OpCollection.ew_ops and op != "assign":
-            shape = (max(sa[0], sb[0]), max(sa[1], sb[1]))
+        if sa is False or sb is False:
+            return NotImplemented
+        if op in _EW_NOT_ASSIGN:
+            s0, s1 = sa[0], sa[1]
+            if sb[0] > s0:
+                s0 = sb[0]
+            if sb[1] > s1:
+                s1 = sb[1]
+            shape = (s0, s1)
         elif op in OpCollection.reduction_ops:
             if "axis" in kwargs:
                 shape = list(sa)

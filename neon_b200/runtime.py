@@ -185,6 +185,13 @@ def mem_stats():
     return {"in_use": a.value, "cached": b.value, "peak": c.value, "device_allocs": d.value}
 
 
+def mem_info():
+    """(free, total) device memory in bytes, as the driver reports it."""
+    f, t = u64(0), u64(0)
+    check(lib().b200_mem_info(C.byref(f), C.byref(t)))
+    return f.value, t.value
+
+
 def host_alloc(nbytes):
     p = C.c_void_p(0)
     check(lib().b200_host_alloc(nbytes, C.byref(p)))

@@ -206,14 +206,16 @@ class ShardedBackend(B200Backend):
         if isinstance(out, ShardedTensor):
             lin = out.flat_of if out.flat_of else (out.shape[1], out.c0, out.local.shape[1])
         local_stack = [s.local if isinstance(s, ShardedTensor) else s for s in stack]
+        if self.check_bounds:
+            self.check_operands(local_stack)
         rounding = self._rounding_bits(local_stack[0])
         key = (program_key(local_stack), rounding, lin)
         cached = self._plans.get(key)
         if cached is None:
             uses_rng = bool(rounding) or any(type(s) is dict and s["op"] == "rand" for s in stack)
             # random words need element coordinates: a flat pass can supply them only when
-            # no block straddles a row of the shard (8192 elements per block at most)
-            row_ok = lin is not None and out.flat_of is None and lin[2] % 8192 == 0
+            # no block straddles a row of the shard (the pass shrinks its blocks to 2048 elements if it has to)
+            row_ok = lin is not None and out.flat_of is None and lin[2] % 2048 == 0
             st = Statement(local_stack, allow_flat=(not uses_rng) or row_ok)
             crosses = st.has_red and st.axis == 1
             local_ids = set(id(s.local) for s in sharded)

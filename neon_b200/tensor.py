@@ -91,7 +91,10 @@ class B200Tensor(Tensor):
         self.size = size
         self.dtype = dtype
         self.nbytes = dtype.itemsize * size
-        self.strides = _contiguous_strides(self.shape) if strides is None else tuple(int(s) for s in strides)
+        if strides is None:
+            self.strides = _contiguous_strides(self.shape)
+        else:                                    # a view of fewer than two axes was padded with unit axes
+            self.strides = tuple(int(s) for s in strides) + (1,) * (len(self.shape) - len(strides))
         self.base = base
         self.allocator = allocator
         self.take_array = take_array
@@ -143,75 +146,76 @@ class B200Tensor(Tensor):
                               name=self.name if name is None else name, rounding=self.rounding,
                               _block=self._block)
 
-    # ---- indexing (nervanagpu.py:193-323)
-    def __getitem__(self, index):
-        if not isinstance(index, tuple):
-            if isinstance(index, slice) and index == _none_slice:
-                return self
-            index = (index,)
-        new_shape, new_strides, offset = [], [], 0
-        take_array = None
-        seen_ellipsis = False
-        ia = aa = 0
-        while ia < len(index):
-            e = index[ia]
-            if aa > len(self.shape):
-                raise IndexError("too many axes in index")
+    # ---- indexing: same views, limits and messages as GPUTensor.__getitem__ (nervanagpu.py:193-323)
+    def _index_records(self, index):
+        """One record per axis of this tensor for the subscript ``index`` (a tuple):
+        ("slice", first, step, count), ("at", position), ("take", int32 index tensor)."""
+        ndim = len(self.shape)
+        plain = [e for e in index if e is not Ellipsis]
+        if len(index) - len(plain) > 1:
+            raise IndexError("more than one ellipsis not allowed in index")
+        if len(plain) > ndim:
+            raise IndexError("invalid use of ellipsis in index" if len(plain) < len(index)
+                             else "too many axes in index")
+        everything = slice(None, None, None)
+        expanded = []
+        for e in index:
+            if e is Ellipsis:
+                expanded.extend([everything] * (ndim - len(plain)))
+            else:
+                expanded.append(e)
+        expanded.extend([everything] * (ndim - len(expanded)))
+        records = []
+        for axis, e in enumerate(expanded):
+            extent = self.shape[axis]
             if isinstance(e, slice):
-                start, stop, step = e.indices(self.shape[aa])
-                new_shape.append(-((start - stop) // step))
-                new_strides.append(step * self.strides[aa])
-                offset += self.strides[aa] * start * self.dtype.itemsize
-                ia += 1
-                aa += 1
+                first, stop, step = e.indices(extent)
+                records.append(("slice", first, step, max(0, -((first - stop) // step))))
             elif isinstance(e, (B200Tensor, np.ndarray, list, tuple)):
                 if isinstance(e, (list, tuple)):
                     e = np.array(e, dtype=np.int32)
                 if isinstance(e, np.ndarray):
                     e = self.__class__(self.backend, e.shape, dtype=np.int32).set(e)
-                size = max(e.shape)
-                if size != e.size:
+                if max(e.shape) != e.size:
                     raise IndexError("Fancy indexing only currently supported dim > 1 in a single dimension.")
-                if take_array is not None:
+                if any(r[0] == "take" for r in records):
                     raise IndexError("Fancy indexing only currently supported one axis at a time.")
                 if e.dtype.type is not np.int32:
                     raise IndexError("Fancy indexing only currently supported with int32 types.")
-                take_array = (e, aa)
-                new_shape.append(size)
-                new_strides.append(self.strides[aa])
-                ia += 1
-                aa += 1
+                records.append(("take", e))
             elif isinstance(e, (int, np.integer)):
-                dim = self.shape[aa]
-                if e < 0:
-                    e += dim
-                if not (0 <= e < dim):
-                    raise IndexError("subindex in axis %d out of range" % ia)
-                offset += self.strides[aa] * int(e) * self.dtype.itemsize
-                if len(self.shape) < 3:
-                    new_shape.append(1)
-                    new_strides.append(self.strides[aa])
-                ia += 1
-                aa += 1
-            elif e is Ellipsis:
-                ia += 1
-                target = len(self.shape) - (len(index) - ia)
-                if target < aa:
-                    raise IndexError("invalid use of ellipsis in index")
-                while aa < target:
-                    new_shape.append(self.shape[aa])
-                    new_strides.append(self.strides[aa])
-                    aa += 1
-                if seen_ellipsis:
-                    raise IndexError("more than one ellipsis not allowed in index")
-                seen_ellipsis = True
+                position = int(e) + extent if e < 0 else int(e)
+                if not 0 <= position < extent:
+                    raise IndexError("subindex in axis %d out of range" % axis)
+                records.append(("at", position))
             else:
-                raise IndexError("invalid subindex in axis %d" % ia)
-        while aa < len(self.shape):
-            new_shape.append(self.shape[aa])
-            new_strides.append(self.strides[aa])
-            aa += 1
-        return self._view(tuple(new_shape), new_strides, offset, take_array=take_array)
+                raise IndexError("invalid subindex in axis %d" % axis)
+        return records
+
+    def __getitem__(self, index):
+        if not isinstance(index, tuple):
+            if isinstance(index, slice) and index == _none_slice:
+                return self
+            index = (index,)
+        shape, strides, offset, take_array = [], [], 0, None
+        keep_unit_axes = len(self.shape) < 3          # a matrix stays a matrix: x[3] is a (1, n) row
+        for axis, record in enumerate(self._index_records(index)):
+            pitch = self.strides[axis]
+            if record[0] == "slice":
+                _, first, step, count = record
+                offset += first * pitch
+                shape.append(count)
+                strides.append(step * pitch)
+            elif record[0] == "at":
+                offset += record[1] * pitch
+                if keep_unit_axes:
+                    shape.append(1)
+                    strides.append(pitch)
+            else:
+                take_array = (record[1], axis)
+                shape.append(record[1].size)
+                strides.append(pitch)
+        return self._view(tuple(shape), strides, offset * self.dtype.itemsize, take_array=take_array)
 
     # ---- assignment (nervanagpu.py:334-383)
     def _assign(self, value):

@@ -156,6 +156,51 @@ def test_single_pass_moments_match_checker(case, b200):
     _compare(case, plain, _oracle64(case))
 
 
+def test_checked_mode_refuses_out_of_range_operands_without_launching():
+    """Checked mode: a view that reaches past its allocation, or an index vector that points
+    outside the indexed axis, raises B200_ERR_INVALID before anything is launched."""
+    from neon_b200 import runtime as rt
+    from neon_b200.backend import B200Backend
+    from neon_b200.tensor import B200Tensor
+    be = B200Backend(rng_seed=0, check_bounds=True)
+    t = be.array(np.arange(400, dtype=np.float32).reshape(4, 100))
+    out = be.empty((4, 100))
+    out[:] = t * 2.0                                              # in range: runs
+    assert np.array_equal(out.get(), 2.0 * np.arange(400, dtype=np.float32).reshape(4, 100))
+    bad = B200Tensor(be, (4, 100), np.float32, gpudata=t.gpudata, strides=(200, 1), base=t, _block=t._block)
+    before = be.launches
+    with pytest.raises(rt.B200Error) as e:
+        out[:] = bad + 1.0
+    assert e.value.status == -1 and be.launches == before
+    idx = be.array(np.array([[0, 3, 7]], dtype=np.int32), dtype=np.int32)     # rows 0..3 exist
+    got = be.empty((3, 100))
+    with pytest.raises(rt.B200Error) as e:
+        got[:] = t.take(idx, axis=0) * 1.0
+    assert e.value.status == -1 and be.launches == before
+    idx.set(np.array([[0, 3, 2]], dtype=np.int32))
+    got[:] = t.take(idx, axis=0) * 1.0
+    assert np.array_equal(got.get(), np.arange(400, dtype=np.float32).reshape(4, 100)[[0, 3, 2]])
+
+
+def test_view_and_fuzz_statements_pass_checked_mode(b200):
+    """The random views and random statements of the other tests once more with every operand
+    checked against its allocation before each launch."""
+    from tests import fuzz
+    b200.check_bounds = True
+    try:
+        for seed in range(0, 160, 4):
+            spec = fuzz.Spec(seed)
+            fuzz.build(b200, spec, fuzz.host_arrays(spec))
+        base = b200.array(np.arange(6 * 7 * 8, dtype=np.float32).reshape(6, 56))
+        host = np.arange(6 * 7 * 8, dtype=np.float32).reshape(6, 56)
+        for sub in ((slice(1, 5), slice(3, 50, 3)), (slice(None), slice(55, None, -2)), (2, slice(None)), (slice(None), 7)):
+            out = b200.empty(base[sub].shape)
+            out[:] = base[sub] + 1.0
+            assert np.array_equal(out.get().reshape(-1), (host[sub] + 1.0).reshape(-1)), sub
+    finally:
+        b200.check_bounds = False
+
+
 def test_bounded_wait_reports_instead_of_hanging():
     """The one software wait in the kernels (a block waiting for its TMA-staged row slice)
     has a time limit.  Announce 16 bytes that never arrive, give it 20 ms: the kernel must

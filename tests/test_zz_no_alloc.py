@@ -30,10 +30,19 @@ def _both(values, op, absolute):
         rt.reduce_full(src, dt, values.size, op, absolute, out_a, scratch)
         rt.memcpy_d2h(ref.ctypes.data, out_a, 4)
         got = []
-        for _ in range(2):                               # two calls in a row share the static scratch
+        for i in range(2):                               # two calls in a row share the static scratch
             res = np.full(1, np.nan, np.float32)
             rt.memset(out_b, 0xFF, 1, 4)
+            rt.stream_sync()
+            allocs_before, free_before = rt.mem_stats()["device_allocs"], rt.mem_info()[0]
             rt.reduce_full_noalloc(src, dt, values.size, op, absolute, out_b)
+            rt.stream_sync()
+            # the call itself allocated nothing: neither through this library's arena nor,
+            # as far as the driver's free-memory figure shows, any other way (after the first
+            # call, which may load the library's device code on this GPU)
+            assert rt.mem_stats()["device_allocs"] == allocs_before
+            if i == 1:
+                assert rt.mem_info()[0] == free_before
             rt.memcpy_d2h(res.ctypes.data, out_b, 4)
             got.append(float(res[0]))
         return float(ref[0]), got
@@ -49,10 +58,13 @@ def test_noalloc_reduction_equals_ordinary_entry_point_twice(n, dtype):
     for op, absolute in ((rt.SUM, False), (rt.MAX, True), (rt.MIN, False)):
         ref, got = _both(v, op, absolute)
         assert got[0] == ref and got[1] == ref, (op, absolute, ref, got)
-    # and the value is right, not merely consistent
-    ref, got = _both(v, rt.SUM, False)
+    # and the values are right, not merely consistent
     v64 = v.astype(np.float64)
+    ref, got = _both(v, rt.SUM, False)
     assert abs(got[1] - v64.sum()) <= 1e-5 * np.abs(v64).sum()
+    assert _both(v, rt.MAX, True)[1][1] == float(np.abs(v).max().astype(np.float32))
+    assert _both(v, rt.MIN, False)[1][1] == float(v.min().astype(np.float32))
+    assert _both(v, rt.MAX, False)[1][1] == float(v.max().astype(np.float32))
 
 
 def test_noalloc_refuses_inputs_beyond_its_maximum():
