@@ -263,7 +263,7 @@ def test_full_size_adam_against_checker_on_a_sample(b200):
                 check_output("adam 1e8 step %d/%s" % (step, name), dev[:, col:col + 1].get(), ref.get(), np.float32)
     # the other columns moved too: the whole tensor, not just the sampled column, was updated
     moved = np.abs(param.get() - ph)
-    assert moved.min() > 0 and abs(np.median(moved[:, col]) / np.median(moved[:, 7]) - 1) < 0.05
+    assert (moved == 0).mean() < 1e-5 and abs(np.median(moved[:, col]) / np.median(moved[:, 7]) - 1) < 0.05
 
 
 def test_full_size_properties_cfg5(b200):
