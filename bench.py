@@ -47,11 +47,12 @@ Z_BYTES_PER_ELEMENT = 6                # dominant kernel: read x, y (fp16), writ
 METRIC = "compound-optree effective HBM GB/s"
 WORKLOAD = ("cfg5: z=tanh(x)*sqrt(|y|)+0.5*x*y (fp16, stochastic rounding), "
             "total=sum(z), peak=max|z|")
-# DRAM traffic of the z kernel from ncu (profiles/ew_kernel_cfg5_fp16_chain.md): reads scale with
-# the element count (4.0003 bytes per element); writes are 2 bytes per element minus what is
-# still in L2 when the kernel ends, a constant that does not grow with the launch (31.6 MB)
-Z_DRAM_READ_PER_ELEMENT = 268.459264e6 / (1 << 26)
-Z_DRAM_WRITE_L2_RESIDUE = 134.217728e6 - 102.589184e6
+# DRAM traffic of the z kernel from ncu (profiles/ew_kernel_cfg5_fp16_chain.md, a 2^29-element
+# launch: 2,147,534,592 bytes read, 1,041,722,112 written): reads scale with the element count
+# (4.0001 bytes per element); writes are 2 bytes per element minus what is still in L2 when the
+# kernel ends, a constant that does not grow with the launch (32.0 MB)
+Z_DRAM_READ_PER_ELEMENT = 2147534592.0 / (1 << 29)
+Z_DRAM_WRITE_L2_RESIDUE = 2.0 * (1 << 29) - 1041722112.0
 
 
 def measured_peak():
@@ -651,8 +652,8 @@ def main():
                      "peak": peak_gbs, "peak_kind": peak_kind, "unit": "GB/s",
                      "frac": z_gbs / peak_gbs, "frac_of_8TBps": z_gbs / 8000.0, "ms_per_launch": z_ms,
                      "algorithmic_bytes_per_launch": n_local * Z_BYTES_PER_ELEMENT, "traffic": traffic,
-                     "traffic_source": "ncu capture of a 2^26-element launch: DRAM reads scaled by the element "
-                                       "count, writes = 2 B/element minus the 31.6 MB still in L2 at kernel end"},
+                     "traffic_source": "ncu capture of a 2^29-element launch: DRAM reads scaled by the element "
+                                       "count, writes = 2 B/element minus the 32.0 MB still in L2 at kernel end"},
         "e2e": {"value": e2e_value, "unit": "GB/s", "h2d_bytes_per_step": 2 * nbytes * world,
                 "d2h_bytes_per_step": 8 * world, "steps": e2e_steps, "ms_per_step": e2e_ms / e2e_steps},
         "gpu_launches": launches, "clocks": clocks, "breakdown": breakdown,
