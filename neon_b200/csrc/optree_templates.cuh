@@ -515,8 +515,9 @@ template <class S, int NR> DEV void finish_slots(float* a, const int* ai) {
 // MODE 1: flat (K == 1, all operands contiguous), scalar tail of N % V elements.
 // MODE 2: 2-d with long rows: blockIdx.y/z select the row, blockIdx.x tiles it.
 // MODE 3: flat over a contiguous 2-d tensor whose row length is p.flat_bpr times the elements
-//         one block handles: like MODE 1, but k carries the row of the block (one 32-bit
-//         division per thread) for statements that need element coordinates.
+//         one block handles: like MODE 1, but k carries the row of the block for statements
+//         that need element coordinates; the grid is (p.flat_bpr, rows), so the row is
+//         blockIdx.y/z and no thread divides.
 // IDX32: the host guarantees that element counts and byte offsets fit 32 bits, so vector
 //        indices are computed in 32-bit arithmetic (widening multiply-adds for addresses).
 // One evaluated vector into the per-lane accumulators.  Generated code sets S::FUSED and
@@ -557,7 +558,8 @@ DEV void accumulate_one(const float (&out)[NR][1], int idx, float (&acc)[NR][V],
     }
 }
 
-// The work of one block: `bx` is the block's index along x, `row` its row (MODE 2 only).
+// The work of one block: `bx` is the block's index along x (MODE 3: among all blocks), `row` its
+// row (MODE 2 and 3).
 template <template <int> class SV, class P, int V, int BLOCK, int UNROLL, int MODE, bool IDX32 = false>
 DEV void ew_body(const P& p, u32 bx, i64 row) {
     typedef SV<V> S;
@@ -570,7 +572,7 @@ DEV void ew_body(const P& p, u32 bx, i64 row) {
     if constexpr (MODE == 2) krow = row;
     // MODE 3: k carries, instead of the row r itself, the amount to add to a flat index of row r to
     // get the element index in the enclosing tensor: lin_0 + r * lin_r
-    if constexpr (MODE == 3) krow = p.lin_0 + (i64)(bx / (u32)p.flat_bpr) * p.lin_r;
+    if constexpr (MODE == 3) krow = p.lin_0 + row * p.lin_r;
     if (MODE == 2 && krow >= p.K) return;
     typename S::L l[UNROLL];
     typename S::H h[UNROLL];
@@ -612,7 +614,13 @@ DEV void ew_body(const P& p, u32 bx, i64 row) {
 
 template <template <int> class SV, class P, int V, int BLOCK, int UNROLL, int MODE, bool IDX32 = false>
 DEV void ew_kernel(const P& p) {
-    ew_body<SV, P, V, BLOCK, UNROLL, MODE, IDX32>(p, blockIdx.x, MODE == 2 ? (i64)blockIdx.y + (i64)blockIdx.z * gridDim.y : 0);
+    const i64 row = (MODE == 2 || MODE == 3) ? (i64)blockIdx.y + (i64)blockIdx.z * gridDim.y : 0;
+    if constexpr (MODE == 3) {
+        if (row >= p.flat_rows) return;              // a grid padded in z
+        ew_body<SV, P, V, BLOCK, UNROLL, MODE, IDX32>(p, (u32)row * p.flat_bpr + blockIdx.x, row);
+    } else {
+        ew_body<SV, P, V, BLOCK, UNROLL, MODE, IDX32>(p, blockIdx.x, row);
+    }
 }
 // ================================================================== split-reduction finish
 // Partials of reduction r, kept index k, split j live at r*K*SPLIT + j*pj + k*pk.
@@ -654,21 +662,24 @@ DEV void st_sys_u64(u64* p, u64 v) { asm volatile("st.relaxed.sys.global.u64 [%0
 DEV u64 ld_sys_u64(const u64* p) { u64 v; asm volatile("ld.relaxed.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory"); return v; }
 DEV u64 xchg_ns() { u64 t; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t)); return t; }
 
-template <class S, class P, int NR>
-DEV void xchg_rows(const P& p, i64 k, float* a, int* ai) {
+// PUT: this thread also publishes (a, ai) as this GPU's result; without it the thread only
+// collects (a block of a cluster whose leader block publishes).  `base`: first entry slot of the
+// pass when one launch exchanges the results of several passes.
+template <class S, class P, int NR, bool PUT = true>
+DEV void xchg_rows(const P& p, i64 k, float* a, int* ai, u32 base = 0) {
     const u32 W = p.x_world, me = p.x_rank;
     const u64 tag = (u64)p.x_epoch << 32;
     const u64* table = reinterpret_cast<const u64*>(p.x_table);
     const u64 half = (u64)(p.x_epoch & 1u) * ((u64)W * p.x_cap * 16u);
 #pragma unroll
     for (int r = 0; r < NR; ++r)
-        if (S::op(r) == OP_ARGMAX || S::op(r) == OP_ARGMIN) ai[r] += p.x_col0;
-    for (u32 q = 0; q < W; ++q) {
+        if (S::xc(r) && (S::op(r) == OP_ARGMAX || S::op(r) == OP_ARGMIN)) ai[r] += p.x_col0;
+    for (u32 q = 0; PUT && q < W; ++q) {
         u64* entry = reinterpret_cast<u64*>(__ldg(table + q) + half) + (u64)me * p.x_cap * 2u;
 #pragma unroll
         for (int r = 0; r < NR; ++r) {
             if (!S::xc(r)) continue;
-            u64* e = entry + ((u64)r * p.K + k) * 2u;
+            u64* e = entry + ((u64)(base + r) * p.K + k) * 2u;
             st_sys_u64(e, tag | __float_as_uint(a[r]));
             if (red_is_arg(S::op(r))) st_sys_u64(e + 1, tag | (u32)ai[r]);
         }
@@ -686,7 +697,7 @@ DEV void xchg_rows(const P& p, i64 k, float* a, int* ai) {
         for (int r = 0; r < NR; ++r) {
             b[r] = red_init(S::op(r)); bi[r] = red_init_idx(S::op(r));
             if (!S::xc(r)) continue;
-            const u64* e = entry + ((u64)r * p.K + k) * 2u;
+            const u64* e = entry + ((u64)(base + r) * p.K + k) * 2u;
 #pragma unroll
             for (int w = 0; w < 2; ++w) {
                 if (w == 1 && !red_is_arg(S::op(r))) continue;
@@ -1221,7 +1232,7 @@ DEV void rr_pass(const P& q, const P& p, i64 k, i64 knext, RowCtx& cx, unsigned 
 // order, so results repeat exactly); the other warps only take part in the barriers.  Blocks
 // PUSH their result into every peer's slots before the cluster barrier, so that after it each
 // block reads only its own shared memory.
-template <template <int> class SV, class P, int V, int C, int THREADS>
+template <template <int> class SV, class P, int V, int C, int THREADS, int XBASE = 0>
 DEV void rr_combine(const P& q, i64 k, const RowCtx& cx, float* a, int* ai, float (*sv)[THREADS / 32],
                     int (*si)[THREADS / 32], u32* slots /* [2 parities][NR][C][2] of this pass */, u32* res) {
     typedef SV<V> S;
@@ -1247,7 +1258,31 @@ DEV void rr_combine(const P& q, i64 k, const RowCtx& cx, float* a, int* ai, floa
             }
         }
     }
-    if constexpr (C > 1) {
+    if constexpr (C > 1 && S::XCHG) {
+        // the row also spans other GPUs: warp 0 folds the C block results, thread 0 of the
+        // cluster's first block publishes the GPU's result to every rank, thread 0 of every
+        // block collects the W results (xchg_rows) and leaves the row's result in res
+        cluster_barrier_warp0_releases();
+        if (warp == 0) {
+#pragma unroll
+            for (int r = 0; r < NR; ++r) {
+                const u32* entry = mine + (r * C + (lane < C ? lane : 0)) * 2;
+                a[r] = __uint_as_float(entry[0]);
+                ai[r] = red_is_arg(S::op(r)) ? (int)entry[1] : -1;
+            }
+#pragma unroll
+            for (int o = C / 2; o > 0; o >>= 1) shfl_merge<S, NR>(a, ai, o);
+            if (lane == 0) {
+                if (cx.rank == 0) xchg_rows<S, P, NR, true>(q, k, a, ai, XBASE);
+                else xchg_rows<S, P, NR, false>(q, k, a, ai, XBASE);
+                finish_slots<S, NR>(a, ai);
+                S::fixup(q, k, a, ai);
+#pragma unroll
+                for (int r = 0; r < NR; ++r) res[r] = (S::op(r) == OP_ARGMAX || S::op(r) == OP_ARGMIN) ? (u32)ai[r] : __float_as_uint(a[r]);
+            }
+        }
+        __syncthreads();
+    } else if constexpr (C > 1) {
         cluster_barrier_warp0_releases();
         // every warp folds the C block results for itself (same values, same order) and leaves
         // them in res: no hand-over between warps, so no block barrier.  res of this pass is next
@@ -1269,6 +1304,7 @@ DEV void rr_combine(const P& q, i64 k, const RowCtx& cx, float* a, int* ai, floa
         __syncwarp();
     } else {
         if (threadIdx.x == 0) {
+            if constexpr (S::XCHG) xchg_rows<S, P, NR, true>(q, k, a, ai, XBASE);
             finish_slots<S, NR>(a, ai);
             S::fixup(q, k, a, ai);
 #pragma unroll

@@ -616,7 +616,7 @@ class Planner(object):
         full_shape = self._full_shape(st)
         root_is_k = st.root.shape[ra] == 1
         out_is_k = st.out_shape[ra] == 1
-        if fuse_final and levels and self.rowres and xchg is None:
+        if fuse_final and levels and self.rowres:
             pz = self._rowres_pass(st, reds, levels, ka, ra, full_shape, rounding, root_is_k and out_is_k)
             if pz is not None:
                 return [pz]
@@ -769,6 +769,13 @@ class Planner(object):
         K, N = full_shape[ka], full_shape[ra]
         if rounding or any(n.kind == "z" for n in st.nodes):
             return None
+        # rows that continue on other GPUs: each pass's results are exchanged in rr_combine
+        xchg = self._xchg
+        crossing = dict((r.nid, bool(xchg) and self._spans_shards(st, r, self._sharded or ())) for r in reds)
+        if not any(crossing.values()):
+            xchg = None
+        elif len(reds) * K > xchg["cap"]:
+            return None
         if st.out.take is not None or any(o.take is not None for o in st.operands):
             return None
         n_passes = len(levels) + (0 if red_out else 1)
@@ -886,6 +893,13 @@ class Planner(object):
         f.u64("status", self.status_ptr)
         f.u64("wait_ns", int(self.wait_limit_ns))
         f.u32("starve", int(self.debug_starve_bytes))
+        if xchg:
+            f.u64("x_table", xchg["table"])
+            f.u32("x_epoch", 0)
+            f.u32("x_rank", xchg["rank"])
+            f.u32("x_world", xchg["world"])
+            f.u32("x_cap", xchg["cap"])
+            f.i32("x_col0", xchg["col0"])
         offs, off = {}, 0
         for pre, o in sorted(staged.items()):
             offs[pre] = off
@@ -898,8 +912,9 @@ class Planner(object):
             ops = " : ".join("r == %d ? %s" % (j, _red_code(r)) for j, r in enumerate(rs[:-1]))
             ops = (ops + " : " if ops else "") + _red_code(rs[-1])
             tail = ["out[%d][i] = %s;" % (j, e) for j, e in enumerate(outs)]
+            xc = " || ".join("r == %d" % j for j, r in enumerate(rs) if crossing[r.nid])
             parts.append(self._struct("S%d" % i, em, tail, len(rs), ops, None, None,
-                                      acc_tail=self._accum_tail(em, rs, outs), fix_lines=fixups[i]))
+                                      acc_tail=self._accum_tail(em, rs, outs), fix_lines=fixups[i], xc=xc))
         if red_out:
             parts.append(self._struct("SF", fin, [], 0, "OP_SUM", fin.h_lines + [store], None, epilogue_only=True))
         else:
@@ -946,8 +961,8 @@ class Planner(object):
             body.append("    rr_pass<S%d, ST, P, %d, %d, %d, %s, %s>(q, p, k, knext, cx, %s, %s, a, ai, sv, si);"
                         % (i, V, threads, unroll, "true" if i == 0 else "false", "true" if last else "false",
                            dyn_cur, bars_cur))
-            body.append("    rr_combine<S%d, P, %d, %d, %d>(q, k, cx, a, ai, sv, si, &slots[%d][0][0][0][0], &s_res[%d]);"
-                        % (i, V, C, threads, i, slot_of[rs[0].nid]))
+            body.append("    rr_combine<S%d, P, %d, %d, %d, %d>(q, k, cx, a, ai, sv, si, &slots[%d][0][0][0][0], &s_res[%d]);"
+                        % (i, V, C, threads, slot_of[rs[0].nid], i, slot_of[rs[0].nid]))
         if red_out:
             body.append("    if (threadIdx.x == 0 && cx.rank == 0) SF<%d>::epilogue(q, k, a, ai);" % V)
         else:
@@ -967,6 +982,7 @@ class Planner(object):
         pz.name, pz.source, pz.fields = name, text, f
         pz.block = (threads, 1, 1)
         pz.smem, pz.cluster = dyn_bytes, C
+        pz.uses_xchg = bool(xchg)
         clusters = max(1, min(K, (self.sm_count * blocks_per_sm) // C))
         pz.grid = (clusters * C, 1, 1)
         pz.desc = "rowres V=%d K=%d N=%d cluster=%d threads=%d smem=%d passes=%d grid=%s" % (
@@ -1040,12 +1056,14 @@ class Planner(object):
 
     @staticmethod
     def _struct(name, em, eval_tail, nred, ops, ep_lines, st_lines, epilogue_only=False, acc_tail=None,
-                fix_lines=None):
+                fix_lines=None, xc=None):
         ind = "\n        "
         nout = max(nred, 1)
         parts = ["template <int V> struct %s {" % name]
-        parts.append("    enum { NRED = %d };" % nred)
+        parts.append("    enum { NRED = %d, XCHG = %d };" % (nred, 1 if xc else 0))
         parts.append("    static DEV constexpr int op(int r) { return %s; }" % ops)
+        if xc:
+            parts.append("    static DEV constexpr bool xc(int r) { return %s; }" % xc)
         if not epilogue_only:
             parts.append("    struct H { %s int unused_; };" % " ".join(em.h_decl))
             parts.append("    struct L { %s int unused_; };" % " ".join(em.l_decl))
@@ -1667,8 +1685,14 @@ class Planner(object):
                     unroll //= 2
                 assert cl % (BLOCK * unroll * V) == 0 and N % V == 0
                 mode = 3
-                f.u32("flat_bpr", cl // (BLOCK * unroll * V))
-            grid = (max(1, (total + BLOCK * unroll - 1) // (BLOCK * unroll)), 1, 1)
+                bpr = cl // (BLOCK * unroll * V)
+                shard_rows = N // cl
+                f.u32("flat_bpr", bpr)
+                f.u32("flat_rows", shard_rows)
+            if mode == 3:                       # one grid row per tensor row: no index division
+                grid = (bpr, min(shard_rows, 65535), (shard_rows + 65534) // 65535)
+            else:
+                grid = (max(1, (total + BLOCK * unroll - 1) // (BLOCK * unroll)), 1, 1)
         widest = max([DT_SIZE[odt]] + [DT_SIZE[o.dt] for o, _ in em.lane_ops])
         idx32 = mode != 0 and (N + BLOCK * unroll * V) * widest < (1 << 32)
         call = "ew_kernel<S, P, %d, %d, %d, %d, %s>(p);" % (V, BLOCK, unroll, mode, "true" if idx32 else "false")
