@@ -703,8 +703,11 @@ DEV void xchg_rows(const P& p, i64 k, float* a, int* ai, u32 base = 0) {
                 if (w == 1 && !red_is_arg(S::op(r))) continue;
                 u64 v = ld_sys_u64(e + w);
                 while ((v >> 32) != (tag >> 32) && !gave_up) {
-                    if (t0 == 0) t0 = xchg_ns();
-                    else if (xchg_ns() - t0 > p.wait_ns) {
+                    if (t0 == 0) {
+                        t0 = xchg_ns();
+                        // a wait of this launch has already run out: do not wait the limit again
+                        if (p.status && (*reinterpret_cast<volatile int*>(p.status) & 4)) gave_up = true;
+                    } else if (xchg_ns() - t0 > p.wait_ns) {
                         if (p.status) atomicOr(reinterpret_cast<int*>(p.status), 4);
                         gave_up = true;
                     }
