@@ -365,15 +365,15 @@ def other_workloads(name, job, scaling):
         return [("batchnorm stats+normalise", st_bn, 4 * n + 2048)], n
     if name == "transpose":
         # the data-feed step in front of every fprop (ArrayIterator): (examples, features) rows
-        # to (features, batch) columns; one large matrix each of fp32, fp16 and uint8
+        # to (features, batch) columns; one 256 MiB matrix each of fp32, fp16 and uint8 (input and
+        # output together are four times the L2)
         stmts = []
-        r, c = 8192, 8192
-        for dt in (np.float32, np.float16, np.uint8):
+        for dt, (r, c) in ((np.float32, (8192, 8192)), (np.float16, (16384, 8192)), (np.uint8, (16384, 16384))):
             a = be.zeros((r, c), dtype=dt)
             out = be.empty((c, r), dtype=dt)
-            stmts.append(("copy_transpose %s" % np.dtype(dt).name,
+            stmts.append(("copy_transpose %s %dx%d" % (np.dtype(dt).name, r, c),
                           (lambda a=a, out=out: be.copy_transpose(a, out)), 2 * a.nbytes))
-        return stmts, r * c
+        return stmts, 8192 * 8192
     if name == "kahan":
         n = 100000000
         stmts = []

@@ -654,8 +654,10 @@ DEV void write_partial(const P& p, i64 k, int j, i64 pj, i64 pk, const float* a,
 // results first).  The wait is bounded in time: a rank that never arrives sets bit 2 of the
 // status word and the kernel carries on to its end.
 // Area layout, both halves alike: entry[W][cap] of two 64-bit words (value, index or count).
-//   P fields: x_table (device array of W area addresses), x_epoch (never 0), x_rank, x_world,
-//   x_cap, x_col0 (first global column of the shard, added to arg-reduction indices).
+//   P fields: x_table (device array of W area addresses), x_epoch and x_base (the launch number
+//   is x_epoch + the 32-bit word at x_base, never 0 and the same on every rank: the word lets a
+//   recorded launch sequence be replayed with fresh numbers without touching its parameters),
+//   x_rank, x_world, x_cap, x_col0 (first global column of the shard, added to arg-reduction indices).
 //   S::XCHG enables it; S::xc(r) says whether slot r spans the shards (a reduction of a
 //   replicated operand does not: every rank already holds the full result).
 DEV void st_sys_u64(u64* p, u64 v) { asm volatile("st.relaxed.sys.global.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory"); }
@@ -668,9 +670,10 @@ DEV u64 xchg_ns() { u64 t; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
 template <class S, class P, int NR, bool PUT = true>
 DEV void xchg_rows(const P& p, i64 k, float* a, int* ai, u32 base = 0) {
     const u32 W = p.x_world, me = p.x_rank;
-    const u64 tag = (u64)p.x_epoch << 32;
+    const u32 epoch = p.x_epoch + *reinterpret_cast<const u32*>(p.x_base);
+    const u64 tag = (u64)epoch << 32;
     const u64* table = reinterpret_cast<const u64*>(p.x_table);
-    const u64 half = (u64)(p.x_epoch & 1u) * ((u64)W * p.x_cap * 16u);
+    const u64 half = (u64)(epoch & 1u) * ((u64)W * p.x_cap * 16u);
 #pragma unroll
     for (int r = 0; r < NR; ++r)
         if (S::xc(r) && (S::op(r) == OP_ARGMAX || S::op(r) == OP_ARGMIN)) ai[r] += p.x_col0;

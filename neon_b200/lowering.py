@@ -599,7 +599,7 @@ class Planner(object):
         of several devices between passes); ``lin=(ncols, col0, local cols)`` makes
         element indices for random numbers those of a wider tensor this one is a
         column slice of; ``sharded`` names the operands (by index) that are column shards, and
-        ``xchg`` (a dict: table, rank, world, cap, col0) makes every reduction that spans
+        ``xchg`` (a dict: table, base, rank, world, cap, col0) makes every reduction that spans
         them finish across the GPUs inside its kernel.
         Raises XchgUnsupported when the statement cannot use the exchange area."""
         self._lin = lin
@@ -896,6 +896,7 @@ class Planner(object):
         if xchg:
             f.u64("x_table", xchg["table"])
             f.u32("x_epoch", 0)
+            f.u64("x_base", xchg["base"])
             f.u32("x_rank", xchg["rank"])
             f.u32("x_world", xchg["world"])
             f.u32("x_cap", xchg["cap"])
@@ -1583,6 +1584,7 @@ class Planner(object):
             f.u64("status", self.status_ptr)
             f.u64("wait_ns", int(self.wait_limit_ns))
             f.u32("x_epoch", 0)
+            f.u64("x_base", xchg["base"])
             f.u32("x_rank", xchg["rank"])
             f.u32("x_world", xchg["world"])
             f.u32("x_cap", xchg["cap"])

@@ -32,7 +32,7 @@ launched them (``RANK`` / ``WORLD_SIZE`` / ``MASTER_ADDR`` / ``MASTER_PORT``).
 import numpy as np
 
 from . import runtime as rt
-from .backend import B200Backend
+from .backend import B200Backend, CapturedGraph
 from .lowering import BoundPlan, Statement, XchgUnsupported, program_key
 from .optree import OpTreeNode, Tensor
 
@@ -136,7 +136,11 @@ class ShardedBackend(B200Backend):
             cap = 16384                      # (rows x reductions) one launch can exchange
             nbytes = 2 * world_size * cap * 16
             self._xchg_local, table = rt.xchg_create(comm, world_size, rank, nbytes)
-            self._xchg = {"table": table, "rank": rank, "world": world_size, "cap": cap}
+            # launch number of an exchange = its kernel parameter + this device word; the word
+            # only changes when a recorded sequence is replayed (see capture)
+            self._xbase_word, self._xbase = rt.malloc(256), 0
+            rt.memset(self._xbase_word, 0, 4, 1, self.stream)
+            self._xchg = {"table": table, "base": self._xbase_word, "rank": rank, "world": world_size, "cap": cap}
 
     # ---- factories: parallel=True -> column shard
     def _make(self, factory, shape, dtype, name, parallel, fill=None):
@@ -246,7 +250,7 @@ class ShardedBackend(B200Backend):
         for pz in plan.passes:
             if pz.uses_xchg:
                 self._xepoch += 1
-                pz.fields.values["x_epoch"] = self._xepoch & 0xFFFFFFFF
+                pz.fields.values["x_epoch"] = (self._xepoch - self._xbase) & 0xFFFFFFFF
                 self.exchanges += 1
             self._launch(pz)
             if crosses:
@@ -255,6 +259,26 @@ class ShardedBackend(B200Backend):
                         self._allreduce(addr_v, count, _NCCL_OP[op])
                     else:
                         self._merge_arg(op, addr_v, addr_i, count, sharded[0])
+
+    # ---- recorded sequences
+    def capture(self, fn):
+        """As ``B200Backend.capture``, for statements over sharded tensors: every rank records
+        the same sequence and replays it at the same point of its program.  Reductions that
+        finish across the GPUs number their launches; a replay gives the recorded launches
+        fresh numbers by moving the device word their parameters are relative to, so recorded
+        and eager statements can be mixed freely."""
+        fn()
+        self.synchronize()
+        first, before = self._xepoch, self.launches
+        rt.graph_begin(self.stream)
+        try:
+            fn()
+        finally:
+            handle = rt.graph_end(self.stream)
+        count = self._xepoch - first
+        self._xepoch = first                      # nothing was launched while recording
+        self.exchanges -= count
+        return ShardedGraph(self, handle, self.launches - before, first, count, self._xbase)
 
     def _merge_arg(self, op, addr_v, addr_i, count, like):
         """argmax / argmin across the shards: every rank contributes (extreme value,
@@ -286,6 +310,25 @@ class ShardedBackend(B200Backend):
         """In-place all-reduce of a replicated fp32 tensor (e.g. shard-local totals)."""
         assert tensor.dtype == np.float32 and tensor.is_contiguous
         self._allreduce(tensor.ptr, tensor.size, _NCCL_OP[op])
+
+
+class ShardedGraph(CapturedGraph):
+    """A recorded statement sequence of a ShardedBackend (see ``ShardedBackend.capture``)."""
+
+    def __init__(self, backend, handle, launches, first, count, base):
+        super(ShardedGraph, self).__init__(backend, handle, launches)
+        # the recorded exchange launches carry parameters first + 1 - base .. first + count - base
+        self.first, self.count, self.base = first, count, base
+
+    def replay(self):
+        be = self.backend
+        if self.count:
+            # the launches must get the numbers be._xepoch + 1 ..: parameter + word = number
+            be._xbase = (be._xepoch - self.first + self.base) & 0xFFFFFFFF
+            rt.memset(be._xbase_word, be._xbase, 4, 1, be.stream)
+            be._xepoch += self.count
+            be.exchanges += self.count
+        super(ShardedGraph, self).replay()
 
 
 class HostGroup(object):

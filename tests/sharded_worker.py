@@ -84,6 +84,37 @@ def main():
     assert np.all(picked >= dev.max(1, keepdims=True) * (1 - 1e-3)), "sharded argmax of deviations"
     del x, y, e
 
+    # ---- a recorded sequence of sharded statements, replayed between eager ones
+    if exchange:
+        rows, cols = 96, 4096 * world
+        xh = rng.randn(rows, cols).astype(np.float32)
+        x = be.array(xh, parallel=True)
+        y = be.empty((rows, cols), parallel=True)
+        top, low = be.empty((rows, 1)), be.empty((rows, 1))
+
+        def sequence():
+            y[:] = (x - be.mean(x, axis=1)) / be.sqrt(be.var(x, axis=1) + 1e-5)
+            top[:] = be.max(y, axis=1)
+            x[:] = y * 2.0 + 1.0
+
+        graph = be.capture(sequence)               # runs it once eagerly, then records it
+        want = xh.astype(np.float64)
+
+        def expected(v):
+            yy = (v - v.mean(1, keepdims=True)) / np.sqrt(v.var(1, keepdims=True) + 1e-5)
+            return yy, yy.max(1, keepdims=True), yy * 2.0 + 1.0
+        _, _, want = expected(want)
+        for turn in range(5):
+            before_x = be.exchanges
+            graph.replay()
+            assert be.exchanges - before_x == 2
+            yy, tt, want = expected(want)
+            low[:] = be.min(y, axis=1)             # an eager exchange between the replays
+            check_output("replayed y, turn %d" % turn, y.get(), yy, np.float32)
+            check_output("replayed max, turn %d" % turn, top.get(), tt, np.float32)
+            check_output("eager min after replay %d" % turn, low.get(), yy.min(1, keepdims=True), np.float32)
+        del x, y, graph
+
     # ---- fp16 chain with stochastic rounding + whole-tensor reductions (config 5 shape class)
     rows, cols = 256, 1024 * world
     xh = rng.uniform(-4, 4, (rows, cols)).astype(np.float16)

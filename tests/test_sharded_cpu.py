@@ -44,7 +44,7 @@ def _worker(rank, world, port, out):
             self.compile = False
             self.rank, self.world_size, self.comm = rank, world, comm
             self.collectives = self.exchanges = 0
-            self._xchg, self._xepoch = None, 0          # no exchange area: collectives between the passes
+            self._xchg, self._xepoch, self._xbase = None, 0, 0   # no exchange area: collectives between the passes
             self.calls = []
             self.plans = []
 
@@ -130,7 +130,7 @@ def _worker(rank, world, port, out):
     # ---- with an exchange area the reductions finish across the GPUs inside their kernels:
     #      statements are planned as on one GPU (moments in one pass, fused final epilogue),
     #      nothing is issued between the passes, every exchange pass gets its own launch number
-    be._xchg = {"table": 0x7D0000000000, "rank": rank, "world": world, "cap": 16384}
+    be._xchg = {"table": 0x7D0000000000, "base": 0x7D0000100000, "rank": rank, "world": world, "cap": 16384}
     be._plans.clear()
     be.plans, be.calls = [], []
     y[:] = (x - be.mean(x, axis=1)) / be.sqrt(be.var(x, axis=1) + 1e-5) * gamma + beta

@@ -111,6 +111,42 @@ def test_copy_transpose_large_matrix(b200):
     assert np.array_equal(out.get().view(np.uint16), h.T.view(np.uint16))
 
 
+@pytest.mark.parametrize("dtype", [np.float16, np.uint8, np.int16, np.int8])
+def test_copy_transpose_of_aligned_one_and_two_byte_matrices(b200, dtype):
+    """Shapes whose pitches are multiples of 16 bytes: 1- and 2-byte elements go through the
+    bulk-tensor tile kernel (edges in both directions, batches, views that keep the alignment),
+    neighbours that break one of its conditions through the plain tile kernel."""
+    be = b200
+    rng = np.random.RandomState(6)
+    es = np.dtype(dtype).itemsize
+    n = 16 // es
+    for shape in [(256, 128), (1008, 528), (2048 + n, 1024 + 16), (16 * n, 4096), (4096, 16 * n), (1008 + 1, 528), (1008, 528 + 1)]:
+        h = _fill(rng, shape, dtype)
+        a = be.array(h, dtype=dtype)
+        out = be.empty(shape[::-1], dtype=dtype)
+        be.copy_transpose(a, out)
+        assert np.array_equal(out.get(), h.T), (shape, dtype)
+    for shape, axes in [((4, 512, 272), (0, 2, 1)), ((3, 2, 256, 192), (0, 1, 3, 2)), ((3, 2, 256, 192), (1, 0, 3, 2)),
+                        ((8, 256, 128), (2, 0, 1)), ((8, 256, 128), (1, 2, 0)), ((2, 3, 4, 128, 256), (2, 0, 1, 4, 3))]:
+        h = _fill(rng, shape, dtype)
+        a = be.array(h, dtype=dtype)
+        out = be.empty(tuple(shape[x] for x in axes), dtype=dtype)
+        be.copy_transpose(a, out, axes=axes)
+        assert np.array_equal(out.get(), np.transpose(h, axes)), (shape, axes, dtype)
+    # views: row and column offsets that keep 16-byte alignment, inside larger tensors
+    h = _fill(rng, (700, 1200), dtype)
+    a = be.array(h, dtype=dtype)
+    base = be.zeros((1100, 800), dtype=dtype)
+    want = np.zeros((1100, 800), dtype)
+    be.copy_transpose(a[32:32 + 640, 64:64 + 1008], base[16:16 + 1008, 48:48 + 640])
+    want[16:16 + 1008, 48:48 + 640] = h[32:32 + 640, 64:64 + 1008].T
+    assert np.array_equal(base.get(), want), dtype
+    # ... and one that does not (odd column offset)
+    be.copy_transpose(a[32:32 + 640, 65:65 + 1008], base[16:16 + 1008, 48:48 + 640])
+    want[16:16 + 1008, 48:48 + 640] = h[32:32 + 640, 65:65 + 1008].T
+    assert np.array_equal(base.get(), want), dtype
+
+
 # ---------------------------------------------------------------- Kahan accumulation
 @pytest.mark.parametrize("dtype", ["float32", "float16", "bfloat16"])
 def test_compensated_sum_nearest_matches_the_restated_kernel(b200, dtype):
