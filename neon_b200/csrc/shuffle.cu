@@ -21,22 +21,14 @@
 //         contiguous in both tensors and everything is 16-byte aligned the
 //         elements are widened to 16 bytes first.
 //
-//   tma   the tile case for 1- and 2-byte elements when both tensors allow it (16-byte aligned
-//         bases and pitches, output extent a multiple of the vector): the tile is fetched by one
-//         tiled bulk-tensor copy into a swizzled shared-memory image and written back by one
-//         bulk-tensor store, so no lane computes a global address; threads only move 16-byte
-//         vectors between the two shared images and transpose micro-blocks in registers.
-//
-// All are pure data movement, bound by HBM: 2 x elem_bytes per element.
+// Both are pure data movement, bound by HBM: 2 x elem_bytes per element.
 
 #include "b200ew.h"
 
-#include <cuda.h>            // CUtensorMap and the encoder's signature; the function itself is looked up at run time
 #include <cuda_runtime.h>
 
 #include <cstdint>
 #include <cstdio>
-#include <mutex>
 
 extern "C" void* b200_detail_stream(uint64_t stream);
 extern "C" int32_t b200_detail_fail(int32_t code, const char* message);
@@ -235,237 +227,6 @@ __global__ void __launch_bounds__(256) shuffle_copy_kernel(const __grid_constant
     }
 }
 
-// ---- bulk-tensor tile kernel (1- and 2-byte elements) --------------------------------------
-// N = 16 / ES elements make a 16-byte vector.  A block moves the tile of TI = 128 / ES input
-// columns (i: one 128-byte line) by 256 output columns (o).  The input is described to the copy
-// engine as (i, o / N, o % N, rest...), so the 128-byte lines of the shared image are ordered
-// [o % N][o / N]: with the 128-byte swizzle (16-byte unit u of line n sits at unit u ^ (n & 7))
-// the eight lanes of a quarter warp, which hold consecutive o / N, read one unit each of eight
-// lines N apart without a bank conflict.  Thread (l, r) reads the N x N micro-block (lines o =
-// N r + v, unit l), transposes it in registers and writes N vectors into the dense output image
-// [i][o], where the same eight lanes fill 128 contiguous bytes.  One bulk-tensor store writes the
-// image; edges need no code (loads beyond the extents read zeros, stores are clipped).
-struct TmP {
-    u32 tiles_i, tiles_o, n2, tiles;   // tiles along i and o, extent of the first batch dimension, tiles in all
-    u64 status;       // mapped host word: set when the wait for a tile's copy runs out
-    u64 wait_ns;
-};
-
-__device__ __forceinline__ u32 smem_addr(const void* p) { return (u32)__cvta_generic_to_shared(p); }
-__device__ __forceinline__ u64 now_ns() { u64 t; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t)); return t; }
-
-// start the copy of tile t into the image at `image`; completion is counted on `bar`
-template <int ES>
-__device__ __forceinline__ void tma_fetch(const CUtensorMap* map, const TmP& p, u32 t, u32 image, u32 bar) {
-    constexpr int N = 16 / ES, R = 256 / N, TI = 128 / ES;
-    const u32 ti = t % p.tiles_i; t /= p.tiles_i;
-    const u32 to = t % p.tiles_o; t /= p.tiles_o;
-    const u32 c2 = t % p.n2, c3 = t / p.n2;
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" :: "r"(bar), "r"(32768u) : "memory");
-    asm volatile("cp.async.bulk.tensor.5d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4, %5, %6}], [%7];"
-                 :: "r"(image), "l"(map), "r"(ti * TI), "r"(to * R), "r"(0u), "r"(c2), "r"(c3), "r"(bar) : "memory");
-}
-
-// Persistent: block b moves tiles b, b + grid, ...; two input images (the copy of the tile after
-// next starts as soon as every thread has its micro-block of the current one in registers) and
-// one output image (its store is waited for just before the next tile's vectors are written).
-template <int ES>
-__global__ void __launch_bounds__(ES == 2 ? 256 : 128)
-shuffle_tma_kernel(const __grid_constant__ CUtensorMap in_map, const __grid_constant__ CUtensorMap out_map,
-                   const __grid_constant__ TmP p) {
-    constexpr int N = 16 / ES;            // micro-block side
-    constexpr int R = 256 / N;            // micro-block rows of a tile
-    constexpr int TI = 128 / ES;          // tile extent along i
-    constexpr u32 kTile = 32768;          // bytes of an image
-    extern __shared__ unsigned char dyn[];
-    __shared__ __align__(8) u64 bars[2];
-
-    const int r = threadIdx.x % R, l = threadIdx.x / R;
-    const u32 in_s = (smem_addr(dyn) + 1023u) & ~1023u;       // the swizzle pattern repeats every 1024 bytes
-    const u32 out_s = in_s + 2 * kTile;
-    const u32 bar_s = smem_addr(bars);
-    if (threadIdx.x == 0) {
-        asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" :: "r"(bar_s));
-        asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" :: "r"(bar_s + 8));
-        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-    }
-    __syncthreads();
-    if (threadIdx.x == 0) {
-        if (blockIdx.x < p.tiles) tma_fetch<ES>(&in_map, p, blockIdx.x, in_s, bar_s);
-        if (blockIdx.x + gridDim.x < p.tiles) tma_fetch<ES>(&in_map, p, blockIdx.x + gridDim.x, in_s + kTile, bar_s + 8);
-    }
-    u32 it = 0;
-    for (u32 t = blockIdx.x; t < p.tiles; t += gridDim.x, ++it) {
-        const u32 stage = it & 1u, parity = (it >> 1) & 1u;
-        {   // wait for the tile, at most p.wait_ns
-            u32 done = 0;
-            u64 t0 = 0;
-            while (true) {
-                asm volatile("{ .reg .pred q; mbarrier.try_wait.parity.shared::cta.b64 q, [%1], %2, %3; selp.u32 %0, 1, 0, q; }"
-                             : "=r"(done) : "r"(bar_s + 8 * stage), "r"(parity), "r"(20000u) : "memory");
-                if (done) break;
-                const u64 now = now_ns();
-                if (t0 == 0) t0 = now;
-                else if (now - t0 > p.wait_ns) {
-                    if (p.status) *reinterpret_cast<volatile u32*>(p.status) = 1u;
-                    return;
-                }
-            }
-        }
-        u32 in[N][4];
-        const u32 image = in_s + stage * kTile;
-#pragma unroll
-        for (int v = 0; v < N; ++v) {
-            const u32 a = image + (u32)(v * R + r) * 128u + (u32)((l ^ (r & 7)) * 16);
-            asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];"
-                         : "=r"(in[v][0]), "=r"(in[v][1]), "=r"(in[v][2]), "=r"(in[v][3]) : "r"(a));
-        }
-        // the previous tile's store has read the output image; everyone has read this input image
-        if (threadIdx.x == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
-        __syncthreads();
-        if (threadIdx.x == 0 && t + 2 * gridDim.x < p.tiles)
-            tma_fetch<ES>(&in_map, p, t + 2 * gridDim.x, image, bar_s + 8 * stage);
-#pragma unroll
-        for (int w = 0; w < N; ++w) {
-            u32 out[4];
-            if constexpr (ES == 2) {
-                // element w of rows 2q and 2q+1 -> word q
-#pragma unroll
-                for (int q = 0; q < 4; ++q)
-                    out[q] = __byte_perm(in[2 * q][w >> 1], in[2 * q + 1][w >> 1], (w & 1) ? 0x7632 : 0x5410);
-            } else {
-                // byte w of rows 4q .. 4q+3 -> word q
-                const u32 sel = ((4u + (w & 3)) << 4) | (u32)(w & 3);
-#pragma unroll
-                for (int q = 0; q < 4; ++q) {
-                    const u32 lo = __byte_perm(in[4 * q][w >> 2], in[4 * q + 1][w >> 2], sel);
-                    const u32 hi = __byte_perm(in[4 * q + 2][w >> 2], in[4 * q + 3][w >> 2], sel);
-                    out[q] = __byte_perm(lo, hi, 0x5410);
-                }
-            }
-            const u32 a = out_s + (u32)(N * l + w) * (256u * ES) + (u32)r * 16u;
-            asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" :: "r"(a), "r"(out[0]), "r"(out[1]), "r"(out[2]), "r"(out[3]) : "memory");
-        }
-        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-        __syncthreads();
-        if (threadIdx.x == 0) {
-            u32 q = t;
-            const u32 ti = q % p.tiles_i; q /= p.tiles_i;
-            const u32 to = q % p.tiles_o; q /= p.tiles_o;
-            const u32 c2 = q % p.n2, c3 = q / p.n2;
-            asm volatile("cp.async.bulk.tensor.4d.global.shared::cta.bulk_group [%0, {%1, %2, %3, %4}], [%5];"
-                         :: "l"(&out_map), "r"(to * 256u), "r"(ti * TI), "r"(c2), "r"(c3), "r"(out_s) : "memory");
-            asm volatile("cp.async.bulk.commit_group;" ::: "memory");
-        }
-    }
-    if (threadIdx.x == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
-}
-
-typedef CUresult (*tensor_map_encode_fn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                                         const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
-                                         CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-enum { kTmaSmem = 3 * 32768 + 1024 };     // two input images, one output image, alignment slack
-
-struct TmaHost {
-    int sm_count = 0;
-    std::mutex mu;
-    bool tried = false;
-    tensor_map_encode_fn encode = nullptr;
-    volatile u32* status_host = nullptr;
-    u64 status_dev = 0;
-};
-TmaHost g_tma;
-
-// the encoder and the mapped status word, once per process; false when the driver offers neither
-bool tma_ready() {
-    std::lock_guard<std::mutex> lock(g_tma.mu);
-    if (g_tma.tried) return g_tma.encode != nullptr;
-    g_tma.tried = true;
-    void* fn = nullptr;
-    cudaDriverEntryPointQueryResult found;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &found) != cudaSuccess ||
-        found != cudaDriverEntryPointSuccess || !fn) { cudaGetLastError(); return false; }
-    void* host = nullptr; void* dev = nullptr;
-    if (cudaHostAlloc(&host, 64, cudaHostAllocMapped) != cudaSuccess ||
-        cudaHostGetDevicePointer(&dev, host, 0) != cudaSuccess) { cudaGetLastError(); return false; }
-    int dev_id = 0;
-    if (cudaGetDevice(&dev_id) != cudaSuccess ||
-        cudaDeviceGetAttribute(&g_tma.sm_count, cudaDevAttrMultiProcessorCount, dev_id) != cudaSuccess || g_tma.sm_count < 1) {
-        cudaGetLastError();
-        return false;
-    }
-    *static_cast<volatile u32*>(host) = 0;
-    g_tma.status_host = static_cast<volatile u32*>(host);
-    g_tma.status_dev = (u64)dev;
-    for (int es = 1; es <= 2; ++es) {
-        const void* k = es == 1 ? (const void*)shuffle_tma_kernel<1> : (const void*)shuffle_tma_kernel<2>;
-        if (cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, kTmaSmem) != cudaSuccess) {
-            cudaGetLastError();
-            return false;
-        }
-    }
-    g_tma.encode = reinterpret_cast<tensor_map_encode_fn>(fn);
-    return true;
-}
-
-// Can the tile case in p (dims[0] = i, dims[1] = o, then the rest) go through the copy engine?
-bool tma_eligible(const ShP& p, int k, int es, u64 dst, u64 src) {
-    if (es > 2 || k > 4) return false;
-    const i64 N = 16 / es, TI = 128 / es;
-    if (dst % 16 || src % 16) return false;
-    if (p.ss[0] != 1 || p.ds[1] != 1 || p.n[1] % N) return false;
-    for (int d = 0; d < k; ++d) {
-        if (d != 0 && (p.ss[d] * es) % 16) return false;
-        if (d != 1 && (p.ds[d] * es) % 16) return false;
-        if (p.n[d] >= (1ll << 31) || p.ss[d] * es >= (1ll << 40) || p.ds[d] * es >= (1ll << 40)) return false;
-    }
-    // whole tiles are moved: not worth it when the padding exceeds a quarter
-    const double area = (double)((p.n[0] + TI - 1) / TI * TI) * (double)((p.n[1] + 255) / 256 * 256);
-    return area <= 1.25 * (double)p.n[0] * (double)p.n[1];
-}
-
-template <int ES> cudaError_t launch_tma(const ShP& p, int k, cudaStream_t s, bool* encoded) {
-    constexpr i64 N = 16 / ES, TI = 128 / ES, R = 256 / N;
-    const CUtensorMapDataType dt = ES == 1 ? CU_TENSOR_MAP_DATA_TYPE_UINT8 : CU_TENSOR_MAP_DATA_TYPE_UINT16;
-    const i64 n2 = k > 2 ? p.n[2] : 1, n3 = k > 3 ? p.n[3] : 1;
-    const i64 ss2 = k > 2 ? p.ss[2] * ES : 16, ss3 = k > 3 ? p.ss[3] * ES : 16;
-    const i64 ds2 = k > 2 ? p.ds[2] * ES : 16, ds3 = k > 3 ? p.ds[3] * ES : 16;
-    CUtensorMap in_map, out_map;
-    {
-        const cuuint64_t dims[5] = {(cuuint64_t)p.n[0], (cuuint64_t)(p.n[1] / N), (cuuint64_t)N, (cuuint64_t)n2, (cuuint64_t)n3};
-        const cuuint64_t strides[4] = {(cuuint64_t)(p.ss[1] * N * ES), (cuuint64_t)(p.ss[1] * ES), (cuuint64_t)ss2, (cuuint64_t)ss3};
-        const cuuint32_t box[5] = {(cuuint32_t)TI, (cuuint32_t)R, (cuuint32_t)N, 1, 1};
-        const cuuint32_t one[5] = {1, 1, 1, 1, 1};
-        if (g_tma.encode(&in_map, dt, 5, reinterpret_cast<void*>(p.src), dims, strides, box, one, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                         CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
-                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS) { *encoded = false; return cudaSuccess; }
-    }
-    {
-        const cuuint64_t dims[4] = {(cuuint64_t)p.n[1], (cuuint64_t)p.n[0], (cuuint64_t)n2, (cuuint64_t)n3};
-        const cuuint64_t strides[3] = {(cuuint64_t)(p.ds[0] * ES), (cuuint64_t)ds2, (cuuint64_t)ds3};
-        const cuuint32_t box[4] = {256, (cuuint32_t)TI, 1, 1};
-        const cuuint32_t one[4] = {1, 1, 1, 1};
-        if (g_tma.encode(&out_map, dt, 4, reinterpret_cast<void*>(p.dst), dims, strides, box, one, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                         CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS) { *encoded = false; return cudaSuccess; }
-    }
-    *encoded = true;
-    TmP t;
-    t.tiles_i = (u32)((p.n[0] + TI - 1) / TI);
-    t.tiles_o = (u32)((p.n[1] + 255) / 256);
-    t.n2 = (u32)n2;
-    t.status = g_tma.status_dev;
-    t.wait_ns = 2000000000ull;
-    const i64 tiles = (i64)t.tiles_i * t.tiles_o * n2 * n3;
-    if (tiles > 0x7fffffffll) { *encoded = false; return cudaSuccess; }
-    t.tiles = (u32)tiles;
-    const i64 resident = 2ll * g_tma.sm_count;                 // two blocks per SM (shared memory)
-    const unsigned grid = (unsigned)(tiles < resident ? tiles : resident);
-    shuffle_tma_kernel<ES><<<grid, ES == 2 ? 256 : 128, kTmaSmem, s>>>(in_map, out_map, t);
-    return cudaGetLastError();
-}
-
 template <int ES, int U> cudaError_t launch_tile(const ShP& p, unsigned grid, cudaStream_t s) {
     shuffle_tile_kernel<ES, U><<<grid, 256, 0, s>>>(p);
     return cudaGetLastError();
@@ -572,22 +333,6 @@ extern "C" b200_status b200_dimshuffle(uint64_t dst, uint64_t src, int32_t elem_
     cudaError_t e;
     i64 blocks;
     int U = 0;                                   // bytes a lane of the tile kernel moves at once
-    if (g_tma.status_host && *g_tma.status_host) {
-        *g_tma.status_host = 0;
-        return b200_detail_fail(B200_ERR_TIMEOUT, "b200_dimshuffle: an earlier call gave up waiting for a tile copy; its output is incomplete");
-    }
-    if (tiled && tma_eligible(p, k, es, dst, src) && tma_ready()) {
-        bool encoded = false;
-        e = es == 1 ? launch_tma<1>(p, k, s, &encoded) : launch_tma<2>(p, k, s, &encoded);
-        if (encoded) {
-            if (e != cudaSuccess) {
-                char msg[160];
-                snprintf(msg, sizeof msg, "b200_dimshuffle: %s", cudaGetErrorString(e));
-                return b200_detail_fail(B200_ERR_CUDA, msg);
-            }
-            return B200_OK;
-        }
-    }
     if (tiled) {
         // vector width: tiles are T = 16 U / es elements a side, so short dimensions waste part of
         // a wide tile, while narrow vectors move fewer bytes per instruction (measured: about 0.7 of

@@ -113,9 +113,9 @@ def test_copy_transpose_large_matrix(b200):
 
 @pytest.mark.parametrize("dtype", [np.float16, np.uint8, np.int16, np.int8])
 def test_copy_transpose_of_aligned_one_and_two_byte_matrices(b200, dtype):
-    """Shapes whose pitches are multiples of 16 bytes: 1- and 2-byte elements go through the
-    bulk-tensor tile kernel (edges in both directions, batches, views that keep the alignment),
-    neighbours that break one of its conditions through the plain tile kernel."""
+    """Shapes whose pitches are multiples of 16 bytes (whole 16-byte vectors on both sides of the
+    tile kernel: edges in both directions, batches, views that keep the alignment) next to
+    neighbours that break the alignment by one element."""
     be = b200
     rng = np.random.RandomState(6)
     es = np.dtype(dtype).itemsize
