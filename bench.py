@@ -414,6 +414,17 @@ def measure_other(name, job, steps, warmup, scaling, extras=True):
            "l2": "working set is L2-resident between steps" if n_local * 4 < 100e6 else "exceeds L2",
            "gpu_launches": launches, "launches_per_step": kinds,
            "breakdown": job.breakdown(step)}
+    # the same sequence recorded once as a CUDA graph and replayed (every rank records and
+    # replays its own; reductions across the GPUs number their launches relative to a device word)
+    if hasattr(be, "capture"):
+        graph = be.capture(lambda: step(0))
+        for _ in range(3):
+            graph.replay()
+        graph_total, _ = job.time_steps(lambda s: graph.replay(), steps)
+        graph_ms = graph_total / steps
+        rec["graph_replay"] = {"ms_per_step": graph_ms, "GBps": nbytes_step / graph_ms / 1e6,
+                               "note": "statement sequence recorded once with be.capture(), replayed with one call"}
+        del graph
     if not extras:
         return rec
     # per statement, from events around each one (a few more steps)
@@ -429,21 +440,6 @@ def measure_other(name, job, steps, warmup, scaling, extras=True):
         ms = float(np.median([be.get_time(*marks[s][i]) for s in range(steps)]))
         rec["statements"].append({"statement": label, "ms": ms, "algorithmic_bytes": nbytes,
                                   "GBps": nbytes / ms / 1e6})
-    # the same sequence recorded once as a CUDA graph and replayed (single GPU only)
-    if world == 1 and hasattr(be, "capture"):
-        ev0, ev1 = be.init_mark(), be.init_mark()
-        graph = be.capture(lambda: step(0))
-        for _ in range(3):
-            graph.replay()
-        be.synchronize()
-        be.record_mark(ev0)
-        for s in range(steps):
-            graph.replay()
-        be.record_mark(ev1)
-        be.synchronize()
-        graph_ms = be.get_time(ev0, ev1) / steps
-        rec["graph_replay"] = {"ms_per_step": graph_ms, "GBps": nbytes_step / graph_ms / 1e6,
-                               "note": "statement sequence recorded once with be.capture(), replayed with one call"}
     # working sets that stay in L2 between steps: the same statements again with L2 flushed
     # (a 256 MiB fill) before each one, timed per statement so that the fill is not counted
     if world == 1 and n_local * 4 < 100e6:
