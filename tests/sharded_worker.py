@@ -61,28 +61,32 @@ def main():
     s0[:] = be.sum(x, axis=0)
     check_output("sharded axis-0 sum", s0.get(), x64.sum(0, keepdims=True), np.float32)
 
-    # ---- more rows than the device holds blocks (the row-resident kernel loops), three passes
-    rows, cols = 700, 16384 * world
-    xh = (0.5 + rng.randn(rows, cols)).astype(np.float16)
-    x = be.array(xh, dtype=np.float16, parallel=True)
-    y = be.empty((rows, cols), dtype=np.float16, parallel=True)
-    x64 = xh.astype(np.float64)
-    before, before_x, launches = be.collectives, be.exchanges, be.launches
-    e = be.exp(x - be.max(x, axis=1))
-    y[:] = e / be.sum(e, axis=1)
-    if exchange:
-        assert (be.collectives - before, be.exchanges - before_x, be.launches - launches) == (0, 1, 1)
-    e64 = np.exp(x64 - x64.max(1, keepdims=True))
-    check_output("sharded softmax", y.get(), e64 / e64.sum(1, keepdims=True), np.float16)
-    y[:] = (x - be.mean(x, axis=1)) / be.sqrt(be.var(x, axis=1) + 1e-5)
-    check_output("sharded standardise", y.get(),
-                 (x64 - x64.mean(1, keepdims=True)) / np.sqrt(x64.var(1, keepdims=True) + 1e-5), np.float16)
-    far = be.empty((rows, 1), dtype=np.int32)
-    far[:] = be.argmax(be.absolute(x - be.mean(x, axis=1)), axis=1)
-    dev = np.abs(x64 - x64.mean(1, keepdims=True))
-    picked = np.take_along_axis(dev, far.get().astype(np.int64), axis=1)
-    assert np.all(picked >= dev.max(1, keepdims=True) * (1 - 1e-3)), "sharded argmax of deviations"
-    del x, y, e
+    # ---- three passes (softmax): one launch while every row has a resident block of its own,
+    #      the multi-launch form beyond that (700 rows of 32 KB: more rows than resident blocks)
+    for rows in (500, 700):
+        cols = 16384 * world
+        xh = (0.5 + rng.randn(rows, cols)).astype(np.float16)
+        x = be.array(xh, dtype=np.float16, parallel=True)
+        y = be.empty((rows, cols), dtype=np.float16, parallel=True)
+        x64 = xh.astype(np.float64)
+        before, before_x, launches = be.collectives, be.exchanges, be.launches
+        e = be.exp(x - be.max(x, axis=1))
+        y[:] = e / be.sum(e, axis=1)
+        if exchange:
+            assert be.collectives == before
+            if rows == 500:
+                assert (be.exchanges - before_x, be.launches - launches) == (1, 1)
+        e64 = np.exp(x64 - x64.max(1, keepdims=True))
+        check_output("sharded softmax", y.get(), e64 / e64.sum(1, keepdims=True), np.float16)
+        y[:] = (x - be.mean(x, axis=1)) / be.sqrt(be.var(x, axis=1) + 1e-5)
+        check_output("sharded standardise", y.get(),
+                     (x64 - x64.mean(1, keepdims=True)) / np.sqrt(x64.var(1, keepdims=True) + 1e-5), np.float16)
+        far = be.empty((rows, 1), dtype=np.int32)
+        far[:] = be.argmax(be.absolute(x - be.mean(x, axis=1)), axis=1)
+        dev = np.abs(x64 - x64.mean(1, keepdims=True))
+        picked = np.take_along_axis(dev, far.get().astype(np.int64), axis=1)
+        assert np.all(picked >= dev.max(1, keepdims=True) * (1 - 1e-3)), "sharded argmax of deviations"
+        del x, y, e
 
     # ---- a recorded sequence of sharded statements, replayed between eager ones
     if exchange:
