@@ -540,8 +540,6 @@ b200_status b200_kernel_max_clusters(uint64_t kernel, int32_t block_threads, int
     attr.id = cudaLaunchAttributeClusterDimension;
     attr.val.clusterDim.x = (unsigned)cluster_size; attr.val.clusterDim.y = 1; attr.val.clusterDim.z = 1;
     cfg.attrs = &attr; cfg.numAttrs = 1;
-    if (cluster_size > 8)      // beyond the portable size: the kernel has to opt in before it is queried or launched
-        CU(cudaFuncSetAttribute(reinterpret_cast<const void *>(kernel), cudaFuncAttributeNonPortableClusterSizeAllowed, 1));
     int n = 0;
     CU(cudaOccupancyMaxActiveClusters(&n, reinterpret_cast<const void *>(kernel), &cfg));
     *clusters = n;

@@ -586,7 +586,6 @@ class Planner(object):
         self.rowres_unroll = 2             # vectors per thread and chunk in the row-resident kernel
         self.rowres_threads = None         # cap on its block size (None: as many as the registers allow)
         self.rowres_exchange_resident_only = True   # see _rowres_pass
-        self.rowres_max_cluster = 8        # largest cluster it may use (16 needs the non-portable opt-in)
         self.status_ptr = 0                # device int the kernels set when a bounded wait gives up
         self.wait_limit_ns = 2000000000    # how long a block waits for its staged row slice
         self.debug_starve_bytes = 0        # tests only: announce this many bytes that never arrive
@@ -845,14 +844,14 @@ class Planner(object):
         nvec = N // V
         row_bytes = sum(DT_SIZE[o.dt] for o in staged.values())          # per element
         C = None
-        for c in (1, 2, 4, 8, 16)[:self.rowres_max_cluster.bit_length()]:
+        for c in (1, 2, 4, 8):
             per = (nvec + c - 1) // c * V
             need = sum(((per * DT_SIZE[o.dt] + 127) & ~127) for o in staged.values())
             if need <= self.rowres_slice_cap:
                 C = c
                 break
         if C is None:                         # does not fit in small slices: one big block per SM
-            for c in (1, 2, 4, 8, 16)[:self.rowres_max_cluster.bit_length()]:
+            for c in (1, 2, 4, 8):
                 per = (nvec + c - 1) // c * V
                 need = sum(((per * DT_SIZE[o.dt] + 127) & ~127) for o in staged.values())
                 if need <= self.smem_cap:
