@@ -85,7 +85,9 @@ b200_status b200_mem_info(uint64_t *free_bytes, uint64_t *total_bytes);
  * replaces drv.mem_alloc as GPUTensor's allocator, the shape-keyed temp pool
  * and the scratch buffer (neon/backends/nervanagpu.py:87,147,836-890,1051-1075) */
 b200_status b200_malloc(uint64_t bytes, uint64_t *dptr);
-b200_status b200_free(uint64_t dptr);
+b200_status b200_free(uint64_t dptr);                   /* reuse is ordered by the library's stream; while streams made
+                                                           with b200_stream_create exist, the block is reused only after
+                                                           the work queued on every stream at this moment has run */
 b200_status b200_mem_trim(void);                        /* give cached blocks back */
 b200_status b200_mem_stats(uint64_t *in_use, uint64_t *cached, uint64_t *peak_in_use,
                            uint64_t *device_allocs);

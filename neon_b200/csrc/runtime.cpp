@@ -21,6 +21,7 @@
 #include <fstream>
 #include <map>
 #include <mutex>
+#include <set>
 #include <string>
 #include <unordered_map>
 #include <vector>
@@ -55,6 +56,11 @@ struct State {
     std::multimap<uint64_t, void *> free_blocks;          // size -> ptr
     std::unordered_map<void *, uint64_t> live;            // ptr -> block size
     uint64_t in_use = 0, cached = 0, peak = 0, device_allocs = 0;
+    // streams made with b200_stream_create; while there are any, a freed block waits in `parked`
+    // until everything queued so far on the library's stream and on each of them has run
+    std::set<cudaStream_t> user_streams;
+    struct Parked { void *p; uint64_t sz; std::vector<cudaEvent_t> events; };
+    std::vector<Parked> parked;
     // kernels
     std::unordered_map<std::string, std::string> headers;
     std::unordered_map<uint64_t, cudaKernel_t> kernels;   // hash(source+name+opts) -> kernel
@@ -66,6 +72,30 @@ struct State {
 State g;
 std::mutex g_mu;
 std::recursive_mutex g_arena_mu;       // arena entry points may be called from any host thread (tensor finalisers)
+
+// Parked blocks whose events have all completed (or all of them, after waiting: `wait`) go to
+// the free list.  Called with the arena lock held.
+void reap_parked(bool wait) {
+    size_t keep = 0;
+    for (size_t i = 0; i < g.parked.size(); ++i) {
+        State::Parked &b = g.parked[i];
+        bool done = true;
+        for (cudaEvent_t e : b.events) {
+            if (wait) cudaEventSynchronize(e);
+            else if (cudaEventQuery(e) != cudaSuccess) { done = false; break; }
+        }
+        if (!done) {
+            cudaGetLastError();                    // cudaErrorNotReady is not an error
+            if (keep != i) g.parked[keep] = std::move(b);
+            ++keep;
+            continue;
+        }
+        for (cudaEvent_t e : b.events) cudaEventDestroy(e);
+        g.free_blocks.emplace(b.sz, b.p);
+        g.cached += b.sz;
+    }
+    g.parked.resize(keep);
+}
 
 uint64_t round_block(uint64_t bytes) {
     if (bytes == 0) bytes = 1;
@@ -196,6 +226,11 @@ b200_status b200_shutdown(void) {
     std::lock_guard<std::mutex> lk(g_mu);
     if (g.device < 0) return B200_OK;
     cudaDeviceSynchronize();
+    {
+        std::lock_guard<std::recursive_mutex> lock(g_arena_mu);
+        reap_parked(true);
+        g.user_streams.clear();
+    }
     for (auto &kv : g.free_blocks) cudaFree(kv.second);
     for (auto &kv : g.live) cudaFree(kv.first);
     g.free_blocks.clear(); g.live.clear();
@@ -238,6 +273,7 @@ b200_status b200_malloc(uint64_t bytes, uint64_t *dptr) {
     if (!dptr) return fail(B200_ERR_INVALID, "dptr is null");
     if (g.device < 0) return fail(B200_ERR_INVALID, "b200_init has not been called");
     std::lock_guard<std::recursive_mutex> lock(g_arena_mu);
+    if (!g.parked.empty()) reap_parked(false);
     uint64_t sz = round_block(bytes);
     auto it = g.free_blocks.lower_bound(sz);
     void *p = nullptr;
@@ -276,6 +312,29 @@ b200_status b200_free(uint64_t dptr) {
     uint64_t sz = it->second;
     g.live.erase(it);
     g.in_use -= sz;
+    if (!g.user_streams.empty()) {
+        // work on another stream may still use the block: hand it out again only after everything
+        // queued so far on every stream has run (with the library's stream alone, reuse is ordered
+        // by that stream and the block is free at once)
+        State::Parked b;
+        b.p = p; b.sz = sz;
+        std::vector<cudaStream_t> streams(g.user_streams.begin(), g.user_streams.end());
+        streams.push_back(g.stream);
+        bool ok = true;
+        for (cudaStream_t st : streams) {
+            cudaEvent_t e;
+            if (cudaEventCreateWithFlags(&e, cudaEventDisableTiming) != cudaSuccess) { ok = false; break; }
+            b.events.push_back(e);
+            if (cudaEventRecord(e, st) != cudaSuccess) { ok = false; break; }
+        }
+        if (ok) {
+            g.parked.push_back(std::move(b));
+            return B200_OK;
+        }
+        cudaGetLastError();                        // could not mark the streams: wait for the device instead
+        for (cudaEvent_t e : b.events) cudaEventDestroy(e);
+        cudaDeviceSynchronize();
+    }
     g.free_blocks.emplace(sz, p);
     g.cached += sz;
     return B200_OK;
@@ -283,6 +342,7 @@ b200_status b200_free(uint64_t dptr) {
 
 b200_status b200_mem_trim(void) {
     std::lock_guard<std::recursive_mutex> lock(g_arena_mu);
+    if (!g.parked.empty()) reap_parked(true);
     if (g.free_blocks.empty()) return B200_OK;
     cudaDeviceSynchronize();
     for (auto &kv : g.free_blocks) cudaFree(kv.second);
@@ -358,11 +418,23 @@ b200_status b200_stream_create(uint64_t *stream) {
     if (!stream) return fail(B200_ERR_INVALID, "stream is null");
     cudaStream_t s;
     CU(cudaStreamCreateWithFlags(&s, cudaStreamNonBlocking));
+    {
+        std::lock_guard<std::recursive_mutex> lock(g_arena_mu);
+        g.user_streams.insert(s);
+    }
     *stream = reinterpret_cast<uint64_t>(s);
     return B200_OK;
 }
 b200_status b200_stream_destroy(uint64_t stream) {
-    if (stream) CU(cudaStreamDestroy(reinterpret_cast<cudaStream_t>(stream)));
+    if (!stream) return B200_OK;
+    cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+    {
+        // blocks parked with an event on this stream: let them finish before the stream goes
+        std::lock_guard<std::recursive_mutex> lock(g_arena_mu);
+        if (!g.parked.empty()) reap_parked(true);
+        g.user_streams.erase(s);
+    }
+    CU(cudaStreamDestroy(s));
     return B200_OK;
 }
 b200_status b200_stream_sync(uint64_t stream) { CU(cudaStreamSynchronize(as_stream(stream))); return B200_OK; }
