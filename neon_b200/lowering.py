@@ -585,7 +585,7 @@ class Planner(object):
         self.rowres_slice_cap = 100 * 1024 # preferred largest slice of a row per block (two blocks per SM)
         self.rowres_unroll = 2             # vectors per thread and chunk in the row-resident kernel
         self.rowres_threads = None         # cap on its block size (None: as many as the registers allow)
-        self.rowres_exchange_resident_only = True   # see _rowres_pass
+        self.rowres_exchange_resident_only = True   # exchange inside the row-resident kernel only for few rows per cluster (see _rowres_pass)
         self.status_ptr = 0                # device int the kernels set when a bounded wait gives up
         self.wait_limit_ns = 2000000000    # how long a block waits for its staged row slice
         self.debug_starve_bytes = 0        # tests only: announce this many bytes that never arrive
@@ -873,11 +873,12 @@ class Planner(object):
         threads = 1024 // blocks_per_sm
         while threads > 256 and seg_vecs < 2 * threads:
             threads //= 2
-        if xchg and self.rowres_exchange_resident_only and K * C > self.sm_count * blocks_per_sm:
-            # rows that also wait for other GPUs: only when every row has its own resident cluster,
-            # so that the waits overlap.  A cluster that loops over rows pays one cross-GPU round
-            # trip per row in sequence (measured at 2 GPUs: 75 us against 67 us for the statistics
-            # kernel + element-wise kernel, whose second read of the shard comes from L2)
+        if xchg and self.rowres_exchange_resident_only and K * C > 2 * self.sm_count * blocks_per_sm:
+            # rows that also wait for other GPUs: only while a cluster has at most two rows to do.
+            # A cluster that loops over rows pays one cross-GPU round trip per row in sequence, and
+            # a shard of 1/N of the tensor is read from L2 by a second launch anyway.  Measured,
+            # batch norm of (256, 401408) fp16, eager: 2 GPUs (3.5 rows per cluster) 68 us against
+            # 62 us for statistics kernel + element-wise kernel; 4 GPUs (1.7 rows) 42 against 52 us
             return None
         unroll = self.rowres_unroll
         if self.rowres_threads:
