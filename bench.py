@@ -522,6 +522,9 @@ def main():
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--no-also", action="store_true", help="skip the cfg3 / cfg4 / weak-scaling extras of the default run")
     ap.add_argument("--scaling", default="strong", choices=("strong", "weak"))
+    ap.add_argument("--rowres", default="auto", choices=("auto", "always", "never"),
+                    help="multi-pass statements over long rows (cfg4): let the planner choose between the one-launch "
+                         "row-resident kernel and one launch per pass (auto), or force either form")
     ap.add_argument("--workload", default="cfg5", help="cfg5 (default, the reported metric), cfg1..cfg4, transpose (data-feed copy_transpose) or kahan (compensated_sum)")
     args = ap.parse_args()
 
@@ -556,6 +559,11 @@ def main():
         from neon_b200 import gen_backend
         be = gen_backend(backend="b200", rng_seed=0, device_id=local_rank)
         job = Job(be, rank, world, (lambda: None), (lambda v: v))
+
+    if args.rowres == "never":
+        be._planner.rowres = False
+    elif args.rowres == "always":
+        be._planner.rowres_exchange_resident_only = False
 
     if args.workload != "cfg5":
         return run_other(args, job)
