@@ -254,11 +254,25 @@ class ShardedBackend(B200Backend):
                 self.exchanges += 1
             self._launch(pz)
             if crosses:
+                # one collective per run of results that share the operation and sit next to each
+                # other in scratch (results of one pass are allocated back to back, each padded to
+                # 256 bytes: the padding is reduced along with them and never read)
+                run = None                       # [op, first address, end address]
                 for op, addr_v, addr_i, count in pz.results:
-                    if op in _NCCL_OP:
-                        self._allreduce(addr_v, count, _NCCL_OP[op])
-                    else:
+                    if op not in _NCCL_OP:
+                        if run is not None:
+                            self._allreduce(run[1], (run[2] - run[1]) // 4, _NCCL_OP[run[0]])
+                            run = None
                         self._merge_arg(op, addr_v, addr_i, count, sharded[0])
+                        continue
+                    if run is not None and run[0] == op and addr_v == ((run[2] + 255) & ~255):
+                        run[2] = addr_v + 4 * count
+                        continue
+                    if run is not None:
+                        self._allreduce(run[1], (run[2] - run[1]) // 4, _NCCL_OP[run[0]])
+                    run = [op, addr_v, addr_v + 4 * count]
+                if run is not None:
+                    self._allreduce(run[1], (run[2] - run[1]) // 4, _NCCL_OP[run[0]])
 
     # ---- recorded sequences
     def capture(self, fn):

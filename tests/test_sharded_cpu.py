@@ -96,6 +96,18 @@ def _worker(rank, world, port, out):
     m[:] = be.max(x, axis=1)
     assert [p.kind for p in be.plans] == ["red_rows", "ew_2d"] and be.calls == [(1, rows)]
 
+    # two sums of one pass (E[x], E[x^2]): their results sit next to each other in scratch and
+    # cross the GPUs in ONE all-reduce (two rows-long results, the first padded to 256 bytes);
+    # a max next to a sum needs a collective of its own
+    be.plans, be.calls = [], []
+    m[:] = be.sum(x * x, axis=1) * (1.0 / cols) - be.square(be.sum(x, axis=1) * (1.0 / cols))
+    assert [p.kind for p in be.plans] == ["red_rows", "ew_2d"]
+    padded = (4 * rows + 255) // 256 * 64
+    assert be.calls == [(0, padded + rows)], be.calls
+    be.plans, be.calls = [], []
+    m[:] = be.sum(x, axis=1) + be.max(x, axis=1)
+    assert sorted(be.calls) == [(0, rows), (1, rows)], be.calls
+
     # axis-0 reductions and element-wise work stay local
     be.plans, be.calls = [], []
     s0 = be.empty((1, cols), parallel=True)
