@@ -1666,7 +1666,12 @@ class Planner(object):
             if st.flat and self._lin is None:
                 lin_expr = "(u64)n"                       # one row: the element index is n itself
             elif st.flat:
-                lin_expr = "(u64)(n + k)"                 # the skeleton passes the row's index shift as k
+                # the skeleton passes the row's index shift as k.  While the enclosing tensor has
+                # fewer than 2^32 elements the sum fits 32 bits, and the upper word of the random
+                # counter is a literal zero the hash can fold, as in the unsharded kernel
+                shard_cols = self._lin[2]
+                enclosing = (st.out_shape[1] // max(shard_cols, 1)) * self._lin[0]
+                lin_expr = "(u64)((u32)n + (u32)k)" if enclosing < (1 << 32) else "(u64)(n + k)"
             elif ra == 1:
                 lin_expr = "(u64)(p.lin_0 + %s * p.lin_r + %s)" % (row, col)     # lin_c is 1
             else:
@@ -1681,6 +1686,7 @@ class Planner(object):
         big = self.ew_unroll
         unroll = big if total >= self.target * BLOCK * big else (2 if total >= self.target * BLOCK else 1)
         unroll = min(unroll, big)
+        block = BLOCK
         if not st.flat and nvec >= BLOCK * unroll and K <= 65535 * 65535:
             # long rows: blocks tile each row (block y/z = row), no index division
             mode = 2
@@ -1691,11 +1697,13 @@ class Planner(object):
                 # flat view of a column shard whose kernel needs element coordinates (random
                 # words): blocks must not straddle rows
                 cl = self._lin[2]
-                while unroll > 1 and cl % (BLOCK * unroll * V):
-                    unroll //= 2
-                assert cl % (BLOCK * unroll * V) == 0 and N % V == 0
+                # whole blocks per row; short rows: half-size blocks keep the vectors per thread up
+                fits = [(u, b) for b in (BLOCK, BLOCK // 2) for u in (4, 2, 1)
+                        if u <= unroll and cl % (b * u * V) == 0]
+                assert fits and N % V == 0
+                unroll, block = max(fits, key=lambda ub: (ub[0], -ub[1]))
                 mode = 3
-                bpr = cl // (BLOCK * unroll * V)
+                bpr = cl // (block * unroll * V)
                 shard_rows = N // cl
                 f.u32("flat_bpr", bpr)
                 f.u32("flat_rows", shard_rows)
@@ -1705,17 +1713,18 @@ class Planner(object):
                 grid = (max(1, (total + BLOCK * unroll - 1) // (BLOCK * unroll)), 1, 1)
         widest = max([DT_SIZE[odt]] + [DT_SIZE[o.dt] for o, _ in em.lane_ops])
         idx32 = mode != 0 and (N + BLOCK * unroll * V) * widest < (1 << 32)
-        call = "ew_kernel<S, P, %d, %d, %d, %d, %s>(p);" % (V, BLOCK, unroll, mode, "true" if idx32 else "false")
+        call = "ew_kernel<S, P, %d, %d, %d, %d, %s>(p);" % (V, block, unroll, mode, "true" if idx32 else "false")
         min_blocks = self.ew_min_blocks
         if min_blocks is None:
             moved = DT_SIZE[odt] + sum(DT_SIZE[o.dt] for o, _ in em.lane_ops)
             min_blocks = 5 if self._issue_bound(st, moved, rounding) else 4
+        min_blocks *= BLOCK // block
         src, name = self._source(f, em, ["out[0][i] = %s;" % val], 0, "OP_SUM", None, st_lines, call,
-                                 min_blocks=min_blocks)
+                                 min_blocks=min_blocks, block=block)
         pz = Pass()
         pz.name = name
         pz.kind = "ew_flat" if st.flat else "ew_2d"
-        pz.source, pz.fields, pz.grid, pz.block = src, f, grid, (BLOCK, 1, 1)
+        pz.source, pz.fields, pz.grid, pz.block = src, f, grid, (block, 1, 1)
         pz.uses_rng = em.uses_rng
         pz.desc = "%s V=%d K=%d N=%d grid=%s" % (pz.kind, V, K, N, grid)
         if "lin_r" in f.values:
@@ -1729,7 +1738,8 @@ class Planner(object):
         return pz
 
     @staticmethod
-    def _source(f, em, eval_tail, nred, ops, ep_lines, st_lines, call, min_blocks=1, acc_tail=None, xc=None):
+    def _source(f, em, eval_tail, nred, ops, ep_lines, st_lines, call, min_blocks=1, acc_tail=None, xc=None,
+                block=BLOCK):
         ind = "\n        "
         nout = max(nred, 1)
         parts = ['#include "optree_templates.cuh"', "using namespace b200;", f.decl(), "template <int V> struct S {"]
@@ -1760,5 +1770,5 @@ class Planner(object):
         import zlib
         name = "ot_%s_%08x" % (call.split("<")[0], zlib.crc32(body.encode()) & 0xFFFFFFFF)
         body += ('extern "C" __global__ void __launch_bounds__(%d, %d) %s(const __grid_constant__ P p) { %s }\n'
-                 % (BLOCK, min_blocks, name, call))
+                 % (block, min_blocks, name, call))
         return body, name
