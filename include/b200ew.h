@@ -137,7 +137,10 @@ b200_status b200_cache_stats(uint64_t *compiled, uint64_t *disk_hits, uint64_t *
  * replaces kernel.prepared_async_call(grid, block, stream, *args, shared_size)
  * (neon/backends/float_ew.py:929-931).  `params` is the kernel's single
  * by-value parameter struct (<= 4096 bytes).  cluster_x > 1 launches
- * thread-block clusters; cooperative != 0 guarantees co-residency of the grid. */
+ * thread-block clusters.  `cooperative` is a set of bits: 1 guarantees
+ * co-residency of the grid; 2 says that the kernel executes griddepcontrol.wait
+ * before its first memory access, so its blocks may be scheduled while the
+ * previous kernel of the stream drains (programmatic dependent launch). */
 b200_status b200_launch(uint64_t kernel, uint32_t grid_x, uint32_t grid_y, uint32_t grid_z,
                         uint32_t block_x, uint32_t block_y, uint32_t block_z,
                         uint32_t smem_bytes, uint64_t stream,

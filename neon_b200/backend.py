@@ -134,6 +134,9 @@ class B200Backend(OpTreeBackend):
         self.set_stochastic_round(stochastic_round)
         self._scratch = _Scratch()
         self._planner = Planner(self.sm_count, precise_math=precise_math)
+        # generated kernels wait for the previous kernel of the stream themselves (first instruction),
+        # so the next launch's blocks can be placed while this one drains
+        self.dependent_launch = os.environ.get("B200EW_DEPENDENT_LAUNCH", "1") != "0"
         self._status = rt.malloc(256)          # kernels set it when a bounded wait gives up
         rt.memset(self._status, 0, 1, 256)
         self._planner.status_ptr = self._status
@@ -506,7 +509,7 @@ class B200Backend(OpTreeBackend):
             rt.event_record(self._trace_events[0], self.stream)
         mark = self._timeline_begin("kernel", pz.name) if self._timeline is not None else None
         rt.launch(kernel, pz.grid, pz.block, pz.fields.pack(), smem=pz.smem, stream=self.stream,
-                  cluster=pz.cluster)
+                  cluster=pz.cluster, dependent=self.dependent_launch)
         if mark is not None:
             rt.event_record(mark, self.stream)
         if self.bench:

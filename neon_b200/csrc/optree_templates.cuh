@@ -41,6 +41,16 @@ typedef unsigned char u8;
 
 namespace b200 {
 
+// First statement of every generated kernel.  Launched with the "programmatic stream
+// serialization" attribute, a kernel's blocks may become resident while the previous kernel of
+// the stream still runs: griddepcontrol.wait holds them until that kernel has completed and its
+// writes are visible (a no-op after a plain launch); launch_dependents lets the next kernel's
+// blocks in as soon as every block of this one has started.
+DEV void grid_enter() {
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+
 enum { F32 = 0, F16 = 1, BF16 = 2, I32 = 3, U32 = 4, I16 = 5, U16 = 6, I8 = 7, U8 = 8 };
 // OP_MOM_MEAN / OP_MOM_M2 are a PAIR of neighbouring reduction slots (r, r + 1) that together
 // carry the first two moments of one expression: see "moments" below.

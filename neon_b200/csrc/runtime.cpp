@@ -637,16 +637,23 @@ b200_status b200_launch(uint64_t kernel, uint32_t gx, uint32_t gy, uint32_t gz,
     cfg.blockDim = dim3(bx, by, bz);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = as_stream(stream);
-    cudaLaunchAttribute attrs[2];
+    cudaLaunchAttribute attrs[3];
     int na = 0;
     if (cluster_x > 1) {
         attrs[na].id = cudaLaunchAttributeClusterDimension;
         attrs[na].val.clusterDim.x = cluster_x; attrs[na].val.clusterDim.y = 1; attrs[na].val.clusterDim.z = 1;
         ++na;
     }
-    if (cooperative) {
+    if (cooperative & 1) {
         attrs[na].id = cudaLaunchAttributeCooperative;
         attrs[na].val.cooperative = 1;
+        ++na;
+    }
+    if (cooperative & 2) {
+        // the kernel executes griddepcontrol.wait before it touches memory: its blocks may be
+        // scheduled while the previous kernel of the stream drains
+        attrs[na].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attrs[na].val.programmaticStreamSerializationAllowed = 1;
         ++na;
     }
     cfg.attrs = na ? attrs : nullptr;

@@ -984,7 +984,7 @@ class Planner(object):
         text = "\n".join(parts) + "\n"
         import zlib
         name = "ot_rowres_kernel_%08x" % (zlib.crc32((text + "\n".join(body)).encode()) & 0xFFFFFFFF)
-        text += ('extern "C" __global__ void __launch_bounds__(%d, %d) %s(const __grid_constant__ P p) {\n    %s\n}\n'
+        text += ('extern "C" __global__ void __launch_bounds__(%d, %d) %s(const __grid_constant__ P p) {\n    grid_enter();\n    %s\n}\n'
                  % (threads, blocks_per_sm, name, "\n    ".join(body)))
         pz = Pass()
         pz.kind = "rowres"
@@ -1769,6 +1769,6 @@ class Planner(object):
         # kernel name = skeleton + digest of the instance, so profiles can tell instances apart
         import zlib
         name = "ot_%s_%08x" % (call.split("<")[0], zlib.crc32(body.encode()) & 0xFFFFFFFF)
-        body += ('extern "C" __global__ void __launch_bounds__(%d, %d) %s(const __grid_constant__ P p) { %s }\n'
+        body += ('extern "C" __global__ void __launch_bounds__(%d, %d) %s(const __grid_constant__ P p) { grid_enter(); %s }\n'
                  % (block, min_blocks, name, call))
         return body, name

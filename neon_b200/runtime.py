@@ -292,9 +292,9 @@ def kernel_max_clusters(kernel, threads, smem, cluster, grid_blocks):
     return n.value
 
 
-def launch(kernel, grid, block, params, smem=0, stream=0, cluster=1, cooperative=False):
+def launch(kernel, grid, block, params, smem=0, stream=0, cluster=1, cooperative=False, dependent=False):
     check(lib().b200_launch(kernel, grid[0], grid[1], grid[2], block[0], block[1], block[2],
-                            smem, stream, params, len(params), cluster, 1 if cooperative else 0))
+                            smem, stream, params, len(params), cluster, (1 if cooperative else 0) | (2 if dependent else 0)))
 
 
 def graph_begin(stream=0):
