@@ -172,6 +172,46 @@ def _worker(rank, world, port, out):
     gathered = [None] * world
     dist.all_gather_object(gathered, be._xepoch)
     assert all(g == gathered[0] for g in gathered)
+
+    # ---- recorded sequences: a replay moves the device word the recorded parameters are relative
+    #      to, so that recorded and eager exchanges together use consecutive launch numbers
+    from neon_b200 import runtime as rt_mod
+    words, launched = [], []
+    saved = (rt_mod.graph_begin, rt_mod.graph_end, rt_mod.graph_launch, rt_mod.graph_destroy, rt_mod.memset)
+    rt_mod.graph_begin = lambda stream: None
+    rt_mod.graph_end = lambda stream: 1
+    rt_mod.graph_destroy = lambda handle: None
+    rt_mod.memset = lambda ptr, value, width, count, stream=0: words.append(value)
+    be.synchronize = lambda: None
+    be._xbase_word = 0x7D0000100000
+    try:
+        def sequence():
+            m[:] = be.max(x, axis=1)
+            total[:] = be.sum(z)
+        start = be._xepoch
+        params = []                                 # the launch-number parameter of every launch, as issued
+        plain_launch = be._launch
+        be._launch = lambda pz: (params.append(pz.fields.values["x_epoch"]), plain_launch(pz))
+        graph = be.capture(sequence)                # runs eagerly once (two numbers), then records
+        eager_params, recorded = params[:2], params[2:]
+        assert eager_params == [start + 1, start + 2] and recorded == [start + 3, start + 4]
+        assert be._xepoch == start + 2              # recording launched nothing
+        numbers = []
+        rt_mod.graph_launch = lambda handle, stream: numbers.extend((r + words[-1]) & 0xFFFFFFFF for r in recorded)
+        graph.replay()
+        del params[:]
+        m[:] = be.min(x, axis=1)                    # an eager exchange between two replays
+        numbers.append((params[0] + words[-1]) & 0xFFFFFFFF)
+        graph.replay()
+        assert numbers == list(range(start + 3, start + 8)), (numbers, start)
+        assert be._xepoch == start + 7
+        gathered = [None] * world
+        dist.all_gather_object(gathered, numbers)
+        assert all(g == gathered[0] for g in gathered)
+    finally:
+        rt_mod.graph_begin, rt_mod.graph_end, rt_mod.graph_launch, rt_mod.graph_destroy, rt_mod.memset = saved
+        del be.synchronize
+        be._launch = plain_launch
     be._xchg = None
     be._plans.clear()
 
