@@ -89,10 +89,20 @@ class _PlanCache(object):
 class CapturedGraph(object):
     """A recorded statement sequence (see ``B200Backend.capture``)."""
 
-    def __init__(self, backend, handle, launches):
+    def __init__(self, backend, handle, launches, rng_table=0, rng_count=0):
         self.backend, self.handle, self.launches = backend, handle, launches
+        # recorded launches that draw random numbers read their keys from this device table
+        self.rng_table, self.rng_count = rng_table, rng_count
+        self._keys = np.empty((max(rng_count, 1), 2), np.uint32)
 
     def replay(self):
+        if self.rng_count:
+            # the keys the same launches would be given now, in the recorded order: a replay
+            # draws exactly the random words eager execution would draw at this point
+            keys = self._keys
+            for i in range(self.rng_count):
+                keys[i] = rt.rng_next_key()
+            rt.memcpy_h2d(self.rng_table, keys.ctypes.data, keys.nbytes, self.backend.stream, sync=False)
         rt.graph_launch(self.handle, self.backend.stream)
         self.backend.launches += self.launches
 
@@ -101,6 +111,9 @@ class CapturedGraph(object):
             if self.handle:
                 rt.graph_destroy(self.handle)
                 self.handle = 0
+            if self.rng_table:
+                rt.free(self.rng_table)
+                self.rng_table = 0
         except Exception:
             pass
 
@@ -137,6 +150,7 @@ class B200Backend(OpTreeBackend):
         # generated kernels wait for the previous kernel of the stream themselves (first instruction),
         # so the next launch's blocks can be placed while this one drains
         self.dependent_launch = os.environ.get("B200EW_DEPENDENT_LAUNCH", "1") != "0"
+        self._rng_rec = None                   # set while a sequence is being recorded (see _record)
         self._status = rt.malloc(256)          # kernels set it when a bounded wait gives up
         rt.memset(self._status, 0, 1, 256)
         self._planner.status_ptr = self._status
@@ -500,9 +514,16 @@ class B200Backend(OpTreeBackend):
             if pz.setup is not None:
                 pz.setup(rt, kernel, pz)
         if pz.uses_rng:
-            k0, k1 = rt.rng_next_key()
-            pz.fields.values["rk0"] = k0
-            pz.fields.values["rk1"] = k1
+            rec = self._rng_rec
+            vals = pz.fields.values
+            if rec is None:
+                vals["rk0"], vals["rk1"] = rt.rng_next_key()
+                vals["rk_tab"] = 0
+            else:                               # being recorded: the key comes from the graph's table at replay
+                if rec["count"] >= rec["capacity"]:
+                    raise RuntimeError("more than %d launches with random numbers in one recorded sequence" % rec["capacity"])
+                vals["rk_tab"] = rec["table"] + 8 * rec["count"]
+                rec["count"] += 1
         if self.bench:
             if self._trace_events is None:
                 self._trace_events = (rt.event_create(), rt.event_create())
@@ -625,19 +646,34 @@ class B200Backend(OpTreeBackend):
         call, which is what makes small, launch-bound statements (a few MB per tensor)
         run at the speed of their kernels instead of the speed of the host.  ``fn`` runs
         twice here: once eagerly (compiles, allocates temporaries), once recorded.
-        Tensor addresses and python numbers are frozen as recorded, and statements that
-        draw random numbers replay the same random words; ``fn`` must not read tensors
-        back or create them.
+        Tensor addresses and python numbers are frozen as recorded; ``fn`` must not read
+        tensors back or create them.  Statements that draw random numbers (``rand``,
+        dropout masks, stochastic rounding) draw fresh ones in every replay -- the words
+        eager execution would draw at that point, bit for bit: their launches read the
+        key of their random stream from a small device table that ``replay`` refills.
+        (``compensated_sum`` is not an op-tree statement: its rounding repeats.)
         """
+        handle, launches, table, count = self._record(fn)
+        return CapturedGraph(self, handle, launches, table, count)
+
+    def _record(self, fn):
+        """Run ``fn`` once, then record it: (graph handle, launches, key table, keys)."""
         fn()
         self.synchronize()
         before = self.launches
-        rt.graph_begin(self.stream)
+        rec = self._rng_rec = {"table": rt.malloc(8 * 1024), "capacity": 1024, "count": 0}
         try:
-            fn()
+            rt.graph_begin(self.stream)
+            try:
+                fn()
+            finally:
+                handle = rt.graph_end(self.stream)
         finally:
-            handle = rt.graph_end(self.stream)
-        return CapturedGraph(self, handle, self.launches - before)
+            self._rng_rec = None
+            if rec["count"] == 0:
+                rt.free(rec["table"])
+                rec["table"] = 0
+        return handle, self.launches - before, rec["table"], rec["count"]
 
     def copy_transpose(self, a, out, axes=None, repeat=1):
         """out = numpy.transpose(a, axes) for tensors of any rank, views included

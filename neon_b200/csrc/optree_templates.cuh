@@ -245,6 +245,17 @@ DEV u32 rng_hash(const Rng& g, u32 lo, u32 hi) {
     return x;
 }
 DEV u32 rng_bits(const Rng& g, u64 idx) { return rng_hash(g, (u32)idx, (u32)(idx >> 32)); }
+// The key of a launch's random stream: its parameters -- or, for a launch that is replayed from a
+// recorded graph, the two words at `tab`, which the host fills before every replay with the key
+// an eager launch would have been given at that point.
+DEV Rng rng_key(u32 k0, u32 k1, u64 tab) {
+    Rng g{k0, k1};
+    if (tab) {
+        const uint2 k = *reinterpret_cast<const uint2*>(tab);
+        g.k0 = k.x; g.k1 = k.y;
+    }
+    return g;
+}
 // 16-bit float stores need at most 13 random bits per element (the top bits of
 // the word), so eight neighbouring elements share ONE hash: group = idx >> 3 is
 // hashed, the four element pairs of the group take successive steps of a linear

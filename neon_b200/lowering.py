@@ -1419,8 +1419,12 @@ class Planner(object):
                 self.uses_rng = True
                 self.f.u32("rk0", 0)
                 self.f.u32("rk1", 0)
+                self.f.u64("rk_tab", 0)
+                fetch = "const Rng rkey = rng_key(p.rk0, p.rk1, p.rk_tab);"
+                if fetch not in self.e_pre:
+                    self.e_pre.append(fetch)
                 sid = 1 + sum(1 for m in self.st.nodes[:n.nid] if m.kind == "z" and m.op == "rand")
-                self.e_lines.append("const float %s = frand(Rng{p.rk0 + %uu, p.rk1}, %s);"
+                self.e_lines.append("const float %s = frand(Rng{rkey.k0 + %uu, rkey.k1}, %s);"
                                     % (name, (sid * 0x68E31DA4) & 0xFFFFFFFF, self.lin_index()))
             else:
                 o, _ = self._leaf(self.st._memo[("t", n.tix)])
@@ -1643,6 +1647,7 @@ class Planner(object):
             em.uses_rng = True
             f.u32("rk0", 0)
             f.u32("rk1", 0)
+            f.u64("rk_tab", 0)
             f.i32("sr_mb", int(rounding))
             em.lin_index()
             # element index of lane i = idx0 + i*step; row-major index of the output tensor
@@ -1661,7 +1666,7 @@ class Planner(object):
             # masks fold; at the full mantissa width of a 16-bit float the mask is dropped, the
             # truncating conversion that follows clears the same bits
             full = (odt == DT_CODES["f2"] and int(rounding) == 10) or (odt == DT_CODES["bf2"] and int(rounding) == 7)
-            st_lines.append("SrCtx c = sr_ctx(%d);%s const Rng g{p.rk0, p.rk1}; u32 ur[V];"
+            st_lines.append("SrCtx c = sr_ctx(%d);%s const Rng g = rng_key(p.rk0, p.rk1, p.rk_tab); u32 ur[V];"
                             % (int(rounding), " c.mask = 0xffffffffu;" if full else ""))
             if st.flat and self._lin is None:
                 lin_expr = "(u64)n"                       # one row: the element index is n itself

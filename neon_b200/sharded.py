@@ -281,18 +281,20 @@ class ShardedBackend(B200Backend):
         finish across the GPUs number their launches; a replay gives the recorded launches
         fresh numbers by moving the device word their parameters are relative to, so recorded
         and eager statements can be mixed freely."""
-        fn()
-        self.synchronize()
-        first, before = self._xepoch, self.launches
-        rt.graph_begin(self.stream)
-        try:
+        state = {}
+
+        def run():
+            # _record calls this twice: eagerly, then while recording
+            if "runs" in state:
+                state["first"] = self._xepoch
+            state["runs"] = True
             fn()
-        finally:
-            handle = rt.graph_end(self.stream)
+        handle, launches, table, keys = self._record(run)
+        first = state["first"]
         count = self._xepoch - first
         self._xepoch = first                      # nothing was launched while recording
         self.exchanges -= count
-        return ShardedGraph(self, handle, self.launches - before, first, count, self._xbase)
+        return ShardedGraph(self, handle, launches, first, count, self._xbase, table, keys)
 
     def _merge_arg(self, op, addr_v, addr_i, count, like):
         """argmax / argmin across the shards: every rank contributes (extreme value,
@@ -329,8 +331,8 @@ class ShardedBackend(B200Backend):
 class ShardedGraph(CapturedGraph):
     """A recorded statement sequence of a ShardedBackend (see ``ShardedBackend.capture``)."""
 
-    def __init__(self, backend, handle, launches, first, count, base):
-        super(ShardedGraph, self).__init__(backend, handle, launches)
+    def __init__(self, backend, handle, launches, first, count, base, rng_table=0, rng_count=0):
+        super(ShardedGraph, self).__init__(backend, handle, launches, rng_table, rng_count)
         # the recorded exchange launches carry parameters first + 1 - base .. first + count - base
         self.first, self.count, self.base = first, count, base
 

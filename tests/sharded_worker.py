@@ -117,6 +117,29 @@ def main():
             check_output("replayed y, turn %d" % turn, y.get(), yy, np.float32)
             check_output("replayed max, turn %d" % turn, top.get(), tt, np.float32)
             check_output("eager min after replay %d" % turn, low.get(), yy.min(1, keepdims=True), np.float32)
+        del graph
+        # stochastic rounding inside a recorded sharded sequence: replays draw what eager steps would
+        zq = be.empty((rows, cols), dtype=np.float16, parallel=True)
+        zq.rounding = True
+
+        def rounded():
+            zq[:] = y * 1.0009765625 + top
+            x[:] = x * 0.5 + 0.25
+            y[:] = (x - be.mean(x, axis=1)) * 3.0
+        x.local.set(xh[:, x.c0:x.c0 + x.local.shape[1]])
+        be.rng_reset()
+        eager_bits = []
+        for _ in range(4):
+            rounded()
+            eager_bits.append(zq.local.get().view(np.uint16).copy())
+        x.local.set(xh[:, x.c0:x.c0 + x.local.shape[1]])
+        be.rng_reset()
+        graph = be.capture(rounded)
+        assert graph.rng_count == 1 and graph.count == 1
+        assert np.array_equal(zq.local.get().view(np.uint16), eager_bits[0])
+        for i in range(1, 4):
+            graph.replay()
+            assert np.array_equal(zq.local.get().view(np.uint16), eager_bits[i]), "replayed rounding, step %d" % i
         del x, y, graph
 
     # ---- fp16 chain with stochastic rounding + whole-tensor reductions (config 5 shape class)

@@ -624,6 +624,55 @@ def test_graph_replay_of_a_statement_sequence(b200):
     be.synchronize()
 
 
+def test_graph_replay_draws_the_random_words_eager_execution_would(b200):
+    """Stochastic rounding, a dropout mask and rand inside a recorded sequence: every replay is
+    bit for bit what the next eager execution of the sequence would have produced."""
+    be = b200
+    rng = np.random.RandomState(2)
+    xh = rng.uniform(-4, 4, (300, 257)).astype(np.float32)
+    x = be.array(xh)
+    z = be.empty((300, 257), dtype=np.float16)
+    z.rounding = True
+    mask, noisy = be.empty((300, 257)), be.empty((300, 257))
+
+    def step():
+        z[:] = x * 1.0009765625 + 0.3
+        be.make_binary_mask(mask, keepthresh=0.6)
+        noisy[:] = x + be.rand() * 0.5
+        x[:] = x * 0.5 + 1.0                       # the sequence feeds itself
+
+    def snapshot():
+        return [t.get().copy() for t in (z, mask, noisy, x)]
+
+    state = be.rng_get_state()
+    eager = []
+    for _ in range(4):
+        step()
+        eager.append(snapshot())
+    # the same four steps again: one eager (inside capture), three replayed
+    x.set(xh)
+    be.rng_set_state(state)
+    graph = be.capture(step)
+    assert graph.rng_count == 3
+    got = [snapshot()]
+    for _ in range(3):
+        graph.replay()
+        got.append(snapshot())
+    for i, (want, have) in enumerate(zip(eager, got)):
+        for name, w, h in zip(("z", "mask", "noisy", "x"), want, have):
+            assert np.array_equal(w.view(np.uint8), h.view(np.uint8)), (i, name)
+    assert not np.array_equal(got[1][1], got[2][1])            # and the masks do change between replays
+    # eager execution carries on from the same point of the random stream
+    step()
+    after_replays = snapshot()
+    x.set(xh)
+    be.rng_set_state(state)
+    for _ in range(5):
+        step()
+    for w, h in zip(snapshot(), after_replays):
+        assert np.array_equal(w.view(np.uint8), h.view(np.uint8))
+
+
 def test_bench_flag_records_every_launch(tmp_path):
     """be.bench turns on per-launch timing (the reference prints msecs per compound kernel,
     float_ew.py:917-938); here the records are kept and can be dumped as JSON."""
