@@ -608,6 +608,12 @@ def main():
     e2e_ms, _ = job.time_steps(e2e_step, e2e_steps)
     clocks = sampler.stop() if rank == 0 else None      # sampled over both timed regions
     breakdown = job.breakdown(lambda s: statements(be, x, y, z, total, peak))
+    # the step recorded once and replayed (fresh rounding bits in every replay, see be.capture)
+    graph = be.capture(lambda: statements(be, x, y, z, total, peak))
+    for _ in range(3):
+        graph.replay()
+    replay_total, _ = job.time_steps(lambda s: graph.replay(), args.steps)
+    del graph
 
     # ---- the other sharded configurations and (N > 1) the weak-scaling figure
     also, weak = {}, None
@@ -661,6 +667,10 @@ def main():
         "e2e": {"value": e2e_value, "unit": "GB/s", "h2d_bytes_per_step": 2 * nbytes * world,
                 "d2h_bytes_per_step": 8 * world, "steps": e2e_steps, "ms_per_step": e2e_ms / e2e_steps},
         "gpu_launches": launches, "clocks": clocks, "breakdown": breakdown,
+        "graph_replay": {"ms_per_step": replay_total / args.steps,
+                         "GBps": n_global * BYTES_PER_ELEMENT / (replay_total / args.steps * 1e-3) / 1e9,
+                         "note": "the three statements recorded once with be.capture(), replayed with one call; "
+                                 "every replay draws fresh rounding bits"},
         "results": {"total": res_total, "peak": res_peak},
     }
     if also:
