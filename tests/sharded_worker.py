@@ -123,16 +123,16 @@ def main():
         zq.rounding = True
 
         def rounded():
+            y[:] = (x - be.mean(x, axis=1)) * 3.0
             zq[:] = y * 1.0009765625 + top
             x[:] = x * 0.5 + 0.25
-            y[:] = (x - be.mean(x, axis=1)) * 3.0
-        x.local.set(xh[:, x.c0:x.c0 + x.local.shape[1]])
+        x.local.set(np.ascontiguousarray(xh[:, x.c0:x.c0 + x.local.shape[1]]))
         be.rng_reset()
         eager_bits = []
         for _ in range(4):
             rounded()
             eager_bits.append(zq.local.get().view(np.uint16).copy())
-        x.local.set(xh[:, x.c0:x.c0 + x.local.shape[1]])
+        x.local.set(np.ascontiguousarray(xh[:, x.c0:x.c0 + x.local.shape[1]]))
         be.rng_reset()
         graph = be.capture(rounded)
         assert graph.rng_count == 1 and graph.count == 1
