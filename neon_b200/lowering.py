@@ -167,15 +167,26 @@ def shares_memory(a, b):
 
 
 def eval_recipe(recipe, stack):
+    """fp32 value of a folded constant (the caller silences numpy's floating-point warnings)."""
     kind = recipe[0]
     if kind == "l":
         return np.float32(float(stack[recipe[1]]))
     if kind == "k":
         return np.float32(recipe[1])
-    with np.errstate(all="ignore"):
-        if kind == "u":
-            return np.float32(UNARY_HOST[recipe[1]](eval_recipe(recipe[2], stack)))
-        return np.float32(BINARY_HOST[recipe[1]](eval_recipe(recipe[2], stack), eval_recipe(recipe[3], stack)))
+    if kind == "u":
+        return np.float32(UNARY_HOST[recipe[1]](eval_recipe(recipe[2], stack)))
+    return np.float32(BINARY_HOST[recipe[1]](eval_recipe(recipe[2], stack), eval_recipe(recipe[3], stack)))
+
+
+def _recipe_reads_stack(recipe):
+    """Does a folded constant depend on a python number of the program (which a later call with
+    the same program_key may change)?"""
+    kind = recipe[0]
+    if kind == "l":
+        return True
+    if kind == "k":
+        return False
+    return any(_recipe_reads_stack(r) for r in recipe[2:])
 
 
 def program_key(stack):
@@ -232,7 +243,11 @@ class BoundPlan(object):
                 elif name[0] == "t" and name[1:].isdigit():
                     ptrs.append((name, st.tensor_pos[int(name[1:])]))
                 elif name[0] == "c" and name[1:].isdigit():
-                    consts.append((name, st.nodes[int(name[1:])].extra))
+                    recipe = st.nodes[int(name[1:])].extra
+                    if _recipe_reads_stack(recipe):
+                        consts.append((name, recipe))
+                    # else: folded from literals of the expression's structure only; the planner
+                    # has stored its value and it cannot change between calls
             self.binds.append((ptrs, consts, takes))
 
     def rebind(self, stack):
@@ -243,8 +258,11 @@ class BoundPlan(object):
             for name, pos in ptrs:
                 obj = stack[pos]
                 vals[name] = (obj["idx"] if type(obj) is dict else obj).ptr
-            for name, recipe in consts:
-                vals[name] = float(eval_recipe(recipe, stack))
+            if consts:
+                # constants may overflow or divide by zero exactly as the kernel would
+                with np.errstate(all="ignore"):
+                    for name, recipe in consts:
+                        vals[name] = float(eval_recipe(recipe, stack))
 
 
 def _fast_flat_ok(t, out_shape):

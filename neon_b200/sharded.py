@@ -203,13 +203,18 @@ class ShardedBackend(B200Backend):
 
     # ---- one statement
     def _run_stack(self, out, stack):
-        sharded = [s for s in stack if isinstance(s, ShardedTensor)]
+        sharded, local_stack = [], []
+        for s in stack:                         # one walk: which operands are shards, and the rank's view of the program
+            if type(s) is ShardedTensor:
+                sharded.append(s)
+                local_stack.append(s.local)
+            else:
+                local_stack.append(s)
         if not sharded:
             return super(ShardedBackend, self)._run_stack(out, stack)
         lin = None
-        if isinstance(out, ShardedTensor):
+        if type(out) is ShardedTensor:
             lin = out.flat_of if out.flat_of else (out.shape[1], out.c0, out.local.shape[1])
-        local_stack = [s.local if isinstance(s, ShardedTensor) else s for s in stack]
         if self.check_bounds:
             self.check_operands(local_stack)
         rounding = self._rounding_bits(local_stack[0])
