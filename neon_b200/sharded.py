@@ -302,23 +302,36 @@ class ShardedBackend(B200Backend):
         return ShardedGraph(self, handle, launches, first, count, self._xbase, table, keys)
 
     def _merge_arg(self, op, addr_v, addr_i, count, like):
-        """argmax / argmin across the shards: every rank contributes (extreme value,
-        global column index) per row, all ranks gather the pairs and keep, per row,
-        the index of the first rank that holds the extreme value -- columns grow with
-        the rank, so that is the first occurrence, as numpy.argmax gives it."""
-        from .tensor import B200Tensor
+        """argmax / argmin across the shards on the path without the exchange area: every rank
+        contributes (extreme value, local index) per row, all ranks gather the pairs, and the
+        host of each rank -- all with the same data, so all with the same answer -- turns the
+        indices into global ones in integer arithmetic and keeps, per row, the smallest global
+        index among the ranks that hold the extreme value: the first occurrence, as
+        numpy.argmax gives it.  (Synchronous, a few hundred bytes per row: this is the
+        fallback; the exchange area does the same inside the reduction kernel.)"""
         W = self.world_size
-        idx = B200Tensor(self, (1, count), np.int32, gpudata=addr_i)
-        c0 = like.c0 if like.flat_of is None else 0
-        idx[:] = idx + float(c0)                                   # local -> global column
-        vals = self.empty((W, count), dtype=np.float32)
-        idxs = self.empty((W, count), dtype=np.int32)
-        rt.allgather(self.comm, addr_v, vals.ptr, 4 * count, self.stream)
-        rt.allgather(self.comm, addr_i, idxs.ptr, 4 * count, self.stream)
-        self.collectives += 2
-        winner = self.empty((1, count), dtype=np.int32)
-        winner[:] = self.argmax(vals, axis=0) if op == "argmax" else self.argmin(vals, axis=0)
-        idx[:] = self.sum(self.onehot(winner, axis=0) * idxs, axis=0)
+        vals, idxs = rt.malloc(4 * count * W), rt.malloc(4 * count * W)
+        try:
+            rt.allgather(self.comm, addr_v, vals, 4 * count, self.stream)
+            rt.allgather(self.comm, addr_i, idxs, 4 * count, self.stream)
+            self.collectives += 2
+            hv, hi = np.empty((W, count), np.float32), np.empty((W, count), np.int32)
+            rt.memcpy_d2h(hv.ctypes.data, vals, hv.nbytes, self.stream, sync=True)
+            rt.memcpy_d2h(hi.ctypes.data, idxs, hi.nbytes, self.stream, sync=True)
+        finally:
+            rt.free(vals)
+            rt.free(idxs)
+        glob = hi.astype(np.int64)
+        if like.flat_of is None:
+            per = like.shape[1] // W
+            glob += (np.arange(W, dtype=np.int64) * per)[:, None]
+        else:                                   # index into the flattened shard -> into the flattened tensor
+            gcols, _, lcols = like.flat_of
+            glob = (glob // lcols) * gcols + (np.arange(W, dtype=np.int64) * lcols)[:, None] + glob % lcols
+        best = hv.max(axis=0) if op == "argmax" else hv.min(axis=0)
+        glob[hv != best[None, :]] = np.iinfo(np.int64).max
+        winner = glob.min(axis=0).astype(np.int32)
+        rt.memcpy_h2d(addr_i, winner.ctypes.data, winner.nbytes, self.stream, sync=True)
 
     def _allreduce(self, addr, count, op):
         mark = self._timeline_begin("collective", "allreduce") if self._timeline is not None else None
