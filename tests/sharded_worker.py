@@ -53,6 +53,15 @@ def main():
     assert np.array_equal(am.get(), x64.argmax(1).reshape(-1, 1)), "sharded argmax"
     am[:] = be.argmin(x, axis=1)
     assert np.array_equal(am.get(), x64.argmin(1).reshape(-1, 1)), "sharded argmin"
+    # a reduction on top of a reduction whose result is the statement's output: the row-resident
+    # kernel with clusters of two, both passes exchanged, the index finished by the cluster's first block
+    before_x, launches = be.exchanges, be.launches
+    am[:] = be.argmax(be.absolute(x - be.mean(x, axis=1)), axis=1)
+    if exchange:
+        assert (be.exchanges - before_x, be.launches - launches) == (1, 1)
+    dev64 = np.abs(x64 - x64.mean(1, keepdims=True))
+    picked = np.take_along_axis(dev64, am.get().astype(np.int64), axis=1)
+    assert np.all(picked >= dev64.max(1, keepdims=True) * (1 - 1e-3)), "sharded argmax of deviations, short rows"
     tie = np.round(xh.astype(np.float32)).astype(np.float16)       # many equal maxima: first one wins
     xt = be.array(tie, dtype=np.float16, parallel=True)
     am[:] = be.argmax(xt, axis=1)
