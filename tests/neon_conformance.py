@@ -19,6 +19,7 @@ import os
 import sys
 
 import numpy as np
+import pytest
 
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 if ROOT not in sys.path:
@@ -77,3 +78,14 @@ def pytest_collection_modifyitems(config, items):
     if drop:
         config.hook.pytest_deselected(items=drop)
         items[:] = keep
+
+
+@pytest.hookimpl(trylast=True)
+def pytest_runtest_setup(item):
+    """neon's older test classes prepare themselves in a plain ``setup`` method (the nose
+    convention), which current pytest no longer calls: call it once the fixtures are up."""
+    inst = getattr(item, "instance", None)
+    prepare = getattr(inst, "setup", None)
+    if inst is not None and callable(prepare) and not hasattr(inst, "setup_method"):
+        prepare()
+

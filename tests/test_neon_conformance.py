@@ -12,9 +12,9 @@ runs on neon's own cpu / mkl backends.
   front end -- a check of the front end (shape inference, operators, views, the
   lazy scalar trees optimizers build) and of this harness.
 
-Files not run: ``test_backend_autodiff_extra.py`` (nose-style ``setup`` methods that
-current pytest no longer calls), and everything about GEMM / convolution / pooling /
-recurrent layers (outside the op-tree path).
+``test_backend_autodiff_extra.py`` prepares its test class in a nose-style ``setup`` method,
+which current pytest no longer calls; the plugin calls it.  Files not run: everything about
+GEMM / convolution / pooling / recurrent layers (outside the op-tree path).
 """
 import os
 import re
@@ -40,9 +40,11 @@ GPU_FILES = {
     "test_backend_copy_transpose.py": (8, None),
     "test_backend_hist.py": (9, None),
     "test_backend_autodiff.py": (36, None),
+    "test_backend_autodiff_extra.py": (7, None),
     "test_optimizer.py": (12, None),
     "test_activations.py": (24, None),
     "test_costs.py": (25, None),
+    "test_initializers.py": (20, None),
     "test_schedule.py": (5, None),
 }
 # what the numpy checker can execute (no random numbers, histograms, rounding modes, eager shift)
@@ -52,9 +54,11 @@ CPU_FILES = {
     "test_backend_tensor.py": (32, None),
     "test_backend_copy_transpose.py": (8, None),
     "test_backend_autodiff.py": (36, None),
+    "test_backend_autodiff_extra.py": (7, None),
     "test_optimizer.py": (12, None),
     "test_activations.py": (23, "not sign"),
     "test_costs.py": (25, None),
+    "test_initializers.py": (20, None),
     "test_schedule.py": (4, "not shift"),
 }
 
