@@ -27,7 +27,7 @@ TEST_FILES = [
     "test_backend_sr.py", "test_backend_randomstate.py", "test_backend_copy_transpose.py",
     "test_backend_hist.py", "test_backend_autodiff.py", "test_backend_autodiff_extra.py",
     "test_optimizer.py", "test_activations.py", "test_costs.py", "test_schedule.py",
-    "test_initializers.py", "test_gradient_bias.py", "test_gradient_batchnorm.py", "grad_funcs.py",
+    "test_initializers.py", "test_misc.py", "test_gradient_bias.py", "test_gradient_batchnorm.py", "grad_funcs.py",
 ]
 
 
